@@ -1,0 +1,278 @@
+"""Adam with the optimizer state in host memory (reference: ``bmtrain/optim/adam_offload.py:13-386``).
+
+fp32 master weights and both moments live in pinned host DRAM.  A step is a
+three-stage software pipeline over fixed-size chunks of every shard:
+
+    D2H copy of the half gradient (copy stream 1)
+      -> AVX-512 Adam on a persistent host thread pool
+        -> H2D copy of the updated half parameter (copy stream 2)
+
+so PCIe traffic in both directions overlaps the host math.  State-dict layout
+(``state``/``param_groups``/``is_whole``) and the ``gather`` option follow the
+reference, so checkpoints resume bit-identically.
+"""
+from __future__ import annotations
+
+from collections import defaultdict
+from copy import deepcopy
+from itertools import chain
+
+import torch
+
+from ..ops import adam as _adam
+from ._distributed import state_dict_gather
+from .adam import _partition_bounds
+
+_CHUNK = 1 << 23  # elements per pipeline stage (16 MiB of half data)
+
+
+def _pinned(shape, dtype, pin):
+    t = torch.empty(shape, dtype=dtype, device="cpu")
+    if pin:
+        try:
+            t = t.pin_memory()
+        except RuntimeError:  # pragma: no cover - no CUDA runtime
+            pass
+    return t
+
+
+class AdamOffloadOptimizer(torch.optim.Optimizer):
+    """Adam whose fp32 state and math live on the host; the device only holds half parameters and gradients."""
+
+    _bmtrain_optimizer = True
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0, hold_steps=0, record_delta=False):
+        if not 0.0 <= lr:
+            raise ValueError(f"Invalid learning rate: {lr}")
+        if not 0.0 <= eps:
+            raise ValueError(f"Invalid epsilon value: {eps}")
+        if not 0.0 <= betas[0] < 1.0:
+            raise ValueError(f"Invalid beta parameter at index 0: {betas[0]}")
+        if not 0.0 <= betas[1] < 1.0:
+            raise ValueError(f"Invalid beta parameter at index 1: {betas[1]}")
+        if not 0.0 <= weight_decay:
+            raise ValueError(f"Invalid weight_decay value: {weight_decay}")
+        self.avg_delta = 0
+        self.var_delta = 0
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self._hold_steps = hold_steps
+        self.record_delta = record_delta
+        self._d2h = self._h2d = None
+        if record_delta:
+            for group in self.param_groups:
+                for p in group["params"]:
+                    p._delta_info = torch.zeros(4, dtype=torch.float32)
+
+    # ------------------------------------------------------------------ state
+    def _init_state(self, p):
+        state = self.state[p]
+        pin = p.is_cuda
+        state["step"] = 0
+        state["exp_avg"] = _pinned(p.size(), torch.float32, pin).zero_()
+        state["exp_avg_sq"] = _pinned(p.size(), torch.float32, pin).zero_()
+        state["_param_fp32"] = _pinned(p.size(), torch.float32, pin)
+        state["_param_fp32"].copy_(p.detach())
+        self._make_staging(p, state)
+        return state
+
+    @staticmethod
+    def _make_staging(p, state):
+        pin = p.is_cuda
+        if p.dtype == torch.float32:
+            state["_grad_fp32"] = _pinned(p.size(), torch.float32, pin)
+        else:
+            state["_param_fp16"] = _pinned(p.size(), p.dtype, pin)
+            state["_grad_fp16"] = _pinned(p.size(), p.dtype, pin)
+
+    def _streams(self):
+        if self._d2h is None:
+            self._d2h = torch.cuda.Stream()
+            self._h2d = torch.cuda.Stream()
+        return self._d2h, self._h2d
+
+    # ------------------------------------------------------------------- step
+    @torch.no_grad()
+    def step(self, closure=None, scale=1):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+
+        work = []  # (param, state, group, lo, hi, event)
+        on_gpu = False
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p.grad is None or not p.requires_grad:
+                    continue
+                if p.grad.is_sparse:
+                    raise RuntimeError("Adam does not support sparse gradients, please consider SparseAdam instead")
+                if p.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+                    raise RuntimeError("Adam only supports fp32, fp16 and bf16 gradients")
+                state = self.state[p]
+                if len(state) == 0:
+                    state = self._init_state(p)
+                on_gpu = on_gpu or p.is_cuda
+                n = p.numel()
+                if p.dtype == torch.float32 or n == 0:
+                    work.append((p, state, group, 0, n, None))
+                else:
+                    for lo in range(0, n, _CHUNK):
+                        work.append((p, state, group, lo, min(n, lo + _CHUNK), None))
+
+        if on_gpu:
+            d2h, h2d = self._streams()
+            d2h.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(d2h):
+                for i, (p, state, group, lo, hi, _) in enumerate(work):
+                    key = "_grad_fp32" if p.dtype == torch.float32 else "_grad_fp16"
+                    g = p.grad.reshape(-1)
+                    state[key].view(-1)[lo:hi].copy_(g[lo:hi], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(d2h)
+                    work[i] = (p, state, group, lo, hi, ev)
+
+        sum_delta = sum_sq_delta = 0.0
+        total_numel = 0
+        stepped = set()
+        for p, state, group, lo, hi, ev in work:
+            if ev is not None:
+                ev.synchronize()
+            beta1, beta2 = group["betas"]
+            sign = -1.0 if group.get("maximize", False) else 1.0
+            if id(p) not in stepped:
+                stepped.add(id(p))
+                first = True
+            else:
+                first = False
+            if p.dtype == torch.float32:
+                grad = state["_grad_fp32"] if p.is_cuda else p.grad
+                grad = grad * (sign / scale)
+                lr = 0.0 if state["step"] < self._hold_steps else group["lr"]
+                torch.optim._functional.adam(
+                    [state["_param_fp32"]], [grad], [state["exp_avg"]], [state["exp_avg_sq"]], [],
+                    [torch.tensor(float(state["step"]))],
+                    amsgrad=False, beta1=beta1, beta2=beta2, lr=lr, weight_decay=group["weight_decay"],
+                    eps=group["eps"], maximize=False,
+                )
+                state["step"] += 1
+                if p.is_cuda:
+                    with torch.cuda.stream(h2d):
+                        p.data.copy_(state["_param_fp32"], non_blocking=True)
+                else:
+                    p.data.copy_(state["_param_fp32"])
+                continue
+            if first:
+                state["step"] += 1
+            if hi == lo:
+                continue
+            lr = 0.0 if state["step"] < self._hold_steps else group["lr"]
+            if p.is_cuda:
+                grad = state["_grad_fp16"].view(-1)[lo:hi]
+            else:
+                grad = p.grad.reshape(-1)[lo:hi].contiguous()
+            if sign < 0:
+                grad = -grad
+            out_half = state["_param_fp16"].view(-1)[lo:hi]
+            delta = p._delta_info if self.record_delta else None
+            _adam.adam_cpu(
+                state["_param_fp32"].view(-1)[lo:hi], out_half, delta, grad,
+                state["exp_avg"].view(-1)[lo:hi], state["exp_avg_sq"].view(-1)[lo:hi],
+                beta1, beta2, group["eps"], lr, scale, group["weight_decay"], state["step"],
+            )
+            total_numel += hi - lo
+            if self.record_delta:
+                sum_delta += float(delta[2])
+                sum_sq_delta += float(delta[3])
+            if p.is_cuda:
+                with torch.cuda.stream(h2d):
+                    p.data.view(-1)[lo:hi].copy_(out_half, non_blocking=True)
+            else:
+                p.data.view(-1)[lo:hi].copy_(out_half)
+        if on_gpu:
+            torch.cuda.current_stream().wait_stream(h2d)
+        if self.record_delta and total_numel:
+            self.avg_delta = sum_delta / total_numel
+            self.var_delta = sum_sq_delta / total_numel - self.avg_delta ** 2
+        return loss
+
+    def get_avg_delta(self):
+        return self.avg_delta if self.record_delta else 0
+
+    def get_var_delta(self):
+        return self.var_delta if self.record_delta else 0
+
+    # ------------------------------------------------------------- state dict
+    def state_dict(self, gather: bool = False) -> dict:
+        param_mappings = {}
+        start_index = 0
+
+        def pack_group(group):
+            nonlocal start_index
+            packed = {k: v for k, v in group.items() if k != "params"}
+            param_mappings.update({id(p): i for i, p in enumerate(group["params"], start_index) if id(p) not in param_mappings})
+            packed["params"] = [param_mappings[id(p)] for p in group["params"]]
+            start_index += len(packed["params"])
+            return packed
+
+        def cut_states(state):
+            return {k: state[k] for k in ("step", "exp_avg", "exp_avg_sq", "_param_fp32")}
+
+        param_groups = [pack_group(g) for g in self.param_groups]
+        packed_state = {(param_mappings[id(k)] if isinstance(k, torch.Tensor) else k): cut_states(v)
+                        for k, v in self.state.items() if len(v) > 0}
+        states = {"state": packed_state, "param_groups": param_groups}
+        if gather:
+            states = deepcopy(states)
+            params = list(chain.from_iterable(g["params"] for g in self.param_groups))
+            comms = {}
+            for i, p in enumerate(params):
+                c = getattr(p, "_bmt_comm", None) or getattr(p, "_zero_comm", None)
+                if c is not None:
+                    comms[i] = c
+            states = state_dict_gather(states, comms)
+            states["is_whole"] = True
+        else:
+            states["is_whole"] = False
+        return states
+
+    def load_state_dict(self, state_dict: dict) -> None:
+        state_dict = deepcopy(state_dict)
+        groups = self.param_groups
+        saved_groups = state_dict["param_groups"]
+        if len(groups) != len(saved_groups):
+            raise ValueError("loaded state dict has a different number of parameter groups")
+        if any(len(g["params"]) != len(s["params"]) for g, s in zip(groups, saved_groups)):
+            raise ValueError("loaded state dict contains a parameter group that doesn't match the size of optimizer's group")
+        id_map = dict(zip(chain.from_iterable(g["params"] for g in saved_groups),
+                          chain.from_iterable(g["params"] for g in groups)))
+        is_whole = state_dict.get("is_whole", False)
+        state = defaultdict(dict)
+        for k, v in state_dict["state"].items():
+            if k not in id_map:
+                state[k] = v
+                continue
+            param = id_map[k]
+            if is_whole:
+                bounds = _partition_bounds(param)
+                if bounds is not None:
+                    for key in ("_param_fp32", "exp_avg_sq", "exp_avg"):
+                        if key in v:
+                            v[key] = v[key][bounds[0]:bounds[1]]
+            if "_param_fp32" not in v:
+                v["_param_fp32"] = param.detach().to("cpu", torch.float32)
+            for name in ("exp_avg", "exp_avg_sq", "_param_fp32"):
+                if name in v:
+                    src = v[name].to("cpu", torch.float32).reshape(param.shape)
+                    dst = _pinned(param.size(), torch.float32, param.is_cuda)
+                    dst.copy_(src)
+                    v[name] = dst
+            self._make_staging(param, v)
+            state[param] = v
+        param_groups = []
+        for g, ng in zip(groups, saved_groups):
+            ng["params"] = g["params"]
+            param_groups.append(ng)
+        self.__setstate__({"state": state, "param_groups": param_groups})
+
+    def zero_grad(self, set_to_none: bool = False):
+        super().zero_grad(set_to_none=set_to_none)

@@ -1,0 +1,176 @@
+"""Loss scaling and multi-optimizer stepping (reference: ``bmtrain/optim/optim_manager.py:9-226``).
+
+State machine: ``backward`` multiplies the loss by ``loss_scale / grad_scale``
+(``grad_scale`` defaults to the ZeRO group size, which turns the summing
+gradient reduce-scatter into a mean).  ``step`` first looks for inf/nan in all
+half-precision gradients (one multi-tensor scan, one max all-reduce, one host
+read); on overflow the scale shrinks, gradients are zeroed and nothing is
+stepped; otherwise every optimizer steps with the current scale, schedulers
+advance, and after ``loss_scale_steps`` clean steps the scale grows.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..block_layer import drain_pending
+from ..global_var import config
+from ..lr_scheduler.warmup import WarmupLRScheduler
+from ..ops import infnan
+from ..utils import print_rank
+
+
+def check_overflow(param_groups) -> None:
+    """Raise ``OverflowError`` if any half-precision gradient (on any rank) holds inf or nan."""
+    dev = config["device"]
+    flag = torch.zeros(1, dtype=torch.uint8, device=dev)
+    grads = [p.grad for group in param_groups for p in group["params"]
+             if p.grad is not None and p.dtype != torch.float32]
+    infnan.multi_has_inf_nan([g if g.is_contiguous() else g.contiguous() for g in grads], flag)
+    if config["comm"].size > 1:
+        f32 = flag.to(torch.int32)
+        config["comm"].all_reduce(f32, "max")
+        flag = f32
+    if int(flag.item()) > 0:
+        raise OverflowError("Gradient overflow")
+
+
+def grad_rescale(param_groups, scale) -> None:
+    for group in param_groups:
+        for p in group["params"]:
+            if p.grad is not None and p.requires_grad:
+                p.grad /= scale
+
+
+class OptimManager:
+    """Drives several optimizers (+ schedulers) under one dynamic loss scale."""
+
+    def __init__(self, loss_scale: Optional[float] = None, loss_scale_factor: float = 2, loss_scale_steps: int = 1024,
+                 min_loss_scale=1, max_loss_scale=float("inf"), grad_scale: Optional[int] = None):
+        if loss_scale is not None:
+            self.loss_scale = loss_scale
+            self.loss_scale_enabled = True
+        else:
+            self.loss_scale = 1
+            self.loss_scale_enabled = False
+        self.steps_since_last_scale = 0
+        self.loss_scale_factor = loss_scale_factor if loss_scale_factor > 1 else 1 / loss_scale_factor
+        self.loss_scale_steps = loss_scale_steps
+        self.min_loss_scale = min_loss_scale
+        self.max_loss_scale = max_loss_scale
+        if grad_scale is None:
+            grad_scale = config["zero_size"]
+        self.grad_scale = grad_scale
+        self.optimizers = []
+        self.lr_schedulers = []
+
+    def add_optimizer(self, optimizer: torch.optim.Optimizer, lr_scheduler: Optional[WarmupLRScheduler] = None):
+        self.optimizers.append(optimizer)
+        self.lr_schedulers.append(lr_scheduler)
+
+    def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        return loss * (self.loss_scale / self.grad_scale)
+
+    def backward(self, loss: torch.Tensor):
+        """Backward of the scaled loss; returns once all gradient reductions are queued behind it."""
+        loss = self.scale_loss(loss)
+        loss.backward()
+        drain_pending()
+
+    def zero_grad(self):
+        for optimizer in self.optimizers:
+            optimizer.zero_grad(set_to_none=False)
+
+    def step(self):
+        drain_pending()
+        if self.loss_scale_enabled:
+            has_overflow = False
+            for optimizer in self.optimizers:
+                try:
+                    check_overflow(optimizer.param_groups)
+                except OverflowError:
+                    has_overflow = True
+                    break
+            if has_overflow:
+                print_rank("Gradient overflow, change scale from %lf to %lf"
+                           % (self.loss_scale, self.loss_scale / self.loss_scale_factor))
+                with torch.no_grad():
+                    if self.loss_scale > self.min_loss_scale:
+                        self._justify_scale(self.loss_scale / self.loss_scale_factor)
+                    self.zero_grad()
+                return
+        for optimizer, lr_scheduler in zip(self.optimizers, self.lr_schedulers):
+            if getattr(optimizer, "_bmtrain_optimizer", False):
+                optimizer.step(scale=self.loss_scale)
+            else:
+                if self.loss_scale_enabled:
+                    grad_rescale(optimizer.param_groups, self.loss_scale)
+                optimizer.step()
+            if lr_scheduler is not None:
+                lr_scheduler.step()
+        if self.loss_scale_enabled:
+            self.steps_since_last_scale += 1
+            if self.steps_since_last_scale >= self.loss_scale_steps and self.loss_scale < self.max_loss_scale:
+                self._justify_scale(self.loss_scale * self.loss_scale_factor)
+
+    def clip_grad_norm(self, param_groups, max_norm, norm_type=2, eps=1e-6):
+        """Clip the global gradient norm (computed on the still loss-scaled gradients); returns the unscaled norm."""
+        drain_pending()
+        scale = self.loss_scale
+        dev = config["device"]
+        parameters = [p for group in param_groups for p in group["params"]]
+        grads = [p.grad.data for p in parameters if p.grad is not None]
+        if norm_type == "inf":
+            total = torch.zeros(1, dtype=torch.float32, device=dev)
+            for g in grads:
+                if g.numel():
+                    total = torch.maximum(total, g.abs().max().float().reshape(1))
+            config["comm"].all_reduce(total, "max")
+            total_norm = total[0]
+        else:
+            norm_type = float(norm_type)
+            total = torch.zeros(1, dtype=torch.float32, device=dev)
+            if norm_type == 2.0:
+                infnan.multi_sq_norm([g if g.is_contiguous() else g.contiguous() for g in grads], total)
+            else:
+                for g in grads:
+                    total += g.float().norm(norm_type) ** norm_type
+            config["comm"].all_reduce(total, "sum")
+            total_norm = total[0] ** (1.0 / norm_type)
+        clip_coef = float(max_norm * scale) / (total_norm + eps)
+        infnan.multi_scale(grads, clip_coef.reshape(1))
+        return total_norm / scale
+
+    @torch.no_grad()
+    def _justify_scale(self, scale):
+        for optimizer in self.optimizers:
+            if hasattr(optimizer, "_on_justify_scale"):
+                optimizer._on_justify_scale(self.loss_scale, scale)
+        self.loss_scale = scale
+        self.steps_since_last_scale = 0
+
+    def state_dict(self, gather_opt: bool = False) -> dict:
+        def opt_state(opt):
+            try:
+                return opt.state_dict(gather_opt)
+            except TypeError:
+                return opt.state_dict()
+
+        return {
+            "optimizers": [opt_state(opt) for opt in self.optimizers],
+            "lr_schedulers": [lrs.state_dict() if lrs else None for lrs in self.lr_schedulers],
+            "loss_scale": self.loss_scale,
+            "loss_scale_enabled": self.loss_scale_enabled,
+        }
+
+    def load_state_dict(self, state_dict: dict) -> None:
+        assert len(self.optimizers) == len(state_dict["optimizers"])
+        assert len(self.lr_schedulers) == len(state_dict["lr_schedulers"])
+        for opt, opt_st in zip(self.optimizers, state_dict["optimizers"]):
+            opt.load_state_dict(opt_st)
+        for lrs, lrs_st in zip(self.lr_schedulers, state_dict["lr_schedulers"]):
+            if lrs is not None and lrs_st is not None:
+                lrs.load_state_dict(lrs_st)
+        self.loss_scale = state_dict["loss_scale"]
+        self.loss_scale_enabled = state_dict["loss_scale_enabled"]

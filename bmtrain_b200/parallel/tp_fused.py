@@ -1,0 +1,57 @@
+"""All-gather -> GEMM and GEMM -> reduce-scatter as single operators.
+
+These are the tensor-parallel hot pairs of ``ColumnParallelLinear`` /
+``RowParallelLinear`` (reference: chunked NCCL + cuBLAS overlap in
+``bmtrain/nn/parallel_linear_func.py:26-105``).  On NVLink-connected B200s
+each pair is one kernel working on peer memory (``csrc/fused_tp.cu``); on other
+setups (CPU ranks, or peer access unavailable) the collective and the GEMM run
+back to back.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..comm import Communicator
+from ..ops import gemm as _gemm
+
+
+def _fused_available(x: torch.Tensor, comm: Communicator) -> bool:
+    if not x.is_cuda or comm.size == 1:
+        return False
+    from . import symm
+
+    return symm.peer_runtime_ready(comm)
+
+
+def all_gather_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], comm: Communicator,
+                    b_is_kn: bool = False, return_gathered: bool = False):
+    """``gather_tokens(x_local) @ W^T`` (or ``@ W`` when ``b_is_kn``: W is (K, N)).
+
+    Returns the (size*m, N) product, and the gathered input as well when asked.
+    """
+    if _fused_available(x_local, comm):
+        from . import fused_ops
+
+        return fused_ops.ag_gemm(x_local, weight, bias, comm, b_is_kn, return_gathered)
+    x_local = x_local.contiguous()
+    x_all = torch.empty((comm.size * x_local.shape[0], x_local.shape[1]), dtype=x_local.dtype, device=x_local.device)
+    comm.all_gather_into(x_all, x_local)
+    out = _gemm.gemm_nn(x_all, weight) if b_is_kn else _gemm.gemm_nt(x_all, weight, bias)
+    return (out, x_all) if return_gathered else out
+
+
+def gemm_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], comm: Communicator,
+                        b_is_kn: bool = False) -> torch.Tensor:
+    """``reduce_scatter_tokens(x @ W^T)`` (+ bias on the scattered result); ``b_is_kn``: ``x @ W``."""
+    if _fused_available(x, comm):
+        from . import fused_ops
+
+        return fused_ops.gemm_rs(x, weight, bias, comm, b_is_kn)
+    full = _gemm.gemm_nn(x, weight) if b_is_kn else _gemm.gemm_nt(x, weight)
+    out = torch.empty((full.shape[0] // comm.size, full.shape[1]), dtype=full.dtype, device=full.device)
+    comm.reduce_scatter_into(out, full, "sum")
+    if bias is not None:
+        out = out + bias
+    return out
