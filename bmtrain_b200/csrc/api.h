@@ -1,0 +1,78 @@
+// C ABI of the CUDA kernel library (_C.so).  Every entry point takes raw device
+// pointers and a CUDA stream handle, returns 0 on success (a cudaError_t value or
+// a negative library code otherwise) and never allocates device memory.
+// The reference exposes its kernels the same way -- pointers as integers through
+// pybind (csrc/bind.cpp:3-35) -- here the boundary is plain C so that ctypes can load it.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BMT_MAX_TENSORS 24
+
+typedef struct {
+    void* p32[BMT_MAX_TENSORS];
+    void* p16[BMT_MAX_TENSORS];
+    void* g[BMT_MAX_TENSORS];
+    void* m[BMT_MAX_TENSORS];
+    void* v[BMT_MAX_TENSORS];
+    int64_t n[BMT_MAX_TENSORS];
+    int32_t count;
+} BmtAdamTable;
+
+typedef struct {
+    void* p[BMT_MAX_TENSORS];
+    int64_t n[BMT_MAX_TENSORS];
+    int32_t count;
+} BmtPtrTable;
+
+// dtype codes: 0 = fp16, 1 = bf16, 2 = fp32
+int bmt_adam_fp16_multi(const BmtAdamTable* tab, float beta1, float beta2, float eps, float lr, float scale, float wd,
+                        float bc1, float bc2, void* stream);
+int bmt_adam_bf16_multi(const BmtAdamTable* tab, float beta1, float beta2, float eps, float lr, float scale, float wd,
+                        float bc1, float bc2, void* stream);
+
+int bmt_has_inf_nan_multi(const BmtPtrTable* tab, int dtype, void* out_flag_u8, void* stream);
+int bmt_sq_norm_multi(const BmtPtrTable* tab, int dtype, void* out_f32, void* stream);
+int bmt_scale_multi(const BmtPtrTable* tab, int dtype, const void* coef_f32, void* stream);
+
+int bmt_ce_row_stats(int64_t m, int64_t n, const void* logits, int dtype, const void* target_i64, int64_t vocab_start,
+                     void* out_3xm_f32, void* stream);
+int bmt_ce_backward(int64_t m, int64_t n, const void* logits, int dtype, const void* target_i64, const void* lse_f32,
+                    const void* grad_loss_f32, int64_t vocab_start, int64_t ignore_index, void* out, void* stream);
+
+int bmt_norm_fwd(int64_t rows, int64_t d, const void* x, const void* w, const void* b, float eps, int rms, int dtype,
+                 void* y, void* stats_2xrows_f32, void* stream);
+int bmt_norm_bwd(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms,
+                 int dtype, int nblk, void* dx, void* partial_2xnblkxd_f32, void* dw, void* db, void* stream);
+
+int bmt_embedding_fwd(int64_t tokens, int64_t d, const void* ids_i64, const void* weight, int dtype, void* out, void* stream);
+int bmt_embedding_bwd(int64_t tokens, int64_t d, const void* ids_i64, const void* grad, int dtype, void* acc_f32, void* stream);
+
+int bmt_masked_softmax(int64_t b, int64_t h, int64_t sq, int64_t sk, void* scores, int dtype, int causal,
+                       const void* mask_u8_b_sq_sk, const void* kv_lens_i32, void* stream);
+int bmt_softmax_bwd(int64_t rows, int64_t cols, const void* p, void* dp_inout, float scale, int dtype, void* stream);
+
+int bmt_swiglu_fwd(int64_t rows, int64_t f, const void* x, int dtype, void* out, void* stream);
+int bmt_swiglu_bwd(int64_t rows, int64_t f, const void* x, const void* g, int dtype, void* dx, void* stream);
+int bmt_colsum(int64_t m, int64_t n, const void* x, int dtype, void* out, void* stream);
+
+// C[M,N] (+)= alpha * op(A) op(B) (+ bias) with optional activation; majors: 0 = reduction dim contiguous, 1 = output dim contiguous.
+int bmt_gemm(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, const void* b, int64_t ldb,
+             int b_major, void* c, int64_t ldc, int c_dtype, const void* bias, int act, int accumulate, int ab_dtype,
+             void* stream);
+int bmt_gemm_batched(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, int64_t a_bs0, int64_t a_bs1,
+                     const void* b, int64_t ldb, int b_major, int64_t b_bs0, int64_t b_bs1, void* c, int64_t ldc,
+                     int c_dtype, int64_t c_bs0, int64_t c_bs1, int64_t batch_inner, int64_t batch_outer,
+                     int64_t b_inner_div, float alpha, int ab_dtype, void* stream);
+// number of kernel launches issued by this library since load (for launch accounting)
+int64_t bmt_launch_count(void);
+void bmt_count_launch(int n);
+// status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out; reading clears it
+int bmt_gemm_status(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,528 @@
+// Persistent tcgen05 GEMM for sm_100a (B200).
+//
+//   C[b][M,N] (+)= alpha * op(A[b]) * op(B[b]) (+ bias[N]) , optional ReLU / GELU
+//
+// * fp16 / bf16 operands, fp32 accumulation in tensor memory (TMEM), output fp16 / bf16 / fp32.
+// * Each operand may be "K-major" (reduction dim contiguous) or "MN-major" (output dim contiguous), so
+//   forward (NT), dgrad (NN) and wgrad (TN) of a linear layer all run here without any transpose pass.
+// * One CTA per SM, static persistent tile loop.  Warp roles:
+//       warp 0      TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, S-stage mbarrier pipeline)
+//       warp 1      MMA issuer    (tcgen05.mma cta_group::1 kind::f16, 128 x BN x 16, one elected thread)
+//       warps 2..5  epilogue      (tcgen05.ld 32x32b -> registers -> alpha/bias/activation -> global)
+//   Two TMEM accumulator buffers let the epilogue of tile i overlap the main loop of tile i+1.
+// * BN (16..256) is picked per problem to minimise wave quantisation on 148 SMs.
+// * Every wait on an mbarrier is bounded (about two seconds of polling); on expiry the kernel records a code in a
+//   device status word, lets in-flight copies land, frees its TMEM and returns.  Nothing traps.
+// * No TMA multicast is used anywhere (every CTA loads its own tiles).
+//
+// The reference has no GEMM kernel: all matmuls go through cuBLAS (bmtrain/nn/linear.py:10-24).
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+#include <string.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 halves = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_STAGES = 8;
+constexpr uint32_t SMEM_BUDGET = 225 * 1024;
+
+__device__ int g_gemm_status = 0;  // 0 = fine; otherwise (code << 16) | blockIdx of the first CTA that gave up
+
+struct GemmParams {
+    int64_t M, N, K;
+    int bn;           // tile N
+    int stages;
+    int a_mn, b_mn;   // 1 = MN-major operand
+    int m_blocks, n_blocks;
+    int64_t batch_inner, batch_outer, b_inner_div;
+    void* c;
+    int64_t ldc, c_bs0, c_bs1;
+    int c_dtype;
+    const void* bias;
+    int bias_dtype;
+    int act;
+    int accumulate;
+    float alpha;
+    uint32_t idesc;
+};
+
+// ------------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: true when the phase completed, false when about two seconds passed without it.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    uint64_t start = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 1023u) == 1023u) {
+            const uint64_t now = global_ns();
+            if (start == 0) start = now;
+            else if (now - start > 2000000000ull) return false;
+        }
+    }
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_4d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle.  Addresses / offsets are encoded in 16-byte units.
+//   K-major operand : rows of 128 bytes, 8-row groups 1024 bytes apart (SBO); LBO unused.
+//   MN-major operand: 64-element (128-byte) runs along MN, K rows 128 bytes apart, 8-row groups 1024 bytes apart
+//                     (SBO), consecutive 64-element MN chunks `lbo_bytes` apart (LBO).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version of the 5th-generation tensor core
+    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+template <typename T> __device__ __forceinline__ void store8(T* dst, const float* v) {
+    bmt::Vec16<T> o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.v[i] = bmt::Cvt<T>::from_f(v[i]);
+    bmt::st16(dst, o);
+}
+template <typename T> __device__ __forceinline__ void load8(const T* src, float* v) {
+    bmt::Vec16<T> o = bmt::ld16(src);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = bmt::Cvt<T>::to_f(o.v[i]);
+}
+
+struct SharedHeader {
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int failed;
+};
+
+template <typename TC>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, TC* crow, int64_t col0, int64_t col_end, const uint32_t (&r)[32], bool row_ok) {
+    // this thread owns one output row and the columns [col0, min(col0 + 32, col_end))
+    if (!row_ok) return;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+    const bool vec = ((p.ldc & 7) == 0) && ((((uintptr_t)p.c) & 15) == 0) && (((p.c_bs0 | p.c_bs1) & 7) == 0) && sizeof(TC) == 2;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int64_t c = col0 + g * 8;
+        if (c >= col_end) break;
+        float* vv = v + g * 8;
+        const bool full8 = c + 8 <= col_end;
+        if (p.bias) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (c + i < col_end)
+                    vv[i] += p.bias_dtype == BMT_DT_F16 ? __half2float(((const __half*)p.bias)[c + i])
+                           : p.bias_dtype == BMT_DT_BF16 ? __bfloat162float(((const __nv_bfloat16*)p.bias)[c + i])
+                                                         : ((const float*)p.bias)[c + i];
+        }
+        if (p.act == 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vv[i] = fmaxf(vv[i], 0.f);
+        } else if (p.act == 2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vv[i] = gelu_f(vv[i]);
+        }
+        if (full8 && vec) {
+            if (p.accumulate) {
+                float old[8];
+                load8(crow + c, old);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) vv[i] += old[i];
+            }
+            store8(crow + c, vv);
+        } else if (full8 && sizeof(TC) == 4 && ((p.ldc & 3) == 0) && ((((uintptr_t)p.c) & 15) == 0)) {
+            float4* d4 = reinterpret_cast<float4*>(crow + c);
+            if (p.accumulate) {
+                float4 o0 = d4[0], o1 = d4[1];
+                vv[0] += o0.x; vv[1] += o0.y; vv[2] += o0.z; vv[3] += o0.w; vv[4] += o1.x; vv[5] += o1.y; vv[6] += o1.z; vv[7] += o1.w;
+            }
+            d4[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+            d4[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (c + i < col_end) {
+                    float o = vv[i];
+                    if (p.accumulate) o += bmt::Cvt<TC>::to_f(crow[c + i]);
+                    crow[c + i] = bmt::Cvt<TC>::from_f(o);
+                }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // tiles first (1024-byte aligned for the 128-byte swizzle), bookkeeping after them
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t a_bytes = BM * BK * 2;
+    const uint32_t b_bytes = (uint32_t)p.bn * BK * 2;
+    const uint32_t stage_bytes = a_bytes + b_bytes;
+    SharedHeader* hdr = (SharedHeader*)(smem + (size_t)p.stages * stage_bytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = (int)((p.K + BK - 1) / BK);
+    const int64_t tiles_per_batch = (int64_t)p.m_blocks * p.n_blocks;
+    const int64_t num_tiles = tiles_per_batch * p.batch_inner * p.batch_outer;
+    const uint32_t tmem_cols = 2 * p.bn <= 32 ? 32 : 2 * p.bn <= 64 ? 64 : 2 * p.bn <= 128 ? 128 : 2 * p.bn <= 256 ? 256 : 512;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) { mbar_init(&hdr->full[s], 1); mbar_init(&hdr->empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&hdr->tmem_full[a], 1); mbar_init(&hdr->tmem_empty[a], 4); }
+        hdr->failed = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(&hdr->tmem_base, tmem_cols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = hdr->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int64_t batch = tile / tiles_per_batch;
+                const int64_t rem = tile % tiles_per_batch;
+                const int m_blk = (int)(rem % p.m_blocks), n_blk = (int)(rem / p.m_blocks);
+                const int bi = (int)(batch % p.batch_inner), bo = (int)(batch / p.batch_inner);
+                const int bib = (int)(bi / p.b_inner_div);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t ph = (it / p.stages) & 1;
+                    if (!mbar_wait(&hdr->empty[s], ph ^ 1)) { ok = false; atomicCAS(&g_gemm_status, 0, (1 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
+                    uint8_t* sa = smem + (size_t)s * stage_bytes;
+                    uint8_t* sb = sa + a_bytes;
+                    mbar_expect_tx(&hdr->full[s], stage_bytes);
+                    if (!p.a_mn) {
+                        tma_load_4d(&tma_a, &hdr->full[s], sa, kb * BK, m_blk * BM, bi, bo);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c)
+                            tma_load_4d(&tma_a, &hdr->full[s], sa + c * (64 * BK * 2), m_blk * BM + c * 64, kb * BK, bi, bo);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_4d(&tma_b, &hdr->full[s], sb, kb * BK, n_blk * p.bn, bib, bo);
+                    } else {
+                        for (int c = 0; c < p.bn / 64; ++c)
+                            tma_load_4d(&tma_b, &hdr->full[s], sb + c * (64 * BK * 2), n_blk * p.bn + c * 64, kb * BK, bib, bo);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+                const uint32_t acc = tcount & 1;
+                const uint32_t acc_ph = (tcount >> 1) & 1;
+                if (!mbar_wait(&hdr->tmem_empty[acc], acc_ph ^ 1)) { ok = false; atomicCAS(&g_gemm_status, 0, (2 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
+                tc_fence_after();
+                const uint32_t tmem_c = tmem_base + acc * p.bn;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t ph = (it / p.stages) & 1;
+                    if (!mbar_wait(&hdr->full[s], ph)) { ok = false; atomicCAS(&g_gemm_status, 0, (3 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint32_t sb = sa + a_bytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major: step 32 bytes inside the 128-byte swizzle row; MN-major: step 16 K rows (2 KiB)
+                        const uint64_t ad = p.a_mn ? make_smem_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                                   : make_smem_desc(sa + k * (UMMA_K * 2), 0, 1024);
+                        const uint64_t bd = p.b_mn ? make_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                                   : make_smem_desc(sb + k * (UMMA_K * 2), 0, 1024);
+                        umma_f16(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&hdr->empty[s]);  // frees the smem stage once these MMAs have read it
+                }
+                if (ok) umma_commit(&hdr->tmem_full[acc]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) are visible to this warp
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            const int64_t batch = tile / tiles_per_batch;
+            const int64_t rem = tile % tiles_per_batch;
+            const int m_blk = (int)(rem % p.m_blocks), n_blk = (int)(rem / p.m_blocks);
+            const int64_t bi = batch % p.batch_inner, bo = batch / p.batch_inner;
+            const uint32_t acc = tcount & 1;
+            const uint32_t acc_ph = (tcount >> 1) & 1;
+            if (!mbar_wait(&hdr->tmem_full[acc], acc_ph)) { ok = false; atomicCAS(&g_gemm_status, 0, (4 << 16) | (blockIdx.x & 0xffff)); break; }
+            tc_fence_after();
+            const int64_t row = (int64_t)m_blk * BM + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+            const int64_t coff = bi * p.c_bs0 + bo * p.c_bs1 + row * p.ldc;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * p.bn;
+            const int64_t tile_end = (int64_t)(n_blk + 1) * p.bn;
+            const int64_t col_end = tile_end < p.N ? tile_end : p.N;
+            for (int c0 = 0; c0 < p.bn; c0 += 32) {
+                const int64_t col0 = (int64_t)n_blk * p.bn + c0;
+                if (col0 >= col_end) break;
+                uint32_t r[32];
+                tmem_ld32(taddr + c0, r);
+                tmem_ld_wait();
+                if (p.c_dtype == BMT_DT_F16) epilogue_chunk<__half>(p, (__half*)p.c + coff, col0, col_end, r, row_ok);
+                else if (p.c_dtype == BMT_DT_BF16) epilogue_chunk<__nv_bfloat16>(p, (__nv_bfloat16*)p.c + coff, col0, col_end, r, row_ok);
+                else epilogue_chunk<float>(p, (float*)p.c + coff, col0, col_end, r, row_ok);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&hdr->tmem_empty[acc]);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncthreads();
+    if (hdr->failed) {
+        // a wait ran out: give copies that are still in flight time to land before the CTA's shared memory goes away
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    int64_t d[4], s[3];
+    int box0, box1, dtype;
+    bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        const uint64_t* w = (const uint64_t*)&k;
+        size_t h = 1469598103934665603ull;
+        for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+        return h;
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_mu;
+
+// 4-D map: dims {inner, rows, batch_inner, batch_outer}; element strides for dims 1..3.
+int make_map(CUtensorMap* out, const void* ptr, int dtype, int64_t inner, int64_t rows, int64_t ld, int64_t nb0, int64_t bs0,
+             int64_t nb1, int64_t bs1, int box_inner, int box_rows) {
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    key.ptr = ptr; key.d[0] = inner; key.d[1] = rows; key.d[2] = nb0; key.d[3] = nb1;
+    key.s[0] = ld; key.s[1] = bs0; key.s[2] = bs1; key.box0 = box_inner; key.box1 = box_rows; key.dtype = dtype;
+    {
+        std::lock_guard<std::mutex> lk(g_maps_mu);
+        auto it = g_maps.find(key);
+        if (it != g_maps.end()) { *out = it->second; return 0; }
+    }
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return -10;
+    if (((uintptr_t)ptr & 15) || (ld & 7) || (nb0 > 1 && (bs0 & 7)) || (nb1 > 1 && (bs1 & 7))) return -11;
+    cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)nb0, (cuuint64_t)nb1};
+    // strides of unit-extent dims are irrelevant but must still be legal (multiple of 16 bytes, non-zero)
+    cuuint64_t st[3] = {(cuuint64_t)ld * 2, (cuuint64_t)(nb0 > 1 ? bs0 : ld * rows) * 2, (cuuint64_t)(nb1 > 1 ? bs1 : ld * rows) * 2};
+    if (st[1] == 0) st[1] = 16;
+    if (st[2] == 0) st[2] = 16;
+    cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1, 1};
+    cuuint32_t es[4] = {1, 1, 1, 1};
+    CUresult r = enc(out, dtype == BMT_DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (void*)ptr,
+                     dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -12;
+    std::lock_guard<std::mutex> lk(g_maps_mu);
+    if (g_maps.size() > 8192) g_maps.clear();
+    g_maps[key] = *out;
+    return 0;
+}
+
+int g_num_sms = 0;
+
+int pick_bn(int64_t M, int64_t N, int64_t batches, bool b_mn, int force_bn) {
+    if (force_bn > 0) return force_bn;
+    const int64_t mb = (M + BM - 1) / BM;
+    int best = 0;
+    double best_cost = 1e30;
+    const int step = b_mn ? 64 : 16;
+    for (int bn = b_mn ? 64 : 32; bn <= 256; bn += step) {
+        const int64_t tiles = mb * ((N + bn - 1) / bn) * batches;
+        const int64_t waves = (tiles + g_num_sms - 1) / g_num_sms;
+        const double cost = (double)waves * (bn + 24);  // 24: per-tile fixed cost in units of N columns
+        if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && bn > best)) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+int launch_gemm(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, int64_t a_bs0, int64_t a_bs1,
+                const void* b, int64_t ldb, int b_major, int64_t b_bs0, int64_t b_bs1, void* c, int64_t ldc, int c_dtype,
+                int64_t c_bs0, int64_t c_bs1, int64_t batch_inner, int64_t batch_outer, int64_t b_inner_div, const void* bias,
+                int act, int accumulate, float alpha, int ab_dtype, cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || batch_inner <= 0 || batch_outer <= 0) return 0;
+    if (k <= 0) return -20;
+    if (g_num_sms == 0) {
+        int dev = 0;
+        BMT_CUDA_OK(cudaGetDevice(&dev));
+        BMT_CUDA_OK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+    }
+    static int force_bn = -1;
+    if (force_bn < 0) { const char* e = getenv("BMT_GEMM_BN"); force_bn = e ? atoi(e) : 0; }
+
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = m; p.N = n; p.K = k;
+    p.a_mn = a_major; p.b_mn = b_major;
+    p.bn = pick_bn(m, n, batch_inner * batch_outer, b_major != 0, force_bn);
+    const uint32_t stage_bytes = BM * BK * 2 + p.bn * BK * 2;
+    int stages = (int)((SMEM_BUDGET - 1024) / stage_bytes);
+    p.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
+    p.m_blocks = (int)((m + BM - 1) / BM);
+    p.n_blocks = (int)((n + p.bn - 1) / p.bn);
+    p.batch_inner = batch_inner; p.batch_outer = batch_outer; p.b_inner_div = b_inner_div > 0 ? b_inner_div : 1;
+    p.c = c; p.ldc = ldc; p.c_bs0 = c_bs0; p.c_bs1 = c_bs1; p.c_dtype = c_dtype;
+    p.bias = bias; p.bias_dtype = ab_dtype; p.act = act; p.accumulate = accumulate; p.alpha = alpha;
+    const uint32_t fmt = ab_dtype == BMT_DT_F16 ? 0u : 1u;
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_major ? 1 : 0) << 15) | ((uint32_t)(b_major ? 1 : 0) << 16) |
+              ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+    CUtensorMap ma, mb;
+    int rc;
+    const int64_t nb_b = (batch_inner + p.b_inner_div - 1) / p.b_inner_div;
+    if (!a_major) rc = make_map(&ma, a, ab_dtype, k, m, lda, batch_inner, a_bs0, batch_outer, a_bs1, BK, BM);
+    else          rc = make_map(&ma, a, ab_dtype, m, k, lda, batch_inner, a_bs0, batch_outer, a_bs1, 64, BK);
+    if (rc) return rc;
+    if (!b_major) rc = make_map(&mb, b, ab_dtype, k, n, ldb, nb_b, b_bs0, batch_outer, b_bs1, BK, p.bn);
+    else          rc = make_map(&mb, b, ab_dtype, n, k, ldb, nb_b, b_bs0, batch_outer, b_bs1, 64, BK);
+    if (rc) return rc;
+
+    const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * batch_inner * batch_outer;
+    const unsigned grid = (unsigned)(tiles < g_num_sms ? tiles : g_num_sms);
+    const size_t smem = (size_t)p.stages * stage_bytes + sizeof(SharedHeader) + 1024;
+    gemm_tcgen05_kernel<<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" int bmt_gemm(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, const void* b, int64_t ldb,
+                        int b_major, void* c, int64_t ldc, int c_dtype, const void* bias, int act, int accumulate, int ab_dtype,
+                        void* stream) {
+    return launch_gemm(m, n, k, a, lda, a_major, 0, 0, b, ldb, b_major, 0, 0, c, ldc, c_dtype, 0, 0, 1, 1, 1, bias, act,
+                       accumulate, 1.0f, ab_dtype, (cudaStream_t)stream);
+}
+
+extern "C" int bmt_gemm_batched(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, int64_t a_bs0,
+                                int64_t a_bs1, const void* b, int64_t ldb, int b_major, int64_t b_bs0, int64_t b_bs1, void* c,
+                                int64_t ldc, int c_dtype, int64_t c_bs0, int64_t c_bs1, int64_t batch_inner, int64_t batch_outer,
+                                int64_t b_inner_div, float alpha, int ab_dtype, void* stream) {
+    return launch_gemm(m, n, k, a, lda, a_major, a_bs0, a_bs1, b, ldb, b_major, b_bs0, b_bs1, c, ldc, c_dtype, c_bs0, c_bs1,
+                       batch_inner, batch_outer, b_inner_div, nullptr, 0, 0, alpha, ab_dtype, (cudaStream_t)stream);
+}
+
+// Status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out.  Reading clears it.
+extern "C" int bmt_gemm_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+    return v;
+}

@@ -1,0 +1,162 @@
+// LayerNorm / RMSNorm forward and backward for sm_100a.
+//
+// Forward: one CTA per row; the row is staged once in shared memory as fp32, mean and
+// variance are exact two-pass statistics over that copy, the output is written with
+// 128-bit stores.  Saves (mean, rstd) per row.
+// Backward: a persistent grid (nblk CTAs) strides over the rows; each CTA produces dx for
+// its rows and keeps per-thread partial dgamma / dbeta in registers, written once to a
+// (nblk x d) fp32 scratch that a second kernel folds over nblk.
+// (The reference calls F.layer_norm: example/layers/layernorm.py:29.)
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int NT = 256;
+constexpr int MAXIT = 8;  // d <= NT * 8 * MAXIT = 16384
+
+template <typename T>
+__global__ void __launch_bounds__(NT) norm_fwd_kernel(int64_t rows, int d, const T* __restrict__ x, const T* __restrict__ w,
+                                                      const T* __restrict__ b, float eps, int rms, T* __restrict__ y,
+                                                      float* __restrict__ stats) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const int64_t r = blockIdx.x;
+    const T* __restrict__ xr = x + r * d;
+    float s = 0.f;
+    for (int c = threadIdx.x * 8; c < d; c += NT * 8) {
+        bmt::Vec16<T> v = bmt::ld16(xr + c);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { float f = bmt::Cvt<T>::to_f(v.v[k]); row[c + k] = f; s += f; }
+    }
+    float mean = 0.f;
+    if (!rms) mean = bmt::block_allreduce<false>(s, scratch) / d;
+    float q = 0.f;
+    for (int c = threadIdx.x * 8; c < d; c += NT * 8) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { float f = row[c + k] - mean; q += f * f; }
+    }
+    const float var = bmt::block_allreduce<false>(q, scratch) / d;
+    const float rstd = rsqrtf(var + eps);
+    if (threadIdx.x == 0) { stats[r] = mean; stats[rows + r] = rstd; }
+    T* __restrict__ yr = y + r * d;
+    for (int c = threadIdx.x * 8; c < d; c += NT * 8) {
+        bmt::Vec16<T> wv = bmt::ld16(w + c), o;
+        bmt::Vec16<T> bv;
+        if (b) bv = bmt::ld16(b + c);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float f = (row[c + k] - mean) * rstd * bmt::Cvt<T>::to_f(wv.v[k]);
+            if (b) f += bmt::Cvt<T>::to_f(bv.v[k]);
+            o.v[k] = bmt::Cvt<T>::from_f(f);
+        }
+        bmt::st16(yr + c, o);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT) norm_bwd_kernel(int64_t rows, int d, const T* __restrict__ x, const T* __restrict__ dy,
+                                                      const T* __restrict__ w, const float* __restrict__ stats, int rms,
+                                                      T* __restrict__ dx, float* __restrict__ partial) {
+    __shared__ float scratch[33];
+    float dg[MAXIT][8], db[MAXIT][8];
+#pragma unroll
+    for (int it = 0; it < MAXIT; ++it)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) dg[it][k] = db[it][k] = 0.f;
+
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float mean = stats[r], rstd = stats[rows + r];
+        const T* __restrict__ xr = x + r * d;
+        const T* __restrict__ gr = dy + r * d;
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int it = 0; it < MAXIT; ++it) {
+            const int c = threadIdx.x * 8 + it * NT * 8;
+            if (c < d) {
+                bmt::Vec16<T> xv = bmt::ld16(xr + c), gv = bmt::ld16(gr + c), wv = bmt::ld16(w + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float xh = (bmt::Cvt<T>::to_f(xv.v[k]) - mean) * rstd;
+                    const float g = bmt::Cvt<T>::to_f(gv.v[k]);
+                    const float wg = g * bmt::Cvt<T>::to_f(wv.v[k]);
+                    s1 += wg; s2 += wg * xh;
+                    dg[it][k] += g * xh; db[it][k] += g;
+                }
+            }
+        }
+        if (rms) s1 = 0.f; else s1 = bmt::block_allreduce<false>(s1, scratch) / d;
+        s2 = bmt::block_allreduce<false>(s2, scratch) / d;
+        T* __restrict__ dr = dx + r * d;
+#pragma unroll
+        for (int it = 0; it < MAXIT; ++it) {
+            const int c = threadIdx.x * 8 + it * NT * 8;
+            if (c < d) {
+                bmt::Vec16<T> xv = bmt::ld16(xr + c), gv = bmt::ld16(gr + c), wv = bmt::ld16(w + c), o;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float xh = (bmt::Cvt<T>::to_f(xv.v[k]) - mean) * rstd;
+                    const float wg = bmt::Cvt<T>::to_f(gv.v[k]) * bmt::Cvt<T>::to_f(wv.v[k]);
+                    o.v[k] = bmt::Cvt<T>::from_f(rstd * (wg - s1 - xh * s2));
+                }
+                bmt::st16(dr + c, o);
+            }
+        }
+    }
+    float* pg = partial + (int64_t)blockIdx.x * d;
+    float* pb = partial + ((int64_t)gridDim.x + blockIdx.x) * d;
+#pragma unroll
+    for (int it = 0; it < MAXIT; ++it) {
+        const int c = threadIdx.x * 8 + it * NT * 8;
+        if (c < d) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { pg[c + k] = dg[it][k]; pb[c + k] = db[it][k]; }
+        }
+    }
+}
+
+template <typename T>
+__global__ void norm_fold_kernel(int d, int nblk, const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= d) return;
+    float a = 0.f, bsum = 0.f;
+    for (int i = 0; i < nblk; ++i) { a += partial[(int64_t)i * d + c]; bsum += partial[((int64_t)nblk + i) * d + c]; }
+    dw[c] = bmt::Cvt<T>::from_f(a);
+    if (db) db[c] = bmt::Cvt<T>::from_f(bsum);
+}
+
+template <typename T>
+int fwd(int64_t rows, int64_t d, const void* x, const void* w, const void* b, float eps, int rms, void* y, void* stats, cudaStream_t s) {
+    norm_fwd_kernel<T><<<(unsigned)rows, NT, d * sizeof(float), s>>>(rows, (int)d, (const T*)x, (const T*)w, (const T*)b, eps, rms, (T*)y, (float*)stats);
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int bwd(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms, int nblk, void* dx,
+        void* partial, void* dw, void* db, cudaStream_t s) {
+    norm_bwd_kernel<T><<<nblk, NT, 0, s>>>(rows, (int)d, (const T*)x, (const T*)dy, (const T*)w, (const float*)stats, rms, (T*)dx, (float*)partial);
+    norm_fold_kernel<T><<<(unsigned)((d + 127) / 128), 128, 0, s>>>((int)d, nblk, (const float*)partial, (T*)dw, (T*)db);
+    bmt_count_launch(2);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" int bmt_norm_fwd(int64_t rows, int64_t d, const void* x, const void* w, const void* b, float eps, int rms, int dtype,
+                            void* y, void* stats, void* stream) {
+    if (rows <= 0) return 0;
+    if (d % 8 != 0 || d > 12032 || dtype == BMT_DT_F32) return -3;  // row staged in <= 47 KB of shared memory
+    cudaStream_t s = (cudaStream_t)stream;
+    return dtype == BMT_DT_F16 ? fwd<__half>(rows, d, x, w, b, eps, rms, y, stats, s)
+                               : fwd<__nv_bfloat16>(rows, d, x, w, b, eps, rms, y, stats, s);
+}
+
+extern "C" int bmt_norm_bwd(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms,
+                            int dtype, int nblk, void* dx, void* partial, void* dw, void* db, void* stream) {
+    if (rows <= 0) return 0;
+    if (d % 8 != 0 || d > NT * 8 * MAXIT || dtype == BMT_DT_F32) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    return dtype == BMT_DT_F16 ? bwd<__half>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s)
+                               : bwd<__nv_bfloat16>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s);
+}

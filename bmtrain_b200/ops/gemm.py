@@ -59,7 +59,14 @@ def _use_torch(t: torch.Tensor) -> bool:
 
 
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
-    return t if (t.stride(-1) == 1 and t.stride(0) >= t.shape[1] and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0) else t.contiguous()
+    """A view TMA can read: unit inner stride, 16-byte aligned base and row pitch (pads a copy when needed)."""
+    if t.stride(-1) == 1 and t.stride(0) >= t.shape[1] and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    if t.shape[1] % 8 == 0:
+        return t.contiguous()
+    padded = torch.zeros(t.shape[0], (t.shape[1] + 7) // 8 * 8, dtype=t.dtype, device=t.device)
+    padded[:, : t.shape[1]].copy_(t)
+    return padded[:, : t.shape[1]]
 
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
