@@ -51,9 +51,9 @@ int bmt_norm_bwd(int64_t rows, int64_t d, const void* x, const void* dy, const v
 int bmt_embedding_fwd(int64_t tokens, int64_t d, const void* ids_i64, const void* weight, int dtype, void* out, void* stream);
 int bmt_embedding_bwd(int64_t tokens, int64_t d, const void* ids_i64, const void* grad, int dtype, void* acc_f32, void* stream);
 
-int bmt_masked_softmax(int64_t b, int64_t h, int64_t sq, int64_t sk, void* scores, int dtype, int causal,
+int bmt_masked_softmax(int64_t b, int64_t h, int64_t sq, int64_t sk, int64_t ld, void* scores, int dtype, int causal,
                        const void* mask_u8_b_sq_sk, const void* kv_lens_i32, void* stream);
-int bmt_softmax_bwd(int64_t rows, int64_t cols, const void* p, void* dp_inout, float scale, int dtype, void* stream);
+int bmt_softmax_bwd(int64_t rows, int64_t cols, int64_t ld, const void* p, void* dp_inout, float scale, int dtype, void* stream);
 
 int bmt_swiglu_fwd(int64_t rows, int64_t f, const void* x, int dtype, void* out, void* stream);
 int bmt_swiglu_bwd(int64_t rows, int64_t f, const void* x, const void* g, int dtype, void* dx, void* stream);

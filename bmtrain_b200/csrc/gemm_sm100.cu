@@ -20,6 +20,7 @@
 #include <mutex>
 #include <unordered_map>
 #include <vector>
+#include <stdio.h>
 #include <string.h>
 
 #include "api.h"
@@ -425,10 +426,16 @@ int make_map(CUtensorMap* out, const void* ptr, int dtype, int64_t inner, int64_
     if (st[2] == 0) st[2] = 16;
     cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1, 1};
     cuuint32_t es[4] = {1, 1, 1, 1};
+    cudaFree(0);  // binds the primary context to this thread (autograd worker threads may not have one current yet)
     CUresult r = enc(out, dtype == BMT_DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (void*)ptr,
                      dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return -12;
+    if (r != CUDA_SUCCESS) {
+        fprintf(stderr, "bmtrain_b200: cuTensorMapEncodeTiled failed (%d): ptr=%p dims={%lld,%lld,%lld,%lld} strides={%lld,%lld,%lld} box={%d,%d}\n",
+                (int)r, ptr, (long long)dims[0], (long long)dims[1], (long long)dims[2], (long long)dims[3], (long long)st[0],
+                (long long)st[1], (long long)st[2], box_inner, box_rows);
+        return -12;
+    }
     std::lock_guard<std::mutex> lk(g_maps_mu);
     if (g_maps.size() > 8192) g_maps.clear();
     g_maps[key] = *out;

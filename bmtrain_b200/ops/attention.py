@@ -58,11 +58,13 @@ class AttentionFunction(torch.autograd.Function):
         assert h % hk == 0 and q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1
         group = h // hk
         # scores (b, h, sq, sk): batch inner = head (kv head = head // group), outer = sample
-        p = torch.empty(b, h, sq, sk, dtype=q.dtype, device=q.device)
+        assert d % 8 == 0, "head dimension must be a multiple of 8"
+        skp = (sk + 7) // 8 * 8  # row pitch keeps every row 16-byte aligned for TMA
+        p = torch.empty(b, h, sq, skp, dtype=q.dtype, device=q.device)[..., :sk]
         _bgemm_heads(lib, "nt", sq, sk, d, q, k, p, b, h, group, scale)
         m8, l32 = _softmax_args(mask, kv_lens)
         _native.check(lib.bmt_masked_softmax(
-            ctypes.c_int64(b), ctypes.c_int64(h), ctypes.c_int64(sq), ctypes.c_int64(sk), _native.ptr(p),
+            ctypes.c_int64(b), ctypes.c_int64(h), ctypes.c_int64(sq), ctypes.c_int64(sk), ctypes.c_int64(p.stride(2)), _native.ptr(p),
             ctypes.c_int(_DT[q.dtype]), ctypes.c_int(1 if causal else 0), _native.ptr(m8), _native.ptr(l32),
             _native.stream_handle()), "masked softmax kernel")
         o = torch.empty(b, sq, h, d, dtype=q.dtype, device=q.device)
@@ -80,11 +82,11 @@ class AttentionFunction(torch.autograd.Function):
         group = ctx.group
         do = do.contiguous()
         # dP = dO V^T
-        dp = torch.empty_like(p)
+        dp = torch.empty(b, h, sq, p.stride(2), dtype=p.dtype, device=p.device)[..., :sk]
         _bgemm_heads(lib, "nt", sq, sk, d, do, v, dp, b, h, group, 1.0)
         # dS = P * (dP - rowsum(dP * P)) * scale   (in place into dp)
         _native.check(lib.bmt_softmax_bwd(
-            ctypes.c_int64(b * h * sq), ctypes.c_int64(sk), _native.ptr(p), _native.ptr(dp), ctypes.c_float(ctx.scale),
+            ctypes.c_int64(b * h * sq), ctypes.c_int64(sk), ctypes.c_int64(p.stride(2)), _native.ptr(p), _native.ptr(dp), ctypes.c_float(ctx.scale),
             ctypes.c_int(_DT[q.dtype]), _native.stream_handle()), "softmax backward kernel")
         dq = torch.empty(b, sq, h, d, dtype=q.dtype, device=q.device)
         _bgemm_heads(lib, "pv", sq, d, sk, dp, k, dq, b, h, group, 1.0)          # dQ = dS K

@@ -1,0 +1,232 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 definition of the same op (B200 only)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
+
+
+@pytest.fixture(scope="module")
+def dev(bmt_gpu):
+    return torch.device("cuda")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (1024, 2560, 2560), (1000, 2568, 520), (333, 80, 96), (2048, 8192, 2560)])
+def test_gemm_layouts(dev, dtype, shape):
+    from bmtrain_b200.ops import gemm as G
+
+    m, n, k = shape
+    torch.manual_seed(1)
+    tol = 6e-3 if dtype == torch.bfloat16 else 1e-3
+    a = torch.randn(m, k, device=dev, dtype=dtype)
+    b = torch.randn(n, k, device=dev, dtype=dtype)
+    bias = torch.randn(n, device=dev, dtype=dtype)
+    ref = a.float() @ b.float().t()
+    assert _rel(G.gemm_nt(a, b), ref) < tol
+    assert _rel(G.gemm_nt(a, b, bias, "relu"), torch.relu(ref + bias.float())) < tol
+    assert _rel(G.gemm_nt(a, b, bias, "gelu"), torch.nn.functional.gelu(ref + bias.float())) < tol
+    bk = torch.randn(k, n, device=dev, dtype=dtype)
+    assert _rel(G.gemm_nn(a, bk), a.float() @ bk.float()) < tol
+    at = torch.randn(k, m, device=dev, dtype=dtype)
+    assert _rel(G.gemm_tn(at, bk), at.float().t() @ bk.float()) < tol
+    acc = torch.randn(m, n, device=dev, dtype=torch.float32)
+    expect = acc + at.float().t() @ bk.float()
+    G.gemm_tn(at, bk, out=acc, accumulate=True)
+    assert _rel(acc, expect) < 1e-4
+    from bmtrain_b200.ops import _native
+    assert _native.cuda_lib().bmt_gemm_status() == 0
+
+
+def test_linear_autograd(dev):
+    from bmtrain_b200.ops import gemm as G
+
+    torch.manual_seed(2)
+    x = torch.randn(4, 96, 256, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(512, 256, device=dev) * 0.05).to(torch.bfloat16).requires_grad_()
+    b = torch.randn(512, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    y = G.linear(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = x.detach().float().requires_grad_(), w.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 6e-3 and _rel(x.grad, xr.grad) < 6e-3 and _rel(w.grad, wr.grad) < 6e-3 and _rel(b.grad, br.grad) < 6e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_adam_multi(dev, dtype):
+    from bmtrain_b200.ops import adam as A
+
+    torch.manual_seed(3)
+    entries, refs = [], []
+    for n in (8, 1000, 4099, 1 << 20):
+        p32 = torch.randn(n, device=dev)
+        g = (torch.randn(n, device=dev) * 64).to(dtype)
+        m = (torch.randn(n, device=dev) * 0.1).to(torch.float16 if dtype == torch.float16 else torch.float32)
+        v = torch.rand(n, device=dev) * 0.1
+        p16 = p32.to(dtype)
+        entries.append((p32, p16, g, m, v))
+        refs.append(tuple(t.cpu().clone() for t in (p32, p16, g, m, v)))
+    A.adam_half_multi(entries, 0.9, 0.999, 1e-8, 1e-3, 64.0, 0.01, 7)
+    A.adam_half_multi(refs, 0.9, 0.999, 1e-8, 1e-3, 64.0, 0.01, 7)  # CPU tensors: PyTorch definition
+    for e, r in zip(entries, refs):
+        assert torch.allclose(e[0].cpu(), r[0], atol=1e-5, rtol=1e-5)
+        assert torch.allclose(e[1].cpu().float(), r[1].float(), atol=1e-2, rtol=1e-2)
+        assert torch.allclose(e[3].cpu().float(), r[3].float(), atol=2e-3, rtol=2e-3)
+        assert torch.allclose(e[4].cpu(), r[4], atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_has_inf_nan(dev, dtype):
+    from bmtrain_b200.ops.infnan import has_inf_nan
+
+    torch.manual_seed(4)
+    for n in (1, 7, 31, 1000, 4097, 100000, 1000003):
+        x = torch.randn(n, device=dev, dtype=dtype)
+        flag = torch.zeros(1, dtype=torch.uint8, device=dev)
+        has_inf_nan(x, flag)
+        assert flag.item() == 0
+        for bad in (float("inf"), float("-inf"), float("nan")):
+            y = x.clone()
+            y[torch.randint(0, n, (1,)).item()] = bad
+            flag.zero_()
+            has_inf_nan(y, flag)
+            assert flag.item() == 1, (n, bad)
+    # a misaligned slice is scanned correctly
+    base = torch.zeros(1001, device=dev, dtype=dtype)
+    base[0] = float("nan")
+    flag = torch.zeros(1, dtype=torch.uint8, device=dev)
+    has_inf_nan(base[1:], flag)
+    assert flag.item() == 0
+
+
+def test_sq_norm_and_scale(dev):
+    from bmtrain_b200.ops import infnan
+
+    torch.manual_seed(5)
+    ts = [torch.randn(n, device=dev, dtype=torch.bfloat16) for n in (5, 1000, 70001)]
+    out = torch.zeros(1, device=dev)
+    infnan.multi_sq_norm(ts, out)
+    ref = sum(t.float().pow(2).sum() for t in ts)
+    assert abs(out.item() - ref.item()) / ref.item() < 1e-4
+    before = [t.clone() for t in ts]
+    infnan.multi_scale(ts, torch.tensor([0.5], device=dev))
+    for t, b in zip(ts, before):
+        assert torch.allclose(t.float(), b.float() * 0.5, atol=1e-2, rtol=1e-2)
+    infnan.multi_scale(ts, torch.tensor([3.0], device=dev))  # coefficients >= 1 leave the data alone
+    for t, b in zip(ts, before):
+        assert torch.allclose(t.float(), b.float() * 0.5, atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("classes", [10, 1000, 10240, 30000, 32003])
+def test_cross_entropy(dev, dtype, classes):
+    import bmtrain_b200 as bmt
+
+    torch.manual_seed(6)
+    n = 77
+    x = torch.randn(n, classes, device=dev, dtype=dtype, requires_grad=True)
+    t = torch.randint(0, classes, (n,), device=dev)
+    t[::7] = -100
+    w = torch.rand(classes, device=dev)
+    for weight in (None, w):
+        loss = bmt.loss.FusedCrossEntropy(weight=weight)(x, t)
+        (loss * 32768).backward()
+        xr = x.detach().float().requires_grad_()
+        ref = torch.nn.functional.cross_entropy(xr, t, weight=weight)
+        (ref * 32768).backward()
+        assert abs(loss.item() - ref.item()) < 1e-3 if dtype == torch.bfloat16 else abs(loss.item() - ref.item()) < 1e-4
+        assert (x.grad.float() - xr.grad).abs().max().item() < (4.0 if dtype == torch.bfloat16 else 0.5)
+        x.grad = None
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norms(dev, dtype, rms):
+    from bmtrain_b200.ops import norm as N
+
+    torch.manual_seed(7)
+    for rows, d in ((5, 64), (300, 2560), (64, 8192)):
+        x = torch.randn(rows, d, device=dev, dtype=dtype, requires_grad=True)
+        w = (1 + 0.1 * torch.randn(d, device=dev)).to(dtype).requires_grad_()
+        b = (0.1 * torch.randn(d, device=dev)).to(dtype).requires_grad_()
+        g = torch.randn(rows, d, device=dev, dtype=dtype)
+        y = N.rms_norm(x, w, 1e-5) if rms else N.layer_norm(x, w, b, 1e-5)
+        y.backward(g)
+        xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+        if rms:
+            yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+        else:
+            yr = torch.nn.functional.layer_norm(xr, (d,), wr, br, 1e-5)
+        yr.backward(g.float())
+        tol = 2e-2 if dtype == torch.bfloat16 else 3e-3
+        assert _rel(y, yr) < tol and _rel(x.grad, xr.grad) < tol and _rel(w.grad, wr.grad) < tol
+        if not rms:
+            assert _rel(b.grad, br.grad) < tol
+
+
+def test_embedding(dev):
+    from bmtrain_b200.ops import embedding as E
+
+    torch.manual_seed(8)
+    w = torch.randn(1000, 256, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 1000, (4, 33), device=dev)
+    out = E.embedding(ids, w)
+    assert torch.equal(out, w[ids])
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref = torch.zeros(1000, 256, device=dev)
+    ref.index_add_(0, ids.reshape(-1), g.reshape(-1, 256).float())
+    assert _rel(w.grad, ref) < 1e-2
+    neg = ids.clone()
+    neg[0, :5] = -1
+    out2 = E.embedding_forward(neg, w.detach())
+    assert out2[0, :5].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [(2, 128, 4, 4, 64, False, True), (2, 512, 8, 8, 80, False, True),
+                                 (1, 256, 8, 2, 128, True, False), (3, 100, 2, 2, 64, True, False)])
+def test_attention(dev, dtype, cfg):
+    from bmtrain_b200.ops import attention as AT
+
+    b, s, h, hk, d, causal, dense = cfg
+    torch.manual_seed(9)
+    q = torch.randn(b, s, h, d, device=dev, dtype=dtype, requires_grad=True)
+    k = torch.randn(b, s, hk, d, device=dev, dtype=dtype, requires_grad=True)
+    v = torch.randn(b, s, hk, d, device=dev, dtype=dtype, requires_grad=True)
+    mask = None
+    if dense:
+        valid = torch.arange(s, device=dev)[None] < torch.tensor([s - 3 * i for i in range(b)], device=dev)[:, None]
+        mask = valid[:, None, :] & valid[:, :, None] & torch.ones(s, s, dtype=torch.bool, device=dev).tril()[None]
+    out = AT.attention(q, k, v, causal=causal, mask=mask)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qr, kr, vr = (t.detach().float().cpu().requires_grad_() for t in (q, k, v))
+    ref = AT._reference_attention(qr, kr, vr, 1.0 / math.sqrt(d), causal, None if mask is None else mask.cpu(), None)
+    ref.backward(g.float().cpu())
+    tol = 3e-2 if dtype == torch.bfloat16 else 5e-3
+    assert _rel(out.cpu(), ref) < tol
+    assert _rel(q.grad.cpu(), qr.grad) < tol and _rel(k.grad.cpu(), kr.grad) < tol and _rel(v.grad.cpu(), vr.grad) < tol
+
+
+def test_swiglu_colsum(dev):
+    from bmtrain_b200.ops import elementwise as EW, gemm as G
+
+    torch.manual_seed(10)
+    x = torch.randn(100, 2 * 512, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    y = EW.swiglu(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = torch.nn.functional.silu(xr[:, :512]) * xr[:, 512:]
+    yr.backward(g.float())
+    assert _rel(y, yr) < 2e-2 and _rel(x.grad, xr.grad) < 2e-2
+    z = torch.randn(1000, 520, device=dev, dtype=torch.float16)
+    assert _rel(G.bias_grad(z), z.float().sum(0)) < 2e-3
