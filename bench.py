@@ -1,0 +1,253 @@
+"""Headline benchmark: tokens/s of ZeRO-3 training on the reference's example GPT.
+
+Config (the reference's example/train.py model): 8 pre-LN blocks, d_model 2560, 32 heads x 80, FFN 8192, vocab 10240,
+bias, learned positions (512), fp16 with OptimManager dynamic loss scaling (2**20), ZeRO-3 TransformerBlockList,
+AdamOffloadOptimizer (fp32 state in host memory, weight decay 1e-2), per-GPU batch 2 x 512 uniform random tokens,
+random-init weights.  Weak scaling: per-GPU work is fixed as N grows.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 10 --warmup 3
+    python bench.py --impl reference ...      # the unmodified reference from baseline/_ref, same loop
+
+Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events around exactly K steps, inputs already on the
+device, max over ranks); `e2e` repeats the measurement with every step's inputs copied from pinned host memory and
+the loss read back to the host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+MODEL = dict(num_layers=8, vocab_size=10240, dim_model=2560, dim_head=80, num_heads=32, dim_ff=8192, max_distance=512)
+BATCH, SEQ = 2, 512
+PUBLISHED_TOKENS_PER_GPU_S = 29.42 * 512  # reference README: GPT-2 13B on 4x8 V100, best batch size
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons, power = [], [], set(), []
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1])); power.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the top half of the samples are the ones taken under load
+        busy = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def setup_env(args):
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("LOCAL_RANK", os.environ["RANK"])
+    os.environ.setdefault("LOCAL_WORLD_SIZE", os.environ["WORLD_SIZE"])
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29517")
+    os.environ.setdefault("BMT_QUIET", "1")
+    world = int(os.environ["WORLD_SIZE"])
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+
+
+def build_ours():
+    import torch
+    import bmtrain_b200 as bmt
+
+    bmt.init_distributed(seed=0)
+    model = bmt.models.GPT(**MODEL, bias=True, dtype=torch.half)
+    bmt.init_parameters(model)
+    loss_func = bmt.loss.FusedCrossEntropy(ignore_index=-100)
+    optimizer = bmt.optim.AdamOffloadOptimizer(model.parameters(), weight_decay=1e-2)
+    lr_scheduler = bmt.lr_scheduler.Noam(optimizer, start_lr=1e-3, warmup_iter=40, end_iter=1000, num_iter=0)
+    om = bmt.optim.OptimManager(loss_scale=2 ** 20)
+    om.add_optimizer(optimizer, lr_scheduler)
+
+    def loss_of(logits, targets):
+        return loss_func(logits.view(-1, logits.size(-1)), targets.view(-1))
+
+    from bmtrain_b200.ops import _native
+    import ctypes
+
+    lib = _native.cuda_lib()
+    lib.bmt_launch_count.restype = ctypes.c_int64
+    return bmt, model, om, loss_of, lib.bmt_launch_count
+
+
+def build_reference():
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref", "example"))
+    import torch
+    import bmtrain as bmt
+    from models import GPT  # the reference's own example model
+
+    bmt.init_distributed(seed=0)
+    model = GPT(num_layers=MODEL["num_layers"], vocab_size=MODEL["vocab_size"], dim_model=MODEL["dim_model"],
+                dim_head=MODEL["dim_head"], num_heads=MODEL["num_heads"], dim_ff=MODEL["dim_ff"],
+                max_distance=MODEL["max_distance"], bias=True, dtype=torch.half)
+    bmt.init_parameters(model)
+    loss_func = torch.nn.CrossEntropyLoss(ignore_index=-100)
+    optimizer = bmt.optim.AdamOffloadOptimizer(model.parameters(), weight_decay=1e-2)
+    lr_scheduler = bmt.lr_scheduler.Noam(optimizer, start_lr=1e-3, warmup_iter=40, end_iter=1000, num_iter=0)
+    om = bmt.optim.OptimManager(loss_scale=2 ** 20)
+    om.add_optimizer(optimizer, lr_scheduler)
+
+    def loss_of(logits, targets):
+        return loss_func(logits.view(-1, logits.size(-1)).float(), targets.view(-1))
+
+    return bmt, model, om, loss_of, (lambda: 0)
+
+
+def main():
+    args = parse()
+    setup_env(args)
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "bmtrain")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"}))
+        return
+    import torch
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
+        return
+    try:
+        bmt, model, om, loss_of, launch_count = build_reference() if args.impl == "reference" else build_ours()
+    except Exception as exc:  # the reference may fail to import/run on this image
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}))
+            return
+        raise
+    rank, world = bmt.rank(), bmt.world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator().manual_seed(1000 + rank)
+    n_batches = 4
+    host = [torch.randint(0, MODEL["vocab_size"], (BATCH, SEQ + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+    pos = torch.arange(SEQ, device=dev)[None].expand(BATCH, -1).contiguous()
+    mask = torch.ones(BATCH, SEQ, dtype=torch.bool, device=dev)
+    on_dev = [h.to(dev) for h in host]
+    skipped = 0
+
+    def step(ids, read_loss):
+        nonlocal skipped
+        inp, tgt = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+        logits = model(inp, pos, mask)
+        loss = loss_of(logits, tgt)
+        om.zero_grad()
+        before = om.loss_scale
+        om.backward(loss)
+        om.step()
+        if om.loss_scale < before:
+            skipped += 1
+        return loss.item() if read_loss else None
+
+    # loss-scale settling (not timed, not counted as warm-up): run until a step is not skipped for overflow
+    for i in range(24):
+        s0 = skipped
+        step(on_dev[i % n_batches], False)
+        if skipped == s0:
+            break
+    for i in range(args.warmup):
+        step(on_dev[i % n_batches], False)
+
+    def timed(e2e: bool):
+        nonlocal skipped
+        skipped = 0
+        bmt.synchronize()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+        l0 = launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        for i in range(args.steps):
+            if e2e:
+                ids = host[i % n_batches].to(dev, non_blocking=True)
+                step(ids, True)
+            else:
+                step(on_dev[i % n_batches], False)
+        end.record()
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        bmt.synchronize()
+        ms = max(start.elapsed_time(end), wall_ms) if e2e else start.elapsed_time(end)
+        t = torch.tensor([ms, float(skipped)], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX) if world > 1 else None
+        clocks = sampler.stop() if sampler else None
+        return float(t[0]), int(t[1]), launch_count() - l0, clocks
+
+    ms, skip_dev, launches, clocks = timed(False)
+    ms_e2e, skip_e2e, _, _ = timed(True)
+    tokens = world * BATCH * SEQ * args.steps
+    value = tokens / (ms / 1e3)
+    if rank == 0:
+        out = {
+            "metric": "tokens/sec/box (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / (PUBLISHED_TOKENS_PER_GPU_S * world),
+            "dtype": "fp16", "data": "synthetic uniform token ids, random-init weights",
+            "impl": args.impl,
+            "config": {"model": "GPT 8x d2560 (32 heads x 80, FFN 8192, vocab 10240, bias, max_distance 512)",
+                       "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"zero3-dp{world}",
+                       "optimizer": "AdamOffloadOptimizer + OptimManager(loss_scale=2**20)",
+                       "l2": "inputs larger than L2: each step streams 1.1 GB of fp16 weights plus activations (L2 is 126 MB)",
+                       "baseline_note": "vs_baseline divides by the reference README's best published figure "
+                                        "(29.42 samples/GPU/s x 512 tokens, GPT-2 13B on 32 V100) x n_gpus"},
+            "clocks": clocks,
+            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": BATCH * (SEQ + 1) * 8, "d2h_bytes_per_step": 4,
+                    "timing": "max(CUDA events, wall clock) around K steps incl. pinned-host input copy and loss read-back"},
+            "gpu_launches": launches,
+            "overflow_skipped_steps": {"device_timed": skip_dev, "e2e": skip_e2e},
+        }
+        print(json.dumps(out))
+    try:
+        torch.distributed.destroy_process_group()
+    except Exception:
+        pass
+
+
+if __name__ == "__main__":
+    main()
