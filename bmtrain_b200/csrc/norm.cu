@@ -160,3 +160,57 @@ extern "C" int bmt_norm_bwd(int64_t rows, int64_t d, const void* x, const void* 
     return dtype == BMT_DT_F16 ? bwd<__half>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s)
                                : bwd<__nv_bfloat16>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s);
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant (see norm_noalloc.h).  Same kernels as bmt_norm_bwd; the partial-sum scratch lives in a
+// file-scope device array whose address is resolved once per device.
+#include <mutex>
+#include <stdio.h>
+
+#include "norm_noalloc.h"
+
+static __device__ __align__(256) float g_norm_noalloc_scratch[2 * BMT_NORM_NOALLOC_MAX_CTAS * BMT_NORM_NOALLOC_MAX_D];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+
+// Device address of the scratch array on the current device.  In host code the array's name is only a handle for
+// the runtime, not a device address, so it is never passed to a kernel directly.
+int noalloc_scratch(float** out) {
+    int dev = 0;
+    BMT_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return BMT_NORM_NOALLOC_BAD_ARG;
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        BMT_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_norm_noalloc_scratch));
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+extern "C" int bmt_norm_bwd_noalloc(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats,
+                                    int rms, int dtype, void* dx, void* dw, void* db, void* stream) {
+    if (rows <= 0) return 0;
+    if (d > BMT_NORM_NOALLOC_MAX_D) {
+        fprintf(stderr, "bmt_norm_bwd_noalloc: d = %lld exceeds the built-in scratch (max d %d); use bmt_norm_bwd with your own scratch\n",
+                (long long)d, BMT_NORM_NOALLOC_MAX_D);
+        return BMT_NORM_NOALLOC_TOO_LARGE;
+    }
+    if (d <= 0 || d % 8 != 0 || (dtype != BMT_DT_F16 && dtype != BMT_DT_BF16) || (rms && db != nullptr)) {
+        fprintf(stderr, "bmt_norm_bwd_noalloc: unsupported arguments (d = %lld must be a positive multiple of 8, dtype fp16/bf16, no bias gradient for RMSNorm)\n",
+                (long long)d);
+        return BMT_NORM_NOALLOC_BAD_ARG;
+    }
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc != 0) return rc;
+    const int nblk = rows < BMT_NORM_NOALLOC_MAX_CTAS ? (int)rows : BMT_NORM_NOALLOC_MAX_CTAS;
+    cudaStream_t s = (cudaStream_t)stream;
+    return dtype == BMT_DT_F16 ? bwd<__half>(rows, d, x, dy, w, stats, rms, nblk, dx, scratch, dw, db, s)
+                               : bwd<__nv_bfloat16>(rows, d, x, dy, w, stats, rms, nblk, dx, scratch, dw, db, s);
+}
