@@ -212,8 +212,9 @@ def main():
         wall_ms = (time.perf_counter() - t0) * 1e3
         bmt.synchronize()
         ms = max(start.elapsed_time(end), wall_ms) if e2e else start.elapsed_time(end)
-        t = torch.tensor([ms, float(skipped)], device=dev, dtype=torch.float64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX) if world > 1 else None
+        t = torch.tensor([ms, float(skipped)], device=dev, dtype=torch.float32)
+        if world > 1:
+            t = bmt.distributed.all_reduce(t, "max")  # same call in both arms (each arm's own collective layer)
         clocks = sampler.stop() if sampler else None
         return float(t[0]), int(t[1]), launch_count() - l0, clocks
 
@@ -244,7 +245,8 @@ def main():
         }
         print(json.dumps(out))
     try:
-        torch.distributed.destroy_process_group()
+        if torch.distributed.is_initialized():
+            torch.distributed.destroy_process_group()
     except Exception:
         pass
 

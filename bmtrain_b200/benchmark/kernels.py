@@ -1,0 +1,111 @@
+"""Single-GPU kernel micro-benchmarks against the measured roofline.
+
+    python -m bmtrain_b200.benchmark.kernels --op gemm --m 8192 --n 8192 --k 8192 --dtype bf16 --layout nt
+    python -m bmtrain_b200.benchmark.kernels --op adam --n 268435456
+    python -m bmtrain_b200.benchmark.kernels --op norm|ce|softmax ...
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, a >L2 buffer is rewritten between timed launches
+(``--flush``, default on) so every launch starts with a cold L2.  Peaks come from ``MEASURED_PEAKS.json`` at the
+repository root when present (fallback: 6.65 TB/s, 1.59 PFLOP/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    try:
+        with open(os.path.join(_ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, 1590.0, "fallback"
+
+
+def time_it(fn, iters: int, flush: bool) -> float:
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if scratch is not None:
+            scratch.fill_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="gemm", choices=["gemm", "adam", "norm", "ce", "softmax"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+    dt = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    hbm, tflops, src = peaks()
+    from bmtrain_b200.ops import adam as A, cross_entropy as CE, gemm as G, norm as N
+
+    flush = not args.no_flush
+    dev = "cuda"
+    if args.op == "gemm":
+        m, n, k = args.m, args.n, args.k
+        if args.layout == "nt":
+            a, b = torch.randn(m, k, device=dev, dtype=dt), torch.randn(n, k, device=dev, dtype=dt)
+            fn = lambda: G.gemm_nt(a, b)
+        elif args.layout == "nn":
+            a, b = torch.randn(m, k, device=dev, dtype=dt), torch.randn(k, n, device=dev, dtype=dt)
+            fn = lambda: G.gemm_nn(a, b)
+        else:
+            a, b = torch.randn(k, m, device=dev, dtype=dt), torch.randn(k, n, device=dev, dtype=dt)
+            fn = lambda: G.gemm_tn(a, b)
+        ms = time_it(fn, args.iters, flush)
+        ach = 2.0 * m * n * k / ms / 1e9
+        print(json.dumps({"op": f"gemm_{args.layout}", "m": m, "n": n, "k": k, "dtype": args.dtype, "ms": ms,
+                          "tflops": ach, "frac_of_peak": ach / tflops, "peak_source": src}))
+    elif args.op == "adam":
+        n = args.n
+        p32 = torch.randn(n, device=dev)
+        p16, g = p32.to(dt), torch.randn(n, device=dev).to(dt)
+        m_ = torch.zeros(n, device=dev, dtype=torch.float16 if dt == torch.float16 else torch.float32)
+        v = torch.zeros(n, device=dev)
+        fn = lambda: A.adam_half_multi([(p32, p16, g, m_, v)], 0.9, 0.999, 1e-8, 1e-3, 1.0, 0.01, 3)
+        ms = time_it(fn, args.iters, flush)
+        nbytes = n * (2 * (4 + 2 + m_.element_size() + 4) + 2)
+        print(json.dumps({"op": "adam", "n": n, "dtype": args.dtype, "ms": ms, "gbs": nbytes / ms / 1e6,
+                          "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_source": src}))
+    elif args.op == "norm":
+        x = torch.randn(args.m, args.n, device=dev, dtype=dt)
+        w, b = torch.ones(args.n, device=dev, dtype=dt), torch.zeros(args.n, device=dev, dtype=dt)
+        fn = lambda: N.layer_norm(x, w, b)
+        ms = time_it(fn, args.iters, flush)
+        nbytes = 2 * x.numel() * 2
+        print(json.dumps({"op": "layernorm_fwd", "rows": args.m, "d": args.n, "ms": ms, "gbs": nbytes / ms / 1e6,
+                          "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_source": src}))
+    elif args.op == "ce":
+        x = torch.randn(args.m, args.n, device=dev, dtype=dt)
+        t = torch.randint(0, args.n, (args.m,), device=dev)
+        fn = lambda: CE.row_stats(x, t)
+        ms = time_it(fn, args.iters, flush)
+        nbytes = x.numel() * 2
+        print(json.dumps({"op": "ce_row_stats", "rows": args.m, "classes": args.n, "ms": ms, "gbs": nbytes / ms / 1e6,
+                          "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_source": src}))
+
+
+if __name__ == "__main__":
+    main()
