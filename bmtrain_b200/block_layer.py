@@ -432,6 +432,11 @@ class Block(torch.nn.Module):
             else:
                 _pending.append(finish)
                 _queue_backward_callback()
+            # let an offloading optimizer start moving this partition's gradient to the host right away
+            for holder in [b.storage] + [s.param for s in b.slots]:
+                hook = getattr(holder, "_bmt_grad_hook", None)
+                if hook is not None and holder.grad is not None and holder.numel() > 0:
+                    hook(holder, None if accumulate else work)
 
     # ------------------------------------------------------------- scheduling
     def _enter_forward(self) -> None:

@@ -48,6 +48,9 @@ int bmt_norm_fwd(int64_t rows, int64_t d, const void* x, const void* w, const vo
 int bmt_norm_bwd(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms,
                  int dtype, int nblk, void* dx, void* partial_2xnblkxd_f32, void* dw, void* db, void* stream);
 
+int bmt_norm_bwd_res(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms,
+                     int dtype, int nblk, void* dx, void* partial_2xnblkxd_f32, void* dw, void* db, const void* dres, void* stream);
+
 int bmt_embedding_fwd(int64_t tokens, int64_t d, const void* ids_i64, const void* weight, int dtype, void* out, void* stream);
 int bmt_embedding_bwd(int64_t tokens, int64_t d, const void* ids_i64, const void* grad, int dtype, void* acc_f32, void* stream);
 
@@ -57,7 +60,25 @@ int bmt_softmax_bwd(int64_t rows, int64_t cols, int64_t ld, const void* p, void*
 
 int bmt_swiglu_fwd(int64_t rows, int64_t f, const void* x, int dtype, void* out, void* stream);
 int bmt_swiglu_bwd(int64_t rows, int64_t f, const void* x, const void* g, int dtype, void* dx, void* stream);
+int bmt_gelu_fwd(int64_t n, const void* x, int dtype, void* out, void* stream);
 int bmt_colsum(int64_t m, int64_t n, const void* x, int dtype, void* out, void* stream);
+
+// Full description of one (optionally batched) GEMM launch; zero-initialise, then fill what is needed.
+typedef struct {
+    int64_t m, n, k;
+    const void* a; int64_t lda; int a_major; int64_t a_bs0, a_bs1;   // majors: 0 = reduction dim contiguous, 1 = output dim contiguous
+    const void* b; int64_t ldb; int b_major; int64_t b_bs0, b_bs1;
+    void* c; int64_t ldc; int c_dtype; int64_t c_bs0, c_bs1;
+    int64_t batch_inner, batch_outer, b_inner_div;                    // B's inner batch index = inner index / b_inner_div
+    const void* bias;                                                 // length n, operand dtype
+    int act;                                                          // 0 none, 1 ReLU, 2 GELU
+    int accumulate;                                                   // C += result
+    float alpha;
+    int ab_dtype;
+    const void* residual; int64_t ldr;                                // + residual (m x n, operand dtype)
+    const void* aux; int64_t ld_aux; int aux_mode;                    // 1: *= (aux > 0), 2: *= gelu'(aux)
+} BmtGemmDesc;
+int bmt_gemm_ex(const BmtGemmDesc* desc, void* stream);
 
 // C[M,N] (+)= alpha * op(A) op(B) (+ bias) with optional activation; majors: 0 = reduction dim contiguous, 1 = output dim contiguous.
 int bmt_gemm(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, const void* b, int64_t ldb,
@@ -67,6 +88,52 @@ int bmt_gemm_batched(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda
                      const void* b, int64_t ldb, int b_major, int64_t b_bs0, int64_t b_bs1, void* c, int64_t ldc,
                      int c_dtype, int64_t c_bs0, int64_t c_bs1, int64_t batch_inner, int64_t batch_outer,
                      int64_t b_inner_div, float alpha, int ab_dtype, void* stream);
+// ---- whole transformer block (pre-LN GPT layout) executed as one native call ---------------------------------
+// y = h1 + fc2(act(fc1(LN2(h1)))),  h1 = x + out(attention(qkv(LN1(x))))
+// All activations are caller-provided buffers; forward fills the "saved" ones, backward consumes them.
+typedef struct {
+    int64_t batch, seq, d_model, n_heads, d_head, d_ff;
+    int dtype;   // 0 fp16, 1 bf16
+    int act;     // 1 ReLU, 2 GELU
+    float eps;
+    int causal;
+    const void* mask;  // uint8 (batch, seq, seq), 1 = attend; may be NULL
+    const void *ln1_w, *ln1_b, *qkv_w, *qkv_b, *out_w, *out_b, *ln2_w, *ln2_b, *fc1_w, *fc1_b, *fc2_w, *fc2_b;
+    const void* x;   // (batch*seq, d_model)
+    void* y;         // (batch*seq, d_model)
+    // saved activations
+    void* ln1;       // (T, d)
+    void* stats1;    // (2, T) fp32
+    void* qkv;       // (T, heads, 3, d_head)
+    void* probs;     // (batch, heads, seq, probs_ld)
+    int64_t probs_ld;
+    void* ctx;       // (T, heads*d_head)
+    void* h1;        // (T, d)
+    void* ln2;       // (T, d)
+    void* stats2;    // (2, T) fp32
+    void* ff;        // (T, d_ff) post-activation
+    void* pre;       // (T, d_ff) pre-activation, GELU only (NULL for ReLU)
+} BmtGptBlock;
+
+typedef struct {
+    const void* dy;  // (T, d)
+    void* dx;        // (T, d)
+    void *d_ln1_w, *d_ln1_b, *d_qkv_w, *d_qkv_b, *d_out_w, *d_out_b, *d_ln2_w, *d_ln2_b, *d_fc1_w, *d_fc1_b, *d_fc2_w, *d_fc2_b;
+    int acc_w;       // 1: the four weight-matrix gradients are accumulated into (C += ...), 0: overwritten
+    // workspace
+    void* d_ff;      // (T, d_ff)
+    void* d_ln2;     // (T, d)   also reused for d_ln1
+    void* d_h1;      // (T, d)
+    void* d_ctx;     // (T, heads*d_head)
+    void* d_probs;   // like probs
+    void* d_qkv;     // like qkv
+    void* norm_partial;  // (2, nblk, d) fp32
+    int nblk;
+} BmtGptBlockGrad;
+
+int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream);
+int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockGrad* g, void* stream);
+
 // number of kernel launches issued by this library since load (for launch accounting)
 int64_t bmt_launch_count(void);
 void bmt_count_launch(int n);

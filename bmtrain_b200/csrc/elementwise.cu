@@ -66,6 +66,19 @@ __global__ void __launch_bounds__(256) colsum_kernel(int64_t m, int64_t n, const
     }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) gelu_kernel(int64_t n8, const T* __restrict__ x, T* __restrict__ out) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+        bmt::Vec16<T> v = bmt::ld16(x + i * 8), o;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float f = bmt::Cvt<T>::to_f(v.v[k]);
+            o.v[k] = bmt::Cvt<T>::from_f(0.5f * f * (1.f + erff(f * 0.70710678118654752f)));
+        }
+        bmt::st16(out + i * 8, o);
+    }
+}
+
 unsigned grid1d(int64_t work) {
     int64_t b = bmt::ceil_div64(work, 256);
     if (b > 148 * 8) b = 148 * 8;
@@ -101,6 +114,17 @@ extern "C" int bmt_colsum(int64_t m, int64_t n, const void* x, int dtype, void* 
     const unsigned g = (unsigned)((n + 63) / 64);
     if (dtype == BMT_DT_F16) colsum_kernel<__half><<<g, 256, 0, s>>>(m, n, (const __half*)x, (__half*)out);
     else colsum_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(m, n, (const __nv_bfloat16*)x, (__nv_bfloat16*)out);
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}
+
+// out = gelu(x), n elements (multiple of 8), exact erf form
+extern "C" int bmt_gelu_fwd(int64_t n, const void* x, int dtype, void* out, void* stream) {
+    if (n <= 0) return 0;
+    if (n % 8 || dtype == BMT_DT_F32) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BMT_DT_F16) gelu_kernel<__half><<<grid1d(n / 8), 256, 0, s>>>(n / 8, (const __half*)x, (__half*)out);
+    else gelu_kernel<__nv_bfloat16><<<grid1d(n / 8), 256, 0, s>>>(n / 8, (const __nv_bfloat16*)x, (__nv_bfloat16*)out);
     bmt_count_launch(1);
     return (int)cudaGetLastError();
 }

@@ -53,6 +53,11 @@ struct GemmParams {
     int accumulate;
     float alpha;
     uint32_t idesc;
+    const void* residual;  // optional (M x N, operand dtype, row pitch ldr): added after bias / activation
+    int64_t ldr;
+    const void* aux;       // optional (M x N, operand dtype, row pitch ld_aux) for the multiplicative epilogues
+    int64_t ld_aux;
+    int aux_mode;          // 0 none, 1: out *= (aux > 0)  (ReLU backward), 2: out *= gelu'(aux)
 };
 
 // ------------------------------------------------------------------------------------------ PTX wrappers
@@ -171,8 +176,30 @@ struct SharedHeader {
     int failed;
 };
 
+__device__ __forceinline__ float gelu_grad_f(float x) {
+    const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+    return cdf + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+template <typename TA> __device__ __forceinline__ void apply_extras(const GemmParams& p, int64_t row, int64_t c, int64_t col_end, float* vv) {
+    if (p.aux_mode) {
+        const TA* ar = (const TA*)p.aux + row * p.ld_aux + c;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (c + i < col_end) {
+                const float a = bmt::Cvt<TA>::to_f(ar[i]);
+                vv[i] = p.aux_mode == 1 ? (a > 0.f ? vv[i] : 0.f) : vv[i] * gelu_grad_f(a);
+            }
+    }
+    if (p.residual) {
+        const TA* rr = (const TA*)p.residual + row * p.ldr + c;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (c + i < col_end) vv[i] += bmt::Cvt<TA>::to_f(rr[i]);
+    }
+}
+
 template <typename TC>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, TC* crow, int64_t col0, int64_t col_end, const uint32_t (&r)[32], bool row_ok) {
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, TC* crow, int64_t row, int64_t col0, int64_t col_end, const uint32_t (&r)[32], bool row_ok) {
     // this thread owns one output row and the columns [col0, min(col0 + 32, col_end))
     if (!row_ok) return;
     float v[32];
@@ -199,6 +226,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, TC* crow, in
         } else if (p.act == 2) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) vv[i] = gelu_f(vv[i]);
+        }
+        if (p.aux_mode || p.residual) {
+            if (p.bias_dtype == BMT_DT_F16) apply_extras<__half>(p, row, c, col_end, vv);
+            else apply_extras<__nv_bfloat16>(p, row, c, col_end, vv);
         }
         if (full8 && vec) {
             if (p.accumulate) {
@@ -348,9 +379,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 uint32_t r[32];
                 tmem_ld32(taddr + c0, r);
                 tmem_ld_wait();
-                if (p.c_dtype == BMT_DT_F16) epilogue_chunk<__half>(p, (__half*)p.c + coff, col0, col_end, r, row_ok);
-                else if (p.c_dtype == BMT_DT_BF16) epilogue_chunk<__nv_bfloat16>(p, (__nv_bfloat16*)p.c + coff, col0, col_end, r, row_ok);
-                else epilogue_chunk<float>(p, (float*)p.c + coff, col0, col_end, r, row_ok);
+                if (p.c_dtype == BMT_DT_F16) epilogue_chunk<__half>(p, (__half*)p.c + coff, row, col0, col_end, r, row_ok);
+                else if (p.c_dtype == BMT_DT_BF16) epilogue_chunk<__nv_bfloat16>(p, (__nv_bfloat16*)p.c + coff, row, col0, col_end, r, row_ok);
+                else epilogue_chunk<float>(p, (float*)p.c + coff, row, col0, col_end, r, row_ok);
             }
             tc_fence_before();
             __syncwarp();
@@ -459,10 +490,15 @@ int pick_bn(int64_t M, int64_t N, int64_t batches, bool b_mn, int force_bn) {
     return best;
 }
 
-int launch_gemm(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, int64_t a_bs0, int64_t a_bs1,
-                const void* b, int64_t ldb, int b_major, int64_t b_bs0, int64_t b_bs1, void* c, int64_t ldc, int c_dtype,
-                int64_t c_bs0, int64_t c_bs1, int64_t batch_inner, int64_t batch_outer, int64_t b_inner_div, const void* bias,
-                int act, int accumulate, float alpha, int ab_dtype, cudaStream_t stream) {
+int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
+    const int64_t m = g.m, n = g.n, k = g.k;
+    const void* a = g.a; const void* b = g.b; void* c = g.c; const void* bias = g.bias;
+    const int64_t lda = g.lda, ldb = g.ldb, ldc = g.ldc;
+    const int a_major = g.a_major, b_major = g.b_major, c_dtype = g.c_dtype, act = g.act, accumulate = g.accumulate, ab_dtype = g.ab_dtype;
+    const int64_t a_bs0 = g.a_bs0, a_bs1 = g.a_bs1, b_bs0 = g.b_bs0, b_bs1 = g.b_bs1, c_bs0 = g.c_bs0, c_bs1 = g.c_bs1;
+    const int64_t batch_inner = g.batch_inner > 0 ? g.batch_inner : 1, batch_outer = g.batch_outer > 0 ? g.batch_outer : 1;
+    const int64_t b_inner_div = g.b_inner_div;
+    const float alpha = g.alpha;
     if (m <= 0 || n <= 0 || batch_inner <= 0 || batch_outer <= 0) return 0;
     if (k <= 0) return -20;
     if (g_num_sms == 0) {
@@ -487,6 +523,8 @@ int launch_gemm(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int
     p.batch_inner = batch_inner; p.batch_outer = batch_outer; p.b_inner_div = b_inner_div > 0 ? b_inner_div : 1;
     p.c = c; p.ldc = ldc; p.c_bs0 = c_bs0; p.c_bs1 = c_bs1; p.c_dtype = c_dtype;
     p.bias = bias; p.bias_dtype = ab_dtype; p.act = act; p.accumulate = accumulate; p.alpha = alpha;
+    p.residual = g.residual; p.ldr = g.ldr; p.aux = g.aux; p.ld_aux = g.ld_aux; p.aux_mode = g.aux ? g.aux_mode : 0;
+    if ((p.residual || p.aux_mode) && batch_inner * batch_outer != 1) return -21;  // fused extras are for plain (unbatched) GEMMs
     const uint32_t fmt = ab_dtype == BMT_DT_F16 ? 0u : 1u;
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_major ? 1 : 0) << 15) | ((uint32_t)(b_major ? 1 : 0) << 16) |
               ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -511,19 +549,30 @@ int launch_gemm(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int
 
 }  // namespace
 
+extern "C" int bmt_gemm_ex(const BmtGemmDesc* desc, void* stream) { return launch_gemm(*desc, (cudaStream_t)stream); }
+
 extern "C" int bmt_gemm(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, const void* b, int64_t ldb,
                         int b_major, void* c, int64_t ldc, int c_dtype, const void* bias, int act, int accumulate, int ab_dtype,
                         void* stream) {
-    return launch_gemm(m, n, k, a, lda, a_major, 0, 0, b, ldb, b_major, 0, 0, c, ldc, c_dtype, 0, 0, 1, 1, 1, bias, act,
-                       accumulate, 1.0f, ab_dtype, (cudaStream_t)stream);
+    BmtGemmDesc g;
+    memset(&g, 0, sizeof(g));
+    g.m = m; g.n = n; g.k = k; g.a = a; g.lda = lda; g.a_major = a_major; g.b = b; g.ldb = ldb; g.b_major = b_major;
+    g.c = c; g.ldc = ldc; g.c_dtype = c_dtype; g.bias = bias; g.act = act; g.accumulate = accumulate; g.ab_dtype = ab_dtype;
+    g.batch_inner = g.batch_outer = g.b_inner_div = 1; g.alpha = 1.0f;
+    return launch_gemm(g, (cudaStream_t)stream);
 }
 
 extern "C" int bmt_gemm_batched(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_major, int64_t a_bs0,
                                 int64_t a_bs1, const void* b, int64_t ldb, int b_major, int64_t b_bs0, int64_t b_bs1, void* c,
                                 int64_t ldc, int c_dtype, int64_t c_bs0, int64_t c_bs1, int64_t batch_inner, int64_t batch_outer,
                                 int64_t b_inner_div, float alpha, int ab_dtype, void* stream) {
-    return launch_gemm(m, n, k, a, lda, a_major, a_bs0, a_bs1, b, ldb, b_major, b_bs0, b_bs1, c, ldc, c_dtype, c_bs0, c_bs1,
-                       batch_inner, batch_outer, b_inner_div, nullptr, 0, 0, alpha, ab_dtype, (cudaStream_t)stream);
+    BmtGemmDesc g;
+    memset(&g, 0, sizeof(g));
+    g.m = m; g.n = n; g.k = k; g.a = a; g.lda = lda; g.a_major = a_major; g.a_bs0 = a_bs0; g.a_bs1 = a_bs1;
+    g.b = b; g.ldb = ldb; g.b_major = b_major; g.b_bs0 = b_bs0; g.b_bs1 = b_bs1;
+    g.c = c; g.ldc = ldc; g.c_dtype = c_dtype; g.c_bs0 = c_bs0; g.c_bs1 = c_bs1;
+    g.batch_inner = batch_inner; g.batch_outer = batch_outer; g.b_inner_div = b_inner_div; g.alpha = alpha; g.ab_dtype = ab_dtype;
+    return launch_gemm(g, (cudaStream_t)stream);
 }
 
 // Status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out.  Reading clears it.

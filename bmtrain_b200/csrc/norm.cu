@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(NT) norm_fwd_kernel(int64_t rows, int d, const
 template <typename T>
 __global__ void __launch_bounds__(NT) norm_bwd_kernel(int64_t rows, int d, const T* __restrict__ x, const T* __restrict__ dy,
                                                       const T* __restrict__ w, const float* __restrict__ stats, int rms,
-                                                      T* __restrict__ dx, float* __restrict__ partial) {
+                                                      T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dres) {
     __shared__ float scratch[33];
     float dg[MAXIT][8], db[MAXIT][8];
 #pragma unroll
@@ -92,12 +92,15 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(int64_t rows, int d, const
         for (int it = 0; it < MAXIT; ++it) {
             const int c = threadIdx.x * 8 + it * NT * 8;
             if (c < d) {
-                bmt::Vec16<T> xv = bmt::ld16(xr + c), gv = bmt::ld16(gr + c), wv = bmt::ld16(w + c), o;
+                bmt::Vec16<T> xv = bmt::ld16(xr + c), gv = bmt::ld16(gr + c), wv = bmt::ld16(w + c), o, rv;
+                if (dres) rv = bmt::ld16(dres + r * d + c);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const float xh = (bmt::Cvt<T>::to_f(xv.v[k]) - mean) * rstd;
                     const float wg = bmt::Cvt<T>::to_f(gv.v[k]) * bmt::Cvt<T>::to_f(wv.v[k]);
-                    o.v[k] = bmt::Cvt<T>::from_f(rstd * (wg - s1 - xh * s2));
+                    float val = rstd * (wg - s1 - xh * s2);
+                    if (dres) val += bmt::Cvt<T>::to_f(rv.v[k]);
+                    o.v[k] = bmt::Cvt<T>::from_f(val);
                 }
                 bmt::st16(dr + c, o);
             }
@@ -115,14 +118,28 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(int64_t rows, int d, const
     }
 }
 
+// Fold the per-CTA partial sums: block = 32 columns x 32 row lanes, rows strided over the lanes, smem tree at the end.
 template <typename T>
-__global__ void norm_fold_kernel(int d, int nblk, const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= d) return;
+__global__ void __launch_bounds__(1024) norm_fold_kernel(int d, int nblk, const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db) {
+    __shared__ float sa[32][33], sb[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int c = blockIdx.x * 32 + tx;
     float a = 0.f, bsum = 0.f;
-    for (int i = 0; i < nblk; ++i) { a += partial[(int64_t)i * d + c]; bsum += partial[((int64_t)nblk + i) * d + c]; }
-    dw[c] = bmt::Cvt<T>::from_f(a);
-    if (db) db[c] = bmt::Cvt<T>::from_f(bsum);
+    if (c < d) {
+        for (int i = ty; i < nblk; i += 32) {
+            a += partial[(int64_t)i * d + c];
+            bsum += partial[((int64_t)nblk + i) * d + c];
+        }
+    }
+    sa[ty][tx] = a; sb[ty][tx] = bsum;
+    __syncthreads();
+    if (ty == 0 && c < d) {
+        float ra = 0.f, rb = 0.f;
+#pragma unroll 8
+        for (int l = 0; l < 32; ++l) { ra += sa[l][tx]; rb += sb[l][tx]; }
+        dw[c] = bmt::Cvt<T>::from_f(ra);
+        if (db) db[c] = bmt::Cvt<T>::from_f(rb);
+    }
 }
 
 template <typename T>
@@ -134,9 +151,9 @@ int fwd(int64_t rows, int64_t d, const void* x, const void* w, const void* b, fl
 
 template <typename T>
 int bwd(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms, int nblk, void* dx,
-        void* partial, void* dw, void* db, cudaStream_t s) {
-    norm_bwd_kernel<T><<<nblk, NT, 0, s>>>(rows, (int)d, (const T*)x, (const T*)dy, (const T*)w, (const float*)stats, rms, (T*)dx, (float*)partial);
-    norm_fold_kernel<T><<<(unsigned)((d + 127) / 128), 128, 0, s>>>((int)d, nblk, (const float*)partial, (T*)dw, (T*)db);
+        void* partial, void* dw, void* db, cudaStream_t s, const void* dres = nullptr) {
+    norm_bwd_kernel<T><<<nblk, NT, 0, s>>>(rows, (int)d, (const T*)x, (const T*)dy, (const T*)w, (const float*)stats, rms, (T*)dx, (float*)partial, (const T*)dres);
+    norm_fold_kernel<T><<<(unsigned)((d + 31) / 32), dim3(32, 32), 0, s>>>((int)d, nblk, (const float*)partial, (T*)dw, (T*)db);
     bmt_count_launch(2);
     return (int)cudaGetLastError();
 }
@@ -159,6 +176,16 @@ extern "C" int bmt_norm_bwd(int64_t rows, int64_t d, const void* x, const void* 
     cudaStream_t s = (cudaStream_t)stream;
     return dtype == BMT_DT_F16 ? bwd<__half>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s)
                                : bwd<__nv_bfloat16>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s);
+}
+
+// Backward that also adds a residual-branch gradient: dx = dres + norm_backward(dy).
+extern "C" int bmt_norm_bwd_res(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms,
+                                int dtype, int nblk, void* dx, void* partial, void* dw, void* db, const void* dres, void* stream) {
+    if (rows <= 0) return 0;
+    if (d % 8 != 0 || d > NT * 8 * MAXIT || dtype == BMT_DT_F32) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    return dtype == BMT_DT_F16 ? bwd<__half>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s, dres)
+                               : bwd<__nv_bfloat16>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s, dres);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -9,6 +9,7 @@ column/row parallel and activations between them are sequence-sharded.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -19,6 +20,11 @@ from ..global_var import config
 from ..layer import DistributedModule
 from ..nn import ColumnParallelLinear, Embedding, LayerNorm, Linear, RowParallelLinear, VPEmbedding
 from ..ops import attention as _attn
+from ..ops import gpt_block as _gpt_block
+
+
+# The per-operator module path below stays available (set BMT_FUSED_BLOCK=0) for debugging and as the general fallback.
+_FUSED_BLOCK = os.environ.get("BMT_FUSED_BLOCK", "1") != "0"
 
 
 class Attention(DistributedModule):
@@ -88,8 +94,20 @@ class TransformerEncoder(DistributedModule):
         self.ff = Feedforward(dim_model, dim_ff, bias=bias, dtype=dtype, activation=activation)
         self.causal = causal
 
+    def _fused_ok(self, hidden: torch.Tensor) -> bool:
+        return (hidden.is_cuda and hidden.dim() == 3 and config["tp_size"] == 1 and _FUSED_BLOCK and self.attn.project_qkv.bias is not None
+                and hidden.dtype in (torch.float16, torch.bfloat16) and self.attn.dim_head % 8 == 0)
+
     def forward(self, hidden: torch.Tensor, mask: Optional[torch.Tensor] = None, position_bias=None):
         bmt_inspect.record_tensor(hidden, "hidden")
+        if self._fused_ok(hidden):
+            # one native call per direction for the whole block (csrc/block_exec.cu)
+            a, f = self.attn, self.ff
+            return _gpt_block.gpt_block(
+                hidden, mask, a.num_heads, a.dim_head, f.activation, self.ln_attn.eps, self.causal,
+                self.ln_attn.weight, self.ln_attn.bias, a.project_qkv.weight, a.project_qkv.bias,
+                a.project_out.weight, a.project_out.bias, self.ln_ff.weight, self.ln_ff.bias,
+                f.w_in.weight, f.w_in.bias, f.w_out.weight, f.w_out.bias)
         x = self.ln_attn(hidden)
         x = self.attn(x, mask, self.causal)
         hidden = hidden + x

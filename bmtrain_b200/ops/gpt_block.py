@@ -1,0 +1,140 @@
+"""Whole pre-LN GPT block as one autograd node on the native block executor (``csrc/block_exec.cu``).
+
+Forward issues 9 kernel launches and backward 21 from C++ in a single call each, all contractions on the tcgen05
+GEMM with fused epilogues (bias, ReLU, residual add, ReLU-mask on dgrad).  The big weight gradients are written
+straight into ``param.grad`` when a gradient buffer of the right dtype is already attached (as the ZeRO block
+does before backward), which removes the separate accumulate pass.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _native
+
+_c_void_p, _i64, _int, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+
+
+class _Block(ctypes.Structure):
+    _fields_ = [
+        ("batch", _i64), ("seq", _i64), ("d_model", _i64), ("n_heads", _i64), ("d_head", _i64), ("d_ff", _i64),
+        ("dtype", _int), ("act", _int), ("eps", _f32), ("causal", _int), ("mask", _c_void_p),
+        ("ln1_w", _c_void_p), ("ln1_b", _c_void_p), ("qkv_w", _c_void_p), ("qkv_b", _c_void_p), ("out_w", _c_void_p),
+        ("out_b", _c_void_p), ("ln2_w", _c_void_p), ("ln2_b", _c_void_p), ("fc1_w", _c_void_p), ("fc1_b", _c_void_p),
+        ("fc2_w", _c_void_p), ("fc2_b", _c_void_p),
+        ("x", _c_void_p), ("y", _c_void_p),
+        ("ln1", _c_void_p), ("stats1", _c_void_p), ("qkv", _c_void_p), ("probs", _c_void_p), ("probs_ld", _i64),
+        ("ctx", _c_void_p), ("h1", _c_void_p), ("ln2", _c_void_p), ("stats2", _c_void_p), ("ff", _c_void_p), ("pre", _c_void_p),
+    ]
+
+
+class _Grad(ctypes.Structure):
+    _fields_ = [
+        ("dy", _c_void_p), ("dx", _c_void_p),
+        ("d_ln1_w", _c_void_p), ("d_ln1_b", _c_void_p), ("d_qkv_w", _c_void_p), ("d_qkv_b", _c_void_p),
+        ("d_out_w", _c_void_p), ("d_out_b", _c_void_p), ("d_ln2_w", _c_void_p), ("d_ln2_b", _c_void_p),
+        ("d_fc1_w", _c_void_p), ("d_fc1_b", _c_void_p), ("d_fc2_w", _c_void_p), ("d_fc2_b", _c_void_p),
+        ("acc_w", _int),
+        ("d_ff", _c_void_p), ("d_ln2", _c_void_p), ("d_h1", _c_void_p), ("d_ctx", _c_void_p), ("d_probs", _c_void_p),
+        ("d_qkv", _c_void_p), ("norm_partial", _c_void_p), ("nblk", _int),
+    ]
+
+
+_PARAM_NAMES = ("ln1_w", "ln1_b", "qkv_w", "qkv_b", "out_w", "out_b", "ln2_w", "ln2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b")
+_WEIGHTS = ("qkv_w", "out_w", "fc1_w", "fc2_w")
+
+
+def _fill(blk: _Block, x, y, mask, params, saved, n_heads, d_head, act, eps, causal):
+    b, s, d = x.shape
+    blk.batch, blk.seq, blk.d_model, blk.n_heads, blk.d_head = b, s, d, n_heads, d_head
+    blk.d_ff = params[8].shape[0]
+    blk.dtype = 0 if x.dtype == torch.float16 else 1
+    blk.act = 1 if act == "relu" else 2
+    blk.eps, blk.causal = eps, 1 if causal else 0
+    blk.mask = None if mask is None else mask.data_ptr()
+    for name, p in zip(_PARAM_NAMES, params):
+        setattr(blk, name, p.data_ptr())
+    blk.x, blk.y = x.data_ptr(), y.data_ptr()
+    for name in ("ln1", "stats1", "qkv", "probs", "ctx", "h1", "ln2", "stats2", "ff"):
+        setattr(blk, name, saved[name].data_ptr())
+    blk.probs_ld = saved["probs"].stride(2)
+    blk.pre = saved["pre"].data_ptr() if saved.get("pre") is not None else None
+
+
+class GPTBlockFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mask, n_heads, d_head, act, eps, causal, *params):
+        lib = _native.cuda_lib()
+        x = x.contiguous()
+        b, s, d = x.shape
+        T, hd, dff = b * s, n_heads * d_head, params[8].shape[0]
+        dev, dt = x.device, x.dtype
+        sp = (s + 7) // 8 * 8
+        mask8 = None if mask is None else mask.to(torch.uint8).contiguous()
+        saved = {
+            "ln1": torch.empty(T, d, dtype=dt, device=dev), "stats1": torch.empty(2, T, dtype=torch.float32, device=dev),
+            "qkv": torch.empty(T, 3 * hd, dtype=dt, device=dev),
+            "probs": torch.empty(b, n_heads, s, sp, dtype=dt, device=dev),
+            "ctx": torch.empty(T, hd, dtype=dt, device=dev), "h1": torch.empty(T, d, dtype=dt, device=dev),
+            "ln2": torch.empty(T, d, dtype=dt, device=dev), "stats2": torch.empty(2, T, dtype=torch.float32, device=dev),
+            "ff": torch.empty(T, dff, dtype=dt, device=dev),
+            "pre": torch.empty(T, dff, dtype=dt, device=dev) if act == "gelu" else None,
+        }
+        y = torch.empty_like(x)
+        blk = _Block()
+        _fill(blk, x, y, mask8, params, saved, n_heads, d_head, act, eps, causal)
+        _native.check(lib.bmt_gpt_block_forward(ctypes.byref(blk), _native.stream_handle()), "GPT block forward")
+        ctx.saved, ctx.x, ctx.mask8, ctx.params = saved, x, mask8, params
+        ctx.cfg = (n_heads, d_head, act, eps, causal)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _native.cuda_lib()
+        x, saved, params = ctx.x, ctx.saved, ctx.params
+        n_heads, d_head, act, eps, causal = ctx.cfg
+        b, s, d = x.shape
+        T, hd, dff = b * s, n_heads * d_head, params[8].shape[0]
+        dev, dt = x.device, x.dtype
+        dy = dy.contiguous()
+        blk = _Block()
+        y_dummy = dy  # forward output pointer is not read by backward
+        _fill(blk, x, y_dummy, ctx.mask8, params, saved, n_heads, d_head, act, eps, causal)
+        g = _Grad()
+        dx = torch.empty_like(x)
+        g.dy, g.dx = dy.data_ptr(), dx.data_ptr()
+        # weight gradients: accumulate in place when the owner already attached same-dtype gradient buffers
+        weights = [p for name, p in zip(_PARAM_NAMES, params) if name in _WEIGHTS]
+        in_place = all(p.is_leaf and p.requires_grad and p.grad is not None and p.grad.dtype == dt and p.grad.is_contiguous()
+                       for p in weights)
+        grads = {}
+        for name, p in zip(_PARAM_NAMES, params):
+            if name in _WEIGHTS and in_place:
+                setattr(g, "d_" + name, p.grad.data_ptr())
+            else:
+                grads[name] = torch.empty_like(p)
+                setattr(g, "d_" + name, grads[name].data_ptr())
+        g.acc_w = 1 if in_place else 0
+        nblk = min(T, 296)
+        work = {
+            "d_ff": torch.empty(T, dff, dtype=dt, device=dev), "d_ln2": torch.empty(T, d, dtype=dt, device=dev),
+            "d_h1": torch.empty(T, d, dtype=dt, device=dev), "d_ctx": torch.empty(T, hd, dtype=dt, device=dev),
+            "d_probs": torch.empty_like(saved["probs"]), "d_qkv": torch.empty(T, 3 * hd, dtype=dt, device=dev),
+            "norm_partial": torch.empty(2, nblk, d, dtype=torch.float32, device=dev),
+        }
+        for name, t in work.items():
+            setattr(g, name, t.data_ptr())
+        g.nblk = nblk
+        _native.check(lib.bmt_gpt_block_backward(ctypes.byref(blk), ctypes.byref(g), _native.stream_handle()), "GPT block backward")
+        ctx.saved = None
+        out = [grads.get(name) if p.requires_grad else None for name, p in zip(_PARAM_NAMES, params)]
+        return (dx, None, None, None, None, None, None) + tuple(out)
+
+
+def gpt_block(x: torch.Tensor, mask: Optional[torch.Tensor], n_heads: int, d_head: int, act: str, eps: float, causal: bool,
+              ln1_w, ln1_b, qkv_w, qkv_b, out_w, out_b, ln2_w, ln2_b, fc1_w, fc1_b, fc2_w, fc2_b) -> torch.Tensor:
+    """``x`` (batch, seq, d_model) -> same shape.  ``mask``: optional bool (batch, seq, seq), True = attend."""
+    return GPTBlockFunction.apply(x, mask, n_heads, d_head, act, eps, causal, ln1_w, ln1_b, qkv_w, qkv_b, out_w, out_b,
+                                  ln2_w, ln2_b, fc1_w, fc1_b, fc2_w, fc2_b)

@@ -58,6 +58,11 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         self._hold_steps = hold_steps
         self.record_delta = record_delta
         self._d2h = self._h2d = None
+        self._staged = {}  # param -> event of a gradient copy that was started during backward
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p.is_cuda and (getattr(p, "_bmt_bucket", None) is not None or getattr(p, "_in_block", False)):
+                    p._bmt_grad_hook = self._on_grad_ready
         if record_delta:
             for group in self.param_groups:
                 for p in group["params"]:
@@ -89,6 +94,34 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
             self._d2h = torch.cuda.Stream()
             self._h2d = torch.cuda.Stream()
         return self._d2h, self._h2d
+
+    # -------------------------------------------------- early gradient staging
+    def _on_grad_ready(self, p, work) -> None:
+        """Called by the owning block when the reduce-scatter of ``p.grad`` has been issued (``work``), or with
+        ``None`` when an earlier staged copy became stale (gradient accumulation)."""
+        if work is None:
+            self._staged.pop(p, None)
+            return
+        state = self.state.get(p)
+        if not state or p.dtype == torch.float32 or p.grad is None:
+            return  # first step: host buffers do not exist yet
+        d2h, _ = self._streams()
+        from ..comm import DONE
+
+        if work is DONE:
+            d2h.wait_stream(torch.cuda.current_stream())
+        else:
+            with torch.cuda.stream(d2h):
+                work.wait()
+        with torch.cuda.stream(d2h):
+            state["_grad_fp16"].view(-1).copy_(p.grad.reshape(-1), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(d2h)
+        self._staged[p] = ev
+
+    def _invalidate_staged(self) -> None:
+        """Gradients were modified after backward (clipping): copies made during backward are stale."""
+        self._staged.clear()
 
     # ------------------------------------------------------------------- step
     @torch.no_grad()
@@ -124,6 +157,9 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
             d2h.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(d2h):
                 for i, (p, state, group, lo, hi, _) in enumerate(work):
+                    if p in self._staged:
+                        work[i] = (p, state, group, lo, hi, self._staged[p])
+                        continue
                     key = "_grad_fp32" if p.dtype == torch.float32 else "_grad_fp16"
                     g = p.grad.reshape(-1)
                     state[key].view(-1)[lo:hi].copy_(g[lo:hi], non_blocking=True)
@@ -190,6 +226,7 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
                 p.data.view(-1)[lo:hi].copy_(out_half)
         if on_gpu:
             torch.cuda.current_stream().wait_stream(h2d)
+        self._staged.clear()
         if self.record_delta and total_numel:
             self.avg_delta = sum_delta / total_numel
             self.var_delta = sum_sq_delta / total_numel - self.avg_delta ** 2
@@ -275,4 +312,9 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         self.__setstate__({"state": state, "param_groups": param_groups})
 
     def zero_grad(self, set_to_none: bool = False):
+        if self._staged:
+            # a skipped step may leave copies in flight: let them finish before the gradients are overwritten
+            for ev in self._staged.values():
+                ev.synchronize()
+            self._staged.clear()
         super().zero_grad(set_to_none=set_to_none)

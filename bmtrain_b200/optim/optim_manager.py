@@ -140,6 +140,9 @@ class OptimManager:
             total_norm = total[0] ** (1.0 / norm_type)
         clip_coef = float(max_norm * scale) / (total_norm + eps)
         infnan.multi_scale(grads, clip_coef.reshape(1))
+        for optimizer in self.optimizers:
+            if hasattr(optimizer, "_invalidate_staged"):
+                optimizer._invalidate_staged()
         return total_norm / scale
 
     @torch.no_grad()
