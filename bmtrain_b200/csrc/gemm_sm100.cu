@@ -259,74 +259,151 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, TC* crow, in
     }
 }
 
+// ---- two-CTA (cta_group::2) helpers: the pair shares one 256 x BN accumulator tile, each CTA feeds its own
+// 128 rows of A and its own half of the B tile, the leader CTA (rank 0) issues the MMAs for both.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion is reported to a barrier that may live in the peer CTA (no multicast: the data goes to
+// the executing CTA's own shared memory only).
+__device__ __forceinline__ void tma_load_4d_2cta(const CUtensorMap* map, uint32_t bar_cluster_addr, void* dst, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2cta(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2cta() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_2cta(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_2cta(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at the same shared-memory offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_2cta(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+template <bool CTA2>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // tiles first (1024-byte aligned for the 128-byte swizzle), bookkeeping after them
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int NCTA = CTA2 ? 2 : 1;
+    const uint32_t rank = CTA2 ? cluster_ctarank() : 0u;          // position inside the CTA pair
+    const uint32_t bn_local = (uint32_t)p.bn / NCTA;               // rows of the B tile this CTA loads
     const uint32_t a_bytes = BM * BK * 2;
-    const uint32_t b_bytes = (uint32_t)p.bn * BK * 2;
+    const uint32_t b_bytes = bn_local * BK * 2;
     const uint32_t stage_bytes = a_bytes + b_bytes;
     SharedHeader* hdr = (SharedHeader*)(smem + (size_t)p.stages * stage_bytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (int)((p.K + BK - 1) / BK);
-    const int64_t tiles_per_batch = (int64_t)p.m_blocks * p.n_blocks;
+    const int64_t tiles_per_batch = (int64_t)p.m_blocks * p.n_blocks;   // m_blocks counts (BM * NCTA)-row tiles
     const int64_t num_tiles = tiles_per_batch * p.batch_inner * p.batch_outer;
+    const int64_t first_tile = blockIdx.x / NCTA, tile_step = gridDim.x / NCTA;
     const uint32_t tmem_cols = 2 * p.bn <= 32 ? 32 : 2 * p.bn <= 64 ? 64 : 2 * p.bn <= 128 ? 128 : 2 * p.bn <= 256 ? 256 : 512;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { mbar_init(&hdr->full[s], 1); mbar_init(&hdr->empty[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&hdr->tmem_full[a], 1); mbar_init(&hdr->tmem_empty[a], 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&hdr->tmem_full[a], 1); mbar_init(&hdr->tmem_empty[a], 4 * NCTA); }
         hdr->failed = 0;
         fence_barrier_init();
     }
-    if (warp == 1) { tmem_alloc(&hdr->tmem_base, tmem_cols); tmem_relinquish(); }
+    if (warp == 1) {
+        if (CTA2) { tmem_alloc_2cta(&hdr->tmem_base, tmem_cols); tmem_relinquish_2cta(); }
+        else { tmem_alloc(&hdr->tmem_base, tmem_cols); tmem_relinquish(); }
+    }
     tc_fence_before();
     __syncthreads();
+    if (CTA2) cluster_sync();   // the peer's barriers must be initialised before anything is signalled across
     tc_fence_after();
     const uint32_t tmem_base = hdr->tmem_base;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------------ TMA producer (one per CTA)
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
                 const int64_t batch = tile / tiles_per_batch;
                 const int64_t rem = tile % tiles_per_batch;
                 const int m_blk = (int)(rem % p.m_blocks), n_blk = (int)(rem / p.m_blocks);
                 const int bi = (int)(batch % p.batch_inner), bo = (int)(batch / p.batch_inner);
                 const int bib = (int)(bi / p.b_inner_div);
+                const int m0 = m_blk * (BM * NCTA) + (int)rank * BM;            // this CTA's rows of A
+                const int n0 = n_blk * p.bn + (int)(rank * bn_local);           // this CTA's rows of the B tile
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % p.stages;
                     const uint32_t ph = (it / p.stages) & 1;
                     if (!mbar_wait(&hdr->empty[s], ph ^ 1)) { ok = false; atomicCAS(&g_gemm_status, 0, (1 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
                     uint8_t* sa = smem + (size_t)s * stage_bytes;
                     uint8_t* sb = sa + a_bytes;
-                    mbar_expect_tx(&hdr->full[s], stage_bytes);
-                    if (!p.a_mn) {
-                        tma_load_4d(&tma_a, &hdr->full[s], sa, kb * BK, m_blk * BM, bi, bo);
-                    } else {
+                    if (!CTA2) {
+                        mbar_expect_tx(&hdr->full[s], stage_bytes);
+                        if (!p.a_mn) {
+                            tma_load_4d(&tma_a, &hdr->full[s], sa, kb * BK, m0, bi, bo);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BM / 64; ++c)
-                            tma_load_4d(&tma_a, &hdr->full[s], sa + c * (64 * BK * 2), m_blk * BM + c * 64, kb * BK, bi, bo);
-                    }
-                    if (!p.b_mn) {
-                        tma_load_4d(&tma_b, &hdr->full[s], sb, kb * BK, n_blk * p.bn, bib, bo);
+                            for (int c = 0; c < BM / 64; ++c)
+                                tma_load_4d(&tma_a, &hdr->full[s], sa + c * (64 * BK * 2), m0 + c * 64, kb * BK, bi, bo);
+                        }
+                        if (!p.b_mn) {
+                            tma_load_4d(&tma_b, &hdr->full[s], sb, kb * BK, n0, bib, bo);
+                        } else {
+                            for (int c = 0; c < (int)bn_local / 64; ++c)
+                                tma_load_4d(&tma_b, &hdr->full[s], sb + c * (64 * BK * 2), n0 + c * 64, kb * BK, bib, bo);
+                        }
                     } else {
-                        for (int c = 0; c < p.bn / 64; ++c)
-                            tma_load_4d(&tma_b, &hdr->full[s], sb + c * (64 * BK * 2), n_blk * p.bn + c * 64, kb * BK, bib, bo);
+                        // both CTAs report to the leader's barrier; the leader announces the bytes of the pair
+                        const uint32_t bar = map_to_cta(smem_u32(&hdr->full[s]), 0);
+                        if (rank == 0) mbar_expect_tx(&hdr->full[s], 2 * stage_bytes);
+                        if (!p.a_mn) {
+                            tma_load_4d_2cta(&tma_a, bar, sa, kb * BK, m0, bi, bo);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < BM / 64; ++c)
+                                tma_load_4d_2cta(&tma_a, bar, sa + c * (64 * BK * 2), m0 + c * 64, kb * BK, bi, bo);
+                        }
+                        if (!p.b_mn) {
+                            tma_load_4d_2cta(&tma_b, bar, sb, kb * BK, n0, bib, bo);
+                        } else {
+                            for (int c = 0; c < (int)bn_local / 64; ++c)
+                                tma_load_4d_2cta(&tma_b, bar, sb + c * (64 * BK * 2), n0 + c * 64, kb * BK, bib, bo);
+                        }
                     }
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only in pair mode)
+        if (lane == 0 && rank == 0) {
             uint32_t it = 0, tcount = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++tcount) {
                 const uint32_t acc = tcount & 1;
                 const uint32_t acc_ph = (tcount >> 1) & 1;
                 if (!mbar_wait(&hdr->tmem_empty[acc], acc_ph ^ 1)) { ok = false; atomicCAS(&g_gemm_status, 0, (2 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
@@ -346,19 +423,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                                                    : make_smem_desc(sa + k * (UMMA_K * 2), 0, 1024);
                         const uint64_t bd = p.b_mn ? make_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
                                                    : make_smem_desc(sb + k * (UMMA_K * 2), 0, 1024);
-                        umma_f16(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (CTA2) umma_f16_2cta(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                        else umma_f16(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    umma_commit(&hdr->empty[s]);  // frees the smem stage once these MMAs have read it
+                    // frees the smem stage (in both CTAs) once these MMAs have read it
+                    if (CTA2) umma_commit_2cta(&hdr->empty[s]); else umma_commit(&hdr->empty[s]);
                 }
-                if (ok) umma_commit(&hdr->tmem_full[acc]);
+                if (ok) { if (CTA2) umma_commit_2cta(&hdr->tmem_full[acc]); else umma_commit(&hdr->tmem_full[acc]); }
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------------ epilogue (warps 2..5), own 128 rows
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) are visible to this warp
         uint32_t tcount = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++tcount) {
             const int64_t batch = tile / tiles_per_batch;
             const int64_t rem = tile % tiles_per_batch;
             const int m_blk = (int)(rem % p.m_blocks), n_blk = (int)(rem / p.m_blocks);
@@ -367,7 +446,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const uint32_t acc_ph = (tcount >> 1) & 1;
             if (!mbar_wait(&hdr->tmem_full[acc], acc_ph)) { ok = false; atomicCAS(&g_gemm_status, 0, (4 << 16) | (blockIdx.x & 0xffff)); break; }
             tc_fence_after();
-            const int64_t row = (int64_t)m_blk * BM + quarter * 32 + lane;
+            const int64_t row = (int64_t)m_blk * (BM * NCTA) + rank * BM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
             const int64_t coff = bi * p.c_bs0 + bo * p.c_bs1 + row * p.ldc;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * p.bn;
@@ -385,7 +464,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&hdr->tmem_empty[acc]);
+            if (lane == 0) {
+                if (CTA2) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->tmem_empty[acc]), 0));
+                else mbar_arrive(&hdr->tmem_empty[acc]);
+            }
         }
     }
 
@@ -397,8 +479,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
         __syncthreads();
     }
+    if (CTA2) cluster_sync();   // the peer may still be signalling barriers in this CTA's shared memory
     tc_fence_after();
-    if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+    if (warp == 1) { if (CTA2) tmem_dealloc_2cta(tmem_base, tmem_cols); else tmem_dealloc(tmem_base, tmem_cols); }
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -475,17 +558,31 @@ int make_map(CUtensorMap* out, const void* ptr, int dtype, int64_t inner, int64_
 
 int g_num_sms = 0;
 
-int pick_bn(int64_t M, int64_t N, int64_t batches, bool b_mn, int force_bn) {
-    if (force_bn > 0) return force_bn;
-    const int64_t mb = (M + BM - 1) / BM;
-    int best = 0;
+// Tile selection.  Per k-block (64 deep) an SM spends about 2.05 * BN clocks on the MMAs of its 128 accumulator rows
+// and has to pull (128 + BN / ncta) * 128 bytes from L2 at about 64 bytes per clock; the slower of the two sets
+// the pace.  A CTA pair (cta_group::2, 256 x BN tile) halves the B bytes per SM, which is what lifts large
+// problems off the L2->SM limit.  The cost also counts waves on the available SMs and a fixed per-tile overhead.
+struct TileChoice { int bn; int cta2; };
+
+TileChoice pick_tile(int64_t M, int64_t N, int64_t K, int64_t batches, bool b_mn, int force_bn, int force_cta2) {
+    TileChoice best{0, 0};
     double best_cost = 1e30;
-    const int step = b_mn ? 64 : 16;
-    for (int bn = b_mn ? 64 : 32; bn <= 256; bn += step) {
-        const int64_t tiles = mb * ((N + bn - 1) / bn) * batches;
-        const int64_t waves = (tiles + g_num_sms - 1) / g_num_sms;
-        const double cost = (double)waves * (bn + 24);  // 24: per-tile fixed cost in units of N columns
-        if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && bn > best)) { best_cost = cost; best = bn; }
+    const double kblocks = (double)((K + BK - 1) / BK);
+    for (int cta2 = 0; cta2 <= 1; ++cta2) {
+        if (force_cta2 >= 0 && cta2 != force_cta2) continue;
+        if (cta2 && M <= BM) continue;
+        const int ncta = cta2 ? 2 : 1;
+        const int step = (b_mn ? 64 : 16) * ncta;
+        for (int bn = (b_mn ? 64 : 32) * ncta; bn <= 256; bn += step) {
+            if (force_bn > 0 && bn != force_bn) continue;
+            const int64_t tiles = ((M + BM * ncta - 1) / (BM * ncta)) * ((N + bn - 1) / bn) * batches;
+            const int64_t slots = g_num_sms / ncta;
+            const int64_t waves = (tiles + slots - 1) / slots;
+            const double mma = 2.05 * bn, load = 2.0 * (128 + bn / ncta);
+            const double per_tile = kblocks * (mma > load ? mma : load) + 600.0 + 6.0 * bn;  // + fill/drain and epilogue
+            const double cost = (double)waves * per_tile;
+            if (cost < best_cost * 0.999) { best_cost = cost; best = TileChoice{bn, cta2}; }
+        }
     }
     return best;
 }
@@ -505,20 +602,26 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
         int dev = 0;
         BMT_CUDA_OK(cudaGetDevice(&dev));
         BMT_CUDA_OK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
-        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
     }
-    static int force_bn = -1;
+    static int force_bn = -1, force_cta2 = -2;
     if (force_bn < 0) { const char* e = getenv("BMT_GEMM_BN"); force_bn = e ? atoi(e) : 0; }
+    if (force_cta2 == -2) { const char* e = getenv("BMT_GEMM_CTA2"); force_cta2 = e ? atoi(e) : -1; }
 
     GemmParams p;
     memset(&p, 0, sizeof(p));
     p.M = m; p.N = n; p.K = k;
     p.a_mn = a_major; p.b_mn = b_major;
-    p.bn = pick_bn(m, n, batch_inner * batch_outer, b_major != 0, force_bn);
-    const uint32_t stage_bytes = BM * BK * 2 + p.bn * BK * 2;
+    TileChoice tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, force_bn, force_cta2);
+    if (tc.bn == 0) tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, 0, -1);  // forced shape not applicable here
+    if (tc.bn == 0) return -22;
+    p.bn = tc.bn;
+    const int ncta = tc.cta2 ? 2 : 1;
+    const uint32_t stage_bytes = BM * BK * 2 + (p.bn / ncta) * BK * 2;
     int stages = (int)((SMEM_BUDGET - 1024) / stage_bytes);
     p.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
-    p.m_blocks = (int)((m + BM - 1) / BM);
+    p.m_blocks = (int)((m + BM * ncta - 1) / (BM * ncta));
     p.n_blocks = (int)((n + p.bn - 1) / p.bn);
     p.batch_inner = batch_inner; p.batch_outer = batch_outer; p.b_inner_div = b_inner_div > 0 ? b_inner_div : 1;
     p.c = c; p.ldc = ldc; p.c_bs0 = c_bs0; p.c_bs1 = c_bs1; p.c_dtype = c_dtype;
@@ -527,7 +630,7 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
     if ((p.residual || p.aux_mode) && batch_inner * batch_outer != 1) return -21;  // fused extras are for plain (unbatched) GEMMs
     const uint32_t fmt = ab_dtype == BMT_DT_F16 ? 0u : 1u;
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_major ? 1 : 0) << 15) | ((uint32_t)(b_major ? 1 : 0) << 16) |
-              ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+              ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)((BM * ncta) >> 4) << 24);
 
     CUtensorMap ma, mb;
     int rc;
@@ -535,16 +638,32 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
     if (!a_major) rc = make_map(&ma, a, ab_dtype, k, m, lda, batch_inner, a_bs0, batch_outer, a_bs1, BK, BM);
     else          rc = make_map(&ma, a, ab_dtype, m, k, lda, batch_inner, a_bs0, batch_outer, a_bs1, 64, BK);
     if (rc) return rc;
-    if (!b_major) rc = make_map(&mb, b, ab_dtype, k, n, ldb, nb_b, b_bs0, batch_outer, b_bs1, BK, p.bn);
+    if (!b_major) rc = make_map(&mb, b, ab_dtype, k, n, ldb, nb_b, b_bs0, batch_outer, b_bs1, BK, p.bn / ncta);
     else          rc = make_map(&mb, b, ab_dtype, n, k, ldb, nb_b, b_bs0, batch_outer, b_bs1, 64, BK);
     if (rc) return rc;
 
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * batch_inner * batch_outer;
-    const unsigned grid = (unsigned)(tiles < g_num_sms ? tiles : g_num_sms);
     const size_t smem = (size_t)p.stages * stage_bytes + sizeof(SharedHeader) + 1024;
-    gemm_tcgen05_kernel<<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+    if (!tc.cta2) {
+        const unsigned grid = (unsigned)(tiles < g_num_sms ? tiles : g_num_sms);
+        gemm_tcgen05_kernel<false><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+        bmt_count_launch(1);
+        return (int)cudaGetLastError();
+    }
+    const int64_t pairs = g_num_sms / 2;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<true>, ma, mb, p);
     bmt_count_launch(1);
-    return (int)cudaGetLastError();
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 }  // namespace
