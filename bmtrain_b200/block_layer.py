@@ -255,6 +255,7 @@ class Block(torch.nn.Module):
         self._zero_level = zero_level
         self._last_out_spec = None
         self._grad_mode = False
+        self._slot_parity = 0
         if _share is not None:
             self.reference(_share)
         else:
@@ -390,6 +391,17 @@ class Block(torch.nn.Module):
             b.work = None
         self._resident = False
 
+    def _peer_runtime(self, b: _Bucket):
+        """NVLink peer-memory runtime for this bucket's ZeRO group, or None (CPU ranks, one rank, fp32, disabled)."""
+        if not b.storage.is_cuda or b.comm.size == 1 or b.dtype not in (torch.float16, torch.bfloat16):
+            return None
+        from .parallel import symm
+
+        return symm.peer_runtime(b.comm)
+
+    def _grad_slot_key(self, b: _Bucket):
+        return ("grad", self._slot_parity, b.key, b.total)
+
     def _prepare_grads(self) -> None:
         """Full-size zeroed gradient buffers; inner ``.grad`` fields become views into them."""
         for b in self._buckets.values():
@@ -399,7 +411,19 @@ class Block(torch.nn.Module):
             if not needs:
                 continue
             if b.full_grad is None:
-                b.full_grad = torch.zeros(b.total, dtype=b.dtype, device=b.storage.device)
+                rt = self._peer_runtime(b)
+                if rt is not None:
+                    # staging buffer in peer-visible memory; peers must have finished reading its previous contents
+                    key = self._grad_slot_key(b)
+                    buf = rt.slot(key, b.total * b.storage.element_size())
+                    done_row = rt.row(key + ("done",))
+                    if rt.epochs.get(done_row, 0) > 0:
+                        rt.signal_wait(done_row, rt.epochs[done_row], signal=False, wait=True)
+                    b.full_grad = buf.tensor(b.dtype, b.total).zero_()
+                    b.full_grad_buf = buf
+                else:
+                    b.full_grad = torch.zeros(b.total, dtype=b.dtype, device=b.storage.device)
+                    b.full_grad_buf = None
             for s in needs:
                 s.param.grad = b.full_grad[s.offset:s.offset + s.numel].view(s.shape)
 
@@ -413,18 +437,37 @@ class Block(torch.nn.Module):
             if b.full_grad is None:
                 continue
             full_grad, b.full_grad = b.full_grad, None
-            piece = torch.empty(b.part, dtype=b.dtype, device=full_grad.device)
-            work = b.comm.reduce_scatter_into(piece, full_grad, "sum", async_op=True)
             accumulate = b.storage.grad is not None
+            rt = self._peer_runtime(b) if getattr(b, "full_grad_buf", None) is not None else None
+            if rt is not None:
+                # fused path: one kernel on the peer stream reads every rank's staging buffer over NVLink, sums in
+                # fp32, adds the gradient accumulated so far, checks inf/nan and writes the partition
+                from .parallel.symm import StreamWork
+
+                key = self._grad_slot_key(b)
+                piece = b.storage.grad if accumulate else torch.empty(b.part, dtype=b.dtype, device=full_grad.device)
+                rt.stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(rt.stream):
+                    rt.reduce_scatter(b.full_grad_buf, rt.row(key + ("ready",)), b.part, piece, accumulate)
+                    done_row = rt.row(key + ("done",))
+                    rt.signal_wait(done_row, rt.next_epoch(done_row), signal=True, wait=False)
+                    ev = torch.cuda.Event()
+                    ev.record(rt.stream)
+                work = StreamWork(ev)
+                fused = True
+            else:
+                piece = torch.empty(b.part, dtype=b.dtype, device=full_grad.device)
+                work = b.comm.reduce_scatter_into(piece, full_grad, "sum", async_op=True)
+                fused = False
             if not accumulate:
                 b.storage.grad = piece
             for s in b.slots:
                 if s.param.requires_grad:
                     s.param.grad = b.storage.grad[s.lo - b.begin:s.hi - b.begin]
 
-            def finish(work=work, b=b, piece=piece, full_grad=full_grad, accumulate=accumulate):
+            def finish(work=work, b=b, piece=piece, full_grad=full_grad, accumulate=accumulate, fused=fused):
                 work.wait()
-                if accumulate:
+                if accumulate and not fused:
                     b.storage.grad.add_(piece)
 
             if work is DONE:
@@ -721,6 +764,7 @@ class TransformerBlockList(torch.nn.Module):
             pre_module = module
             module._is_first_layer = False
             module._is_last_layer = False
+            module._slot_parity = i % 2  # neighbouring blocks alternate between two peer-visible gradient staging slots
             self.add_module(str(i), module)
         self._modules[str(0)]._is_first_layer = True
         self._modules[str(len(modules) - 1)]._is_last_layer = True

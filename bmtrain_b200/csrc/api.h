@@ -134,6 +134,19 @@ typedef struct {
 int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream);
 int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockGrad* g, void* stream);
 
+// ---- peer memory (one NVLink domain) ------------------------------------------------------------------------------
+int bmt_symm_alloc(int64_t bytes, void** out);
+int bmt_symm_free(void* p);
+int bmt_ipc_get_handle(void* p, void* handle64);
+int bmt_ipc_open_handle(const void* handle64, void** out);
+int bmt_ipc_close(void* p);
+int bmt_ipc_handle_size(void);
+int bmt_fused_reduce_scatter(const void* const* peers, void* const* peer_flags, int world, int rank, int slot,
+                             unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
+                             void* overflow_u8, void* status_i32, double timeout_s, void* stream);
+int bmt_symm_signal_wait(void* device_flag_table, int world, int rank, int slot, unsigned int epoch, int do_signal,
+                         int do_wait, void* status_i32, double timeout_s, void* stream);
+
 // number of kernel launches issued by this library since load (for launch accounting)
 int64_t bmt_launch_count(void);
 void bmt_count_launch(int n);

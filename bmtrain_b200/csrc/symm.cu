@@ -1,0 +1,183 @@
+// Peer-memory runtime for one NVLink / NVSwitch domain and the fused gradient reduce-scatter kernel.
+//
+// Symmetric buffers: every rank cudaMallocs a buffer of the same size, exports it with cudaIpcGetMemHandle and
+// maps the buffers of its peers with cudaIpcOpenMemHandle (the handles travel through the Python side's process
+// group).  Kernels then receive a table of W device pointers, one per rank, and read or write peers' memory with
+// ordinary loads and stores that cross NVLink.  Synchronisation between ranks uses small flag arrays that live in
+// the same kind of buffer: a rank publishes "epoch e reached" by storing e into its slot of every peer's flag
+// array (st.release.sys); waiting is a bounded poll with ld.acquire.sys that gives up after a time limit and
+// reports through a status word -- nothing spins forever and nothing traps.
+// (The reference only has blocking NCCL wrappers: csrc/include/nccl.hpp:8-188.)
+#include <stdio.h>
+#include <string.h>
+
+#include "api.h"
+#include "common.cuh"
+
+extern "C" int bmt_symm_alloc(int64_t bytes, void** out) {
+    void* p = nullptr;
+    BMT_CUDA_OK(cudaMalloc(&p, (size_t)bytes));
+    BMT_CUDA_OK(cudaMemset(p, 0, (size_t)bytes));
+    *out = p;
+    return 0;
+}
+extern "C" int bmt_symm_free(void* p) { return (int)cudaFree(p); }
+extern "C" int bmt_ipc_get_handle(void* p, void* handle64) {
+    cudaIpcMemHandle_t h;
+    BMT_CUDA_OK(cudaIpcGetMemHandle(&h, p));
+    memcpy(handle64, &h, sizeof(h));
+    return 0;
+}
+extern "C" int bmt_ipc_open_handle(const void* handle64, void** out) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    void* p = nullptr;
+    BMT_CUDA_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *out = p;
+    return 0;
+}
+extern "C" int bmt_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+extern "C" int bmt_ipc_handle_size(void) { return (int)sizeof(cudaIpcMemHandle_t); }
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t now_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Wait until flags[0..n) are all >= epoch (counters only grow); false after `limit_ns`.
+__device__ bool wait_flags(const unsigned int* flags, int n, unsigned int epoch, uint64_t limit_ns) {
+    const uint64_t t0 = now_ns();
+    for (int j = 0; j < n; ++j) {
+        unsigned int spins = 0;
+        while ((int)(ld_acquire_sys(flags + j) - epoch) < 0) {
+            if ((++spins & 255u) == 0 && now_ns() - t0 > limit_ns) return false;
+        }
+    }
+    return true;
+}
+
+struct RsArgs {
+    const void* peer[8];       // full gradient buffer of every rank (own rank included), `total` elements each
+    unsigned int* peer_flags[8];  // flag array of every rank (own included): slot s*W + j = "rank j finished producing slot s"
+    int world, rank, slot;
+    unsigned int epoch;
+    int64_t part;              // elements of one partition; this rank reduces [rank*part, (rank+1)*part)
+    void* out;                 // partition gradient (param dtype)
+    int accumulate;            // out += ...
+    float scale;               // result multiplied by this (1/loss_scale, or 1)
+    unsigned char* overflow;   // set to 1 when an inf/nan shows up in the reduced values
+    int* status;               // set to a non-zero code when the wait ran out
+    uint64_t limit_ns;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) fused_rs_kernel(RsArgs a) {
+    __shared__ int ok_s;
+    // 1. tell every rank that this rank's buffer (written by earlier kernels of this stream) is complete
+    if (blockIdx.x == 0 && threadIdx.x < a.world) {
+        __threadfence_system();
+        st_release_sys(a.peer_flags[threadIdx.x] + a.slot * a.world + a.rank, a.epoch);
+    }
+    // 2. wait until every rank has said the same (bounded)
+    if (threadIdx.x == 0) {
+        const bool ok = wait_flags(a.peer_flags[a.rank] + a.slot * a.world, a.world, a.epoch, a.limit_ns);
+        if (!ok) atomicCAS(a.status, 0, 0x100 | a.rank);
+        ok_s = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!ok_s) return;
+    // 3. this rank's partition: sum over ranks in rank order (fp32), scale, accumulate, inf/nan, write
+    const int64_t base = (int64_t)a.rank * a.part;
+    const int64_t nvec = a.part / 8;
+    T* __restrict__ out = (T*)a.out;
+    bool bad = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        bmt::Vec16<T> v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j < a.world) v[j] = bmt::ld16((const T*)a.peer[j] + base + i * 8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j < a.world) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] += bmt::Cvt<T>::to_f(v[j].v[k]);
+            }
+        bmt::Vec16<T> o;
+        if (a.accumulate) {
+            bmt::Vec16<T> old = bmt::ld16(out + i * 8);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = acc[k] * a.scale + bmt::Cvt<T>::to_f(old.v[k]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] *= a.scale;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            bad |= !(fabsf(acc[k]) <= 3.402823466e38f);
+            o.v[k] = bmt::Cvt<T>::from_f(acc[k]);
+            bad |= !(fabsf(bmt::Cvt<T>::to_f(o.v[k])) <= 3.402823466e38f);
+        }
+        bmt::st16(out + i * 8, o);
+    }
+    if (__syncthreads_or(bad) && threadIdx.x == 0 && a.overflow) *a.overflow = 1;
+}
+
+__global__ void symm_signal_wait_kernel(unsigned int* const* peer_flags_table, unsigned int** unused, int world, int rank, int slot,
+                                        unsigned int epoch, int do_signal, int do_wait, int* status, uint64_t limit_ns) {
+    // grid of one block: publish and/or wait on a flag row (used as a cross-rank barrier on a stream)
+    if (do_signal && threadIdx.x < world) {
+        __threadfence_system();
+        st_release_sys(peer_flags_table[threadIdx.x] + slot * world + rank, epoch);
+    }
+    if (do_wait && threadIdx.x == 0) {
+        if (!wait_flags(peer_flags_table[rank] + slot * world, world, epoch, limit_ns)) atomicCAS(status, 0, 0x200 | rank);
+    }
+}
+
+}  // namespace
+
+// Fused reduce-scatter: out[0..part) (+)= scale * sum_j peer_j[rank*part + i], with inf/nan detection.
+// peers / peer_flags: host arrays of `world` device pointers.  part must be a multiple of 8 elements and every
+// buffer 16-byte aligned.  dtype: 0 fp16, 1 bf16, 2 fp32.
+extern "C" int bmt_fused_reduce_scatter(const void* const* peers, void* const* peer_flags, int world, int rank, int slot,
+                                        unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
+                                        void* overflow_u8, void* status_i32, double timeout_s, void* stream) {
+    if (world < 1 || world > 8) return -30;
+    if (part % 8 != 0) return -31;
+    RsArgs a;
+    memset(&a, 0, sizeof(a));
+    for (int j = 0; j < world; ++j) { a.peer[j] = peers[j]; a.peer_flags[j] = (unsigned int*)peer_flags[j]; }
+    a.world = world; a.rank = rank; a.slot = slot; a.epoch = epoch; a.part = part; a.out = out; a.accumulate = accumulate;
+    a.scale = scale; a.overflow = (unsigned char*)overflow_u8; a.status = (int*)status_i32;
+    a.limit_ns = (uint64_t)(timeout_s * 1e9);
+    int64_t blocks = bmt::ceil_div64(part / 8, 256);
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks < 1) blocks = 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BMT_DT_F16) fused_rs_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>(a);
+    else if (dtype == BMT_DT_BF16) fused_rs_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(a);
+    else return -32;
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}
+
+// Stream-ordered cross-rank signal and/or bounded wait on flag row `slot` (device table of per-rank flag pointers).
+extern "C" int bmt_symm_signal_wait(void* device_flag_table, int world, int rank, int slot, unsigned int epoch, int do_signal,
+                                    int do_wait, void* status_i32, double timeout_s, void* stream) {
+    symm_signal_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned int* const*)device_flag_table, nullptr, world, rank, slot,
+                                                                epoch, do_signal, do_wait, (int*)status_i32,
+                                                                (uint64_t)(timeout_s * 1e9));
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}

@@ -242,6 +242,11 @@ def is_initialized() -> bool:
 
 def shutdown() -> None:
     """Tear the process groups down (tests call this between cases)."""
+    if config.get("device") is not None and config["device"].type == "cuda":
+        from .parallel import symm
+
+        torch.cuda.synchronize()
+        symm.reset()
     if dist.is_initialized():
         dist.destroy_process_group()
     config["initialized"] = False

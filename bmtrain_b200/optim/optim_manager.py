@@ -28,6 +28,14 @@ def check_overflow(param_groups) -> None:
     grads = [p.grad for group in param_groups for p in group["params"]
              if p.grad is not None and p.dtype != torch.float32]
     infnan.multi_has_inf_nan([g if g.is_contiguous() else g.contiguous() for g in grads], flag)
+    if dev.type == "cuda":
+        # gradients reduced by the fused NVLink kernel were checked there
+        from ..parallel import symm
+
+        for rt in symm._runtimes.values():
+            if rt is not None:
+                flag |= rt.overflow
+                rt.overflow.zero_()
     if config["comm"].size > 1:
         f32 = flag.to(torch.int32)
         config["comm"].all_reduce(f32, "max")

@@ -1,6 +1,205 @@
-"""Peer-memory runtime hook (filled in by the NVLink symmetric-buffer implementation)."""
+"""Peer-memory (NVLink) runtime: symmetric buffers, flag rows and the fused gradient reduce-scatter.
+
+One :class:`PeerRuntime` exists per communicator whose ranks sit in one NVLink / NVSwitch domain.  It owns
+
+* symmetric buffers -- every rank allocates the same size, the CUDA IPC handles are exchanged through the
+  communicator's process group and every rank maps all peers' buffers (``csrc/symm.cu``),
+* a symmetric flag buffer: row ``s`` holds one 32-bit counter per rank; rank ``r`` publishes "reached epoch e on
+  row s" by storing ``e`` into slot ``r`` of that row on every peer,
+* a device status word that kernels set when a bounded wait runs out (:meth:`PeerRuntime.check`).
+
+Creation is collective: every rank of the communicator has to construct buffers in the same order.
+(The reference has nothing comparable; its collectives are NCCL calls on torch storages.)
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
 from ..comm import Communicator
+from ..global_var import config
+from ..ops import _native
+
+_FLAG_ROWS = 256
+_runtimes: Dict[int, Optional["PeerRuntime"]] = {}
+
+
+class _CudaArray:
+    """Adapter exposing raw device memory through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+        self._owner = owner
+
+
+class SymmetricBuffer:
+    """``nbytes`` of device memory on every rank of ``comm``; ``ptrs[j]`` is rank j's buffer as seen from this process."""
+
+    def __init__(self, comm: Communicator, nbytes: int):
+        lib = _native.cuda_lib()
+        self.comm, self.nbytes = comm, int(nbytes)
+        local = ctypes.c_void_p()
+        _native.check(lib.bmt_symm_alloc(ctypes.c_int64(self.nbytes), ctypes.byref(local)), "symmetric allocation")
+        self.local_ptr = local.value
+        handle = (ctypes.c_ubyte * lib.bmt_ipc_handle_size())()
+        _native.check(lib.bmt_ipc_get_handle(ctypes.c_void_p(self.local_ptr), handle), "IPC handle export")
+        gathered: List = [None] * comm.size
+        dist.all_gather_object(gathered, bytes(handle), group=comm.group)
+        self.ptrs: List[int] = []
+        self._opened: List[int] = []
+        for j, raw in enumerate(gathered):
+            if j == comm.rank:
+                self.ptrs.append(self.local_ptr)
+                continue
+            buf = (ctypes.c_ubyte * len(raw)).from_buffer_copy(raw)
+            out = ctypes.c_void_p()
+            _native.check(lib.bmt_ipc_open_handle(buf, ctypes.byref(out)), "IPC handle import")
+            self.ptrs.append(out.value)
+            self._opened.append(out.value)
+        self._bytes = torch.as_tensor(_CudaArray(self.local_ptr, self.nbytes, self), device=config["device"])
+
+    def tensor(self, dtype: torch.dtype, numel: int, byte_offset: int = 0) -> torch.Tensor:
+        """A tensor that aliases the local buffer."""
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        return self._bytes[byte_offset:byte_offset + nbytes].view(dtype)
+
+    def ptr_table(self, byte_offset: int = 0):
+        return (ctypes.c_void_p * self.comm.size)(*[p + byte_offset for p in self.ptrs])
+
+    def close(self) -> None:
+        lib = _native.cuda_lib()
+        for p in self._opened:
+            lib.bmt_ipc_close(ctypes.c_void_p(p))
+        self._opened = []
+        if self.local_ptr:
+            self._bytes = None
+            lib.bmt_symm_free(ctypes.c_void_p(self.local_ptr))
+            self.local_ptr = 0
+
+
+class StreamWork:
+    """Handle whose ``wait()`` makes the current stream wait for an event (same contract as a c10d work object)."""
+
+    def __init__(self, event: torch.cuda.Event):
+        self.event = event
+
+    def wait(self) -> None:
+        torch.cuda.current_stream().wait_event(self.event)
+
+
+class PeerRuntime:
+    """Flags, status word and gradient staging slots of one communicator."""
+
+    def __init__(self, comm: Communicator):
+        self.comm = comm
+        dev = config["device"]
+        self.flags = SymmetricBuffer(comm, _FLAG_ROWS * comm.size * 4)
+        self.flag_ptrs = self.flags.ptr_table()
+        self.flag_table_dev = torch.tensor(list(self.flags.ptrs), dtype=torch.int64, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.overflow = torch.zeros(1, dtype=torch.uint8, device=dev)
+        self.epochs: Dict[int, int] = {}
+        self.rows: Dict[Tuple, int] = {}
+        self.slots: Dict[Tuple, SymmetricBuffer] = {}
+        self.timeout_s = float(os.environ.get("BMT_PEER_TIMEOUT", "10"))
+        self.stream = torch.cuda.Stream(priority=-1)
+
+    # ----------------------------------------------------------------- bookkeeping
+    def row(self, key: Tuple) -> int:
+        if key not in self.rows:
+            if len(self.rows) >= _FLAG_ROWS:
+                raise RuntimeError("out of flag rows")
+            self.rows[key] = len(self.rows)
+        return self.rows[key]
+
+    def next_epoch(self, row: int) -> int:
+        self.epochs[row] = self.epochs.get(row, 0) + 1
+        return self.epochs[row]
+
+    def slot(self, key: Tuple, nbytes: int) -> SymmetricBuffer:
+        """Symmetric staging buffer for ``key`` (allocated collectively on first use, regrown when too small)."""
+        buf = self.slots.get(key)
+        if buf is None or buf.nbytes < nbytes:
+            if buf is not None:
+                torch.cuda.synchronize()
+                self.comm.barrier()
+                buf.close()
+            buf = SymmetricBuffer(self.comm, nbytes)
+            self.slots[key] = buf
+        return buf
+
+    def check(self) -> None:
+        """Raise if a kernel's bounded wait on a peer ran out (reads the device status word: host sync)."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"peer wait timed out on communicator {self.comm.name} (code {code:#x}): "
+                               "a rank did not reach the matching step within the time limit")
+
+    # -------------------------------------------------------------------- kernels
+    def signal_wait(self, row: int, epoch: int, signal: bool, wait: bool) -> None:
+        lib = _native.cuda_lib()
+        _native.check(lib.bmt_symm_signal_wait(
+            ctypes.c_void_p(self.flag_table_dev.data_ptr()), ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank),
+            ctypes.c_int(row), ctypes.c_uint(epoch), ctypes.c_int(int(signal)), ctypes.c_int(int(wait)),
+            _native.ptr(self.status), ctypes.c_double(self.timeout_s), _native.stream_handle()), "peer signal/wait kernel")
+
+    def reduce_scatter(self, full: SymmetricBuffer, row: int, part: int, out: torch.Tensor, accumulate: bool,
+                       scale: float = 1.0) -> None:
+        """``out`` (+)= scale * sum over ranks of their ``full`` buffer, restricted to this rank's partition.
+
+        Runs on the current stream; the kernel itself tells the peers that this rank's buffer is complete and
+        waits (bounded) for theirs, adds in fp32 in rank order, and ORs inf/nan into ``self.overflow``.
+        """
+        lib = _native.cuda_lib()
+        epoch = self.next_epoch(row)
+        dt = {torch.float16: 0, torch.bfloat16: 1}[out.dtype]
+        _native.check(lib.bmt_fused_reduce_scatter(
+            full.ptr_table(), self.flag_ptrs, ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank), ctypes.c_int(row),
+            ctypes.c_uint(epoch), ctypes.c_int64(part), _native.ptr(out), ctypes.c_int(int(accumulate)), ctypes.c_float(scale),
+            ctypes.c_int(dt), _native.ptr(self.overflow), _native.ptr(self.status), ctypes.c_double(self.timeout_s),
+            _native.stream_handle()), "fused reduce-scatter kernel")
+
+
+def _same_node(comm: Communicator) -> bool:
+    return config["local_size"] == config["world_size"]
+
+
+def peer_runtime(comm: Communicator) -> Optional[PeerRuntime]:
+    """The runtime of ``comm``, created on first use (collective); None when peer memory cannot be used."""
+    key = id(comm)
+    if key in _runtimes:
+        return _runtimes[key]
+    ok = (config["device"] is not None and config["device"].type == "cuda" and 2 <= comm.size <= 8 and _same_node(comm)
+          and os.environ.get("BMT_PEER", "1") != "0")
+    rt = None
+    if ok:
+        try:
+            rt = PeerRuntime(comm)
+            good = 1
+        except Exception:  # IPC / peer mapping not available: every rank has to agree to fall back
+            good = 0
+        flag = torch.tensor([good], dtype=torch.int32, device=config["device"])
+        comm.all_reduce(flag, "min")
+        if int(flag.item()) == 0:
+            rt = None
+    _runtimes[key] = rt
+    return rt
 
 
 def peer_runtime_ready(comm: Communicator) -> bool:
-    return False
+    return peer_runtime(comm) is not None
+
+
+def reset() -> None:
+    """Forget every runtime (process-group teardown)."""
+    for rt in _runtimes.values():
+        if rt is not None:
+            for buf in rt.slots.values():
+                buf.close()
+            rt.flags.close()
+    _runtimes.clear()

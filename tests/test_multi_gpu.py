@@ -1,0 +1,73 @@
+"""Multi-GPU paths (2 B200s, one process per GPU, NCCL + peer memory).  Skipped with fewer than two GPUs."""
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(n):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def body_fused_rs(fused: bool):
+    """ZeRO-3 training of a small fp16 GPT on 2 ranks: gradients through the fused NVLink reduce-scatter must match
+    the NCCL path and a single-process fp32 oracle."""
+    import os
+
+    import bmtrain_b200 as bmt
+    from bmtrain_b200.parallel import symm
+    from oracle import OracleGPT
+    from bmtrain_b200.store import _save_to_rank0
+
+    rank, world = bmt.rank(), bmt.world_size()
+    cfg = dict(num_layers=3, vocab=2048, d=256, dh=64, h=4, dff=1024, max_distance=128)
+    torch.manual_seed(7)
+    ref = OracleGPT(cfg["num_layers"], cfg["vocab"], cfg["d"], cfg["dh"], cfg["h"], cfg["dff"], cfg["max_distance"], activation="gelu")
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.normal_(0, 0.02)
+        for blk in ref.transformers:
+            blk.ln_attn.weight.add_(1.0)
+            blk.ln_ff.weight.add_(1.0)
+        ref.layernorm.weight.add_(1.0)
+    model = bmt.models.GPT(cfg["num_layers"], cfg["vocab"], cfg["d"], cfg["dh"], cfg["h"], cfg["dff"], cfg["max_distance"],
+                           dtype=torch.float16, activation="gelu")
+    model.load_state_dict(ref.state_dict())
+    assert symm.peer_runtime(bmt.config["zero_comm"]) is not None or not fused
+    loss_fn = bmt.loss.FusedCrossEntropy()
+    g = torch.Generator().manual_seed(100 + rank)
+    ids = torch.randint(0, cfg["vocab"], (2, 65), generator=g).cuda()
+    all_ids = [torch.randint(0, cfg["vocab"], (2, 65), generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
+    pos = torch.arange(64, device="cuda")[None].expand(2, -1).contiguous()
+    mask = torch.ones(2, 64, dtype=torch.bool, device="cuda")
+    scale = 1024.0
+    for it in range(2):  # second pass: gradient accumulation on top of the first
+        logits = model(ids[:, :-1].contiguous(), pos, mask)
+        loss = loss_fn(logits.view(-1, logits.shape[-1]), ids[:, 1:].contiguous().view(-1))
+        (loss * scale / world).backward()
+    bmt.synchronize()
+    for rt in symm._runtimes.values():
+        if rt is not None:
+            rt.check()
+            assert int(rt.overflow.item()) == 0
+    # oracle gradients: mean over ranks, two accumulated passes
+    for r in range(world):
+        rid = all_ids[r]
+        lg = ref(rid[:, :-1], pos.cpu(), mask.cpu())
+        l = torch.nn.functional.cross_entropy(lg.view(-1, cfg["vocab"]), rid[:, 1:].reshape(-1))
+        (l * 2 / world).backward()
+    got = {r["name"]: r for r in bmt.inspect.inspect_model(model, "*")}
+    for name, p in ref.named_parameters():
+        key = name
+        ref_std = (p.grad * scale).std().item()
+        assert abs(got[key]["grad_std"] - ref_std) <= 0.03 * ref_std + 1e-4, (name, got[key]["grad_std"], ref_std)
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_zero3_fused_reduce_scatter_2gpu(fused, monkeypatch):
+    _need(2)
+    monkeypatch.setenv("BMT_PEER", "1" if fused else "0")
+    run_distributed("test_multi_gpu", "body_fused_rs", 2, device="cuda", fused=fused)
