@@ -147,6 +147,15 @@ int bmt_fused_reduce_scatter(const void* const* peers, void* const* peer_flags, 
 int bmt_symm_signal_wait(void* device_flag_table, int world, int rank, int slot, unsigned int epoch, int do_signal,
                          int do_wait, void* status_i32, double timeout_s, void* stream);
 
+// fused tensor-parallel operators: one kernel does the GEMM and the collective over peer memory
+int bmt_gemm_reduce_scatter(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, int done_row,
+                            unsigned int epoch, void* const* inbox_slots, const void* inbox_local, int64_t rows_per_rank,
+                            void* counter_u32, void* out, const void* bias, void* status_i32, double timeout_s, void* stream);
+int bmt_gemm_rs_grid(int64_t m, int64_t n, int64_t k, int b_major);
+int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, unsigned int epoch,
+                        const void* src, int64_t ld_src, int64_t rows, void* const* gathered, void* const* counters,
+                        int comm_ctas, void* status_i32, double timeout_s, void* stream);
+
 // number of kernel launches issued by this library since load (for launch accounting)
 int64_t bmt_launch_count(void);
 void bmt_count_launch(int n);

@@ -33,7 +33,7 @@ constexpr int BK = 64;          // 64 halves = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_STAGES = 8;
-constexpr uint32_t SMEM_BUDGET = 225 * 1024;
+constexpr uint32_t SMEM_BUDGET = 222 * 1024;  // tiles; header, alignment slack and the kernels' small static arrays fit below the 227 KiB limit
 
 __device__ int g_gemm_status = 0;  // 0 = fine; otherwise (code << 16) | blockIdx of the first CTA that gave up
 
@@ -306,9 +306,66 @@ __device__ __forceinline__ void umma_commit_2cta(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
-template <bool CTA2>
+// ---- fused collectives over peer memory (NVLink) ----------------------------------------------------------------
+// mode 1, GEMM -> reduce-scatter: the epilogue stores every output row straight into the inbox of the rank that owns
+//         the row (own rank: local memory, other ranks: P2P stores).  When all CTAs of this rank are done, the last one
+//         publishes "rank r delivered" to every peer; each CTA then waits (bounded) for all ranks and sums the inbox
+//         slots of its share of the local rows (+ bias) into the output.
+// mode 2, all-gather -> GEMM: the last `ag_ctas` CTAs do no math; they push this rank's rows of A into the gathered
+//         buffer of every rank (own first) in pieces and bump a per-128-row-block counter on the destination.  The
+//         TMA producers of the compute CTAs visit local row blocks first and wait (bounded) on the counter of a block
+//         before loading it, so the transfer overlaps the math block by block.
+// Flags: `flags[j]` is rank j's flag array, row `x` of it has one counter per rank.  free_row: "my inbox / gathered
+// buffer may be overwritten for this epoch" (published at kernel start); done_row: "my contributions are delivered".
+struct FusedComm {
+    int mode;                 // 0 none, 1 GEMM -> reduce-scatter, 2 all-gather -> GEMM
+    int world, rank;
+    unsigned int* flags[8];
+    int free_row, done_row;
+    unsigned int epoch;
+    int* status;
+    uint64_t limit_ns;
+    // mode 1
+    void* rs_inbox[8];        // destination j: base of slot `rank` inside j's inbox (rs_rows x N, pitch N)
+    const void* rs_inbox_local;  // this rank's inbox: world slots of rs_rows x N
+    int64_t rs_rows;          // rows per rank
+    unsigned int* rs_counter; // local, monotonic count of CTAs that finished their tiles
+    void* rs_out;             // rs_rows x N
+    const void* rs_bias;
+    // mode 2
+    int ag_ctas;
+    const void* ag_src;       // this rank's rows (ag_rows x K, pitch ag_ld_src)
+    int64_t ag_ld_src, ag_rows;
+    void* ag_dst[8];          // every rank's gathered buffer (world * ag_rows x K, pitch K)
+    unsigned int* ag_count[8];// every rank's per-row-block counters
+    int ag_piece_rows;        // rows copied per piece; BM / ag_piece_rows pieces per row block
+};
+
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded poll until *p >= target (counters only grow).
+__device__ __forceinline__ bool wait_counter(const unsigned int* p, unsigned int target, uint64_t limit_ns) {
+    uint64_t t0 = 0;
+    for (unsigned int spins = 0;; ++spins) {
+        if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+        if ((spins & 255u) == 255u) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_ns) return false;
+        }
+    }
+}
+
+template <bool CTA2, int FUSED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p,
+                    const FusedComm f) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // tiles first (1024-byte aligned for the 128-byte swizzle), bookkeeping after them
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -324,7 +381,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int k_blocks = (int)((p.K + BK - 1) / BK);
     const int64_t tiles_per_batch = (int64_t)p.m_blocks * p.n_blocks;   // m_blocks counts (BM * NCTA)-row tiles
     const int64_t num_tiles = tiles_per_batch * p.batch_inner * p.batch_outer;
-    const int64_t first_tile = blockIdx.x / NCTA, tile_step = gridDim.x / NCTA;
+    const int compute_ctas = FUSED == 2 ? (int)gridDim.x - f.ag_ctas : (int)gridDim.x;
+    const bool comm_cta = FUSED == 2 && (int)blockIdx.x >= compute_ctas;
+    const int64_t first_tile = comm_cta ? num_tiles : blockIdx.x / NCTA, tile_step = compute_ctas / NCTA;
+    const int blocks_per_rank = FUSED == 2 ? (int)(f.ag_rows / BM) : 0;
     const uint32_t tmem_cols = 2 * p.bn <= 32 ? 32 : 2 * p.bn <= 64 ? 64 : 2 * p.bn <= 128 ? 128 : 2 * p.bn <= 256 ? 256 : 512;
 
     if (threadIdx.x == 0) {
@@ -343,7 +403,62 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = hdr->tmem_base;
 
-    if (warp == 0) {
+    if (FUSED != 0 && blockIdx.x == 0 && threadIdx.x < (unsigned)f.world) {
+        // everything this rank did earlier on the stream is complete: peers may write into its buffers for this epoch
+        st_release_sys_u32(f.flags[threadIdx.x] + f.free_row * f.world + f.rank, f.epoch);
+    }
+
+    if (comm_cta) {
+        // ------------------------------------------------------------------ all-gather pusher (whole CTA)
+        const int n_pushers = f.ag_ctas, me = (int)blockIdx.x - compute_ctas;
+        const int pieces_per_block = BM / f.ag_piece_rows;
+        const int64_t row_bytes = p.K * 2;
+        const int64_t total_pieces = (int64_t)f.world * blocks_per_rank * pieces_per_block;
+        bool ok = true;
+        for (int64_t g = me; g < total_pieces && ok; g += n_pushers) {
+            // destination-major order starting with this rank itself, then the peers in ring order
+            const int dsti = (int)(g / ((int64_t)blocks_per_rank * pieces_per_block));
+            const int dst = (f.rank + dsti) % f.world;
+            const int64_t rem = g % ((int64_t)blocks_per_rank * pieces_per_block);
+            const int blk = (int)(rem / pieces_per_block), piece = (int)(rem % pieces_per_block);
+            if (dst != f.rank) {
+                __shared__ int free_ok;
+                if (threadIdx.x == 0) free_ok = wait_counter(f.flags[f.rank] + f.free_row * f.world + dst, f.epoch, f.limit_ns) ? 1 : 0;
+                __syncthreads();
+                if (!free_ok) { if (threadIdx.x == 0) { atomicCAS(f.status, 0, 0x300 | f.rank); atomicCAS(&g_gemm_status, 0, (5 << 16) | (blockIdx.x & 0xffff)); } ok = false; break; }
+            }
+            const int64_t src_row0 = (int64_t)blk * BM + (int64_t)piece * f.ag_piece_rows;
+            const int64_t dst_row0 = (int64_t)f.rank * f.ag_rows + src_row0;
+            const int64_t vec_per_row = row_bytes / 16;
+            const int64_t nvec = (int64_t)f.ag_piece_rows * vec_per_row;
+            const char* src = (const char*)f.ag_src;
+            char* dstp = (char*)f.ag_dst[dst];
+            for (int64_t v = threadIdx.x; v < nvec; v += NUM_THREADS * 4) {
+                int4 buf[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int64_t vv = v + (int64_t)u * NUM_THREADS;
+                    if (vv < nvec) {
+                        const int64_t r = vv / vec_per_row, cidx = vv % vec_per_row;
+                        buf[u] = *reinterpret_cast<const int4*>(src + (src_row0 + r) * f.ag_ld_src * 2 + cidx * 16);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int64_t vv = v + (int64_t)u * NUM_THREADS;
+                    if (vv < nvec) {
+                        const int64_t r = vv / vec_per_row, cidx = vv % vec_per_row;
+                        *reinterpret_cast<int4*>(dstp + (dst_row0 + r) * row_bytes + cidx * 16) = buf[u];
+                    }
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                __threadfence_system();
+                atomicAdd_system(f.ag_count[dst] + (f.rank * blocks_per_rank + blk), 1u);
+            }
+        }
+    } else if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one per CTA)
         if (lane == 0) {
             uint32_t it = 0;
@@ -351,7 +466,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
                 const int64_t batch = tile / tiles_per_batch;
                 const int64_t rem = tile % tiles_per_batch;
-                const int m_blk = (int)(rem % p.m_blocks), n_blk = (int)(rem / p.m_blocks);
+                int m_blk = (int)(rem % p.m_blocks);
+                const int n_blk = (int)(rem / p.m_blocks);
+                if (FUSED == 2) {
+                    // local row blocks first, then the peers' blocks in the order in which they are pushed
+                    m_blk = (m_blk + f.rank * blocks_per_rank) % p.m_blocks;
+                    const unsigned int target = f.epoch * (unsigned int)(BM / f.ag_piece_rows);
+                    if (!wait_counter(f.ag_count[f.rank] + m_blk, target, f.limit_ns)) {
+                        ok = false; atomicCAS(f.status, 0, 0x400 | f.rank); atomicCAS(&g_gemm_status, 0, (6 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break;
+                    }
+                    asm volatile("fence.proxy.async.global;" ::: "memory");  // the block was written with ordinary stores, TMA reads it
+                }
                 const int bi = (int)(batch % p.batch_inner), bo = (int)(batch / p.batch_inner);
                 const int bib = (int)(bi / p.b_inner_div);
                 const int m0 = m_blk * (BM * NCTA) + (int)rank * BM;            // this CTA's rows of A
@@ -436,11 +561,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         // ------------------------------------------------------------------ epilogue (warps 2..5), own 128 rows
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) are visible to this warp
         uint32_t tcount = 0;
+        uint32_t rs_free_mask = 0;     // destinations whose inbox is known to be free (mode 1)
         bool ok = true;
         for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++tcount) {
             const int64_t batch = tile / tiles_per_batch;
             const int64_t rem = tile % tiles_per_batch;
-            const int m_blk = (int)(rem % p.m_blocks), n_blk = (int)(rem / p.m_blocks);
+            int m_blk = (int)(rem % p.m_blocks);
+            const int n_blk = (int)(rem / p.m_blocks);
+            if (FUSED == 2) m_blk = (m_blk + f.rank * blocks_per_rank) % p.m_blocks;
             const int64_t bi = batch % p.batch_inner, bo = batch / p.batch_inner;
             const uint32_t acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1;
@@ -448,7 +576,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             tc_fence_after();
             const int64_t row = (int64_t)m_blk * (BM * NCTA) + rank * BM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
-            const int64_t coff = bi * p.c_bs0 + bo * p.c_bs1 + row * p.ldc;
+            int64_t coff = bi * p.c_bs0 + bo * p.c_bs1 + row * p.ldc;
+            char* cbase = (char*)p.c;
+            if (FUSED == 1 && row_ok) {
+                // route the row to the inbox of its owner; wait once per destination until that rank freed the inbox
+                const int owner = (int)(row / f.rs_rows);
+                if (owner != f.rank && !((rs_free_mask >> owner) & 1u)) {
+                    if (!wait_counter(f.flags[f.rank] + f.free_row * f.world + owner, f.epoch, f.limit_ns)) {
+                        atomicCAS(f.status, 0, 0x500 | f.rank); atomicCAS(&g_gemm_status, 0, (7 << 16) | (blockIdx.x & 0xffff));
+                    }
+                    rs_free_mask |= 1u << owner;
+                }
+                cbase = (char*)f.rs_inbox[owner];
+                coff = (row - (int64_t)owner * f.rs_rows) * p.N;
+            }
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * p.bn;
             const int64_t tile_end = (int64_t)(n_blk + 1) * p.bn;
             const int64_t col_end = tile_end < p.N ? tile_end : p.N;
@@ -458,9 +599,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 uint32_t r[32];
                 tmem_ld32(taddr + c0, r);
                 tmem_ld_wait();
-                if (p.c_dtype == BMT_DT_F16) epilogue_chunk<__half>(p, (__half*)p.c + coff, row, col0, col_end, r, row_ok);
-                else if (p.c_dtype == BMT_DT_BF16) epilogue_chunk<__nv_bfloat16>(p, (__nv_bfloat16*)p.c + coff, row, col0, col_end, r, row_ok);
-                else epilogue_chunk<float>(p, (float*)p.c + coff, row, col0, col_end, r, row_ok);
+                if (p.c_dtype == BMT_DT_F16) epilogue_chunk<__half>(p, (__half*)cbase + coff, row, col0, col_end, r, row_ok);
+                else if (p.c_dtype == BMT_DT_BF16) epilogue_chunk<__nv_bfloat16>(p, (__nv_bfloat16*)cbase + coff, row, col0, col_end, r, row_ok);
+                else epilogue_chunk<float>(p, (float*)cbase + coff, row, col0, col_end, r, row_ok);
             }
             tc_fence_before();
             __syncwarp();
@@ -482,6 +623,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (CTA2) cluster_sync();   // the peer may still be signalling barriers in this CTA's shared memory
     tc_fence_after();
     if (warp == 1) { if (CTA2) tmem_dealloc_2cta(tmem_base, tmem_cols); else tmem_dealloc(tmem_base, tmem_cols); }
+
+    if (FUSED == 1) {
+        // ---- reduce phase of GEMM -> reduce-scatter
+        __shared__ int rs_ok;
+        if (threadIdx.x == 0) {
+            __threadfence_system();  // this CTA's inbox stores (ordered before by the barrier above) become visible system-wide
+            const unsigned int done = atomicAdd(f.rs_counter, 1u) + 1u;
+            if (done == f.epoch * gridDim.x) {
+                // last CTA of this rank: everything is delivered
+                __threadfence_system();
+                for (int j = 0; j < f.world; ++j) st_release_sys_u32(f.flags[j] + f.done_row * f.world + f.rank, f.epoch);
+            }
+            bool ok = true;
+            for (int j = 0; j < f.world && ok; ++j) ok = wait_counter(f.flags[f.rank] + f.done_row * f.world + j, f.epoch, f.limit_ns);
+            if (!ok) { atomicCAS(f.status, 0, 0x600 | f.rank); atomicCAS(&g_gemm_status, 0, (8 << 16) | (blockIdx.x & 0xffff)); }
+            rs_ok = ok ? 1 : 0;
+        }
+        __syncthreads();
+        if (rs_ok) {
+            const int64_t nvec = f.rs_rows * p.N / 8;
+            const int64_t slot_elems = f.rs_rows * p.N;
+            for (int64_t v = (int64_t)blockIdx.x * NUM_THREADS + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * NUM_THREADS) {
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                const int64_t e = v * 8;
+                if (p.c_dtype == BMT_DT_F16) {
+                    for (int j = 0; j < f.world; ++j) { float t[8]; load8((const __half*)f.rs_inbox_local + j * slot_elems + e, t);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[i] += t[i]; }
+                    if (f.rs_bias) { float t[8]; load8((const __half*)f.rs_bias + e % p.N, t);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[i] += t[i]; }
+                    store8((__half*)f.rs_out + e, acc);
+                } else {
+                    for (int j = 0; j < f.world; ++j) { float t[8]; load8((const __nv_bfloat16*)f.rs_inbox_local + j * slot_elems + e, t);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[i] += t[i]; }
+                    if (f.rs_bias) { float t[8]; load8((const __nv_bfloat16*)f.rs_bias + e % p.N, t);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[i] += t[i]; }
+                    store8((__nv_bfloat16*)f.rs_out + e, acc);
+                }
+            }
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -587,7 +772,7 @@ TileChoice pick_tile(int64_t M, int64_t N, int64_t K, int64_t batches, bool b_mn
     return best;
 }
 
-int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
+int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fused = nullptr) {
     const int64_t m = g.m, n = g.n, k = g.k;
     const void* a = g.a; const void* b = g.b; void* c = g.c; const void* bias = g.bias;
     const int64_t lda = g.lda, ldb = g.ldb, ldc = g.ldc;
@@ -602,8 +787,10 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
         int dev = 0;
         BMT_CUDA_OK(cudaGetDevice(&dev));
         BMT_CUDA_OK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
-        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
-        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
     }
     static int force_bn = -1, force_cta2 = -2;
     if (force_bn < 0) { const char* e = getenv("BMT_GEMM_BN"); force_bn = e ? atoi(e) : 0; }
@@ -613,7 +800,10 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
     memset(&p, 0, sizeof(p));
     p.M = m; p.N = n; p.K = k;
     p.a_mn = a_major; p.b_mn = b_major;
-    TileChoice tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, force_bn, force_cta2);
+    const int comm_ctas = (fused && fused->mode == 2) ? fused->ag_ctas : 0;
+    if (fused) g_num_sms -= comm_ctas;  // tile choice for the CTAs that do math
+    TileChoice tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, force_bn, fused ? 0 : force_cta2);
+    if (fused) g_num_sms += comm_ctas;
     if (tc.bn == 0) tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, 0, -1);  // forced shape not applicable here
     if (tc.bn == 0) return -22;
     p.bn = tc.bn;
@@ -644,9 +834,20 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
 
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * batch_inner * batch_outer;
     const size_t smem = (size_t)p.stages * stage_bytes + sizeof(SharedHeader) + 1024;
+    FusedComm none;
+    memset(&none, 0, sizeof(none));
+    if (fused) {
+        if (tc.cta2) return -23;
+        const int compute = g_num_sms - comm_ctas;
+        const unsigned grid = (unsigned)(tiles < compute ? tiles : compute) + comm_ctas;
+        if (fused->mode == 1) gemm_tcgen05_kernel<false, 1><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, *fused);
+        else gemm_tcgen05_kernel<false, 2><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, *fused);
+        bmt_count_launch(1);
+        return (int)cudaGetLastError();
+    }
     if (!tc.cta2) {
         const unsigned grid = (unsigned)(tiles < g_num_sms ? tiles : g_num_sms);
-        gemm_tcgen05_kernel<false><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+        gemm_tcgen05_kernel<false, 0><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, none);
         bmt_count_launch(1);
         return (int)cudaGetLastError();
     }
@@ -661,7 +862,7 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<true>, ma, mb, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<true, 0>, ma, mb, p, none);
     bmt_count_launch(1);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
@@ -692,6 +893,58 @@ extern "C" int bmt_gemm_batched(int64_t m, int64_t n, int64_t k, const void* a, 
     g.c = c; g.ldc = ldc; g.c_dtype = c_dtype; g.c_bs0 = c_bs0; g.c_bs1 = c_bs1;
     g.batch_inner = batch_inner; g.batch_outer = batch_outer; g.b_inner_div = b_inner_div; g.alpha = alpha; g.ab_dtype = ab_dtype;
     return launch_gemm(g, (cudaStream_t)stream);
+}
+
+// GEMM -> reduce-scatter over the rows of C (see FusedComm mode 1).  `inbox_slots[j]`: where this rank's slot starts in rank
+// j's inbox; `grid_hint` receives the number of CTAs launched (the caller's counter advances by it per call).
+extern "C" int bmt_gemm_reduce_scatter(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, int done_row,
+                                       unsigned int epoch, void* const* inbox_slots, const void* inbox_local, int64_t rows_per_rank,
+                                       void* counter_u32, void* out, const void* bias, void* status_i32, double timeout_s,
+                                       void* stream) {
+    if (world < 2 || world > 8 || desc->m != rows_per_rank * world) return -40;
+    if (desc->n % 8 != 0) return -41;
+    FusedComm f;
+    memset(&f, 0, sizeof(f));
+    f.mode = 1; f.world = world; f.rank = rank; f.free_row = free_row; f.done_row = done_row; f.epoch = epoch;
+    f.status = (int*)status_i32; f.limit_ns = (uint64_t)(timeout_s * 1e9);
+    for (int j = 0; j < world; ++j) { f.flags[j] = (unsigned int*)flags[j]; f.rs_inbox[j] = inbox_slots[j]; }
+    f.rs_inbox_local = inbox_local; f.rs_rows = rows_per_rank; f.rs_counter = (unsigned int*)counter_u32; f.rs_out = out;
+    f.rs_bias = bias;
+    BmtGemmDesc g = *desc;
+    g.bias = nullptr; g.residual = nullptr; g.aux = nullptr; g.accumulate = 0; g.act = 0;
+    g.batch_inner = g.batch_outer = g.b_inner_div = 1;
+    g.c = (void*)inbox_local; g.ldc = desc->n; g.c_dtype = desc->ab_dtype;
+    return launch_gemm(g, (cudaStream_t)stream, &f);
+}
+
+// Number of CTAs the fused GEMM -> reduce-scatter launches for this problem (its completion counter advances by that much).
+extern "C" int bmt_gemm_rs_grid(int64_t m, int64_t n, int64_t k, int b_major) {
+    if (g_num_sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+        if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    }
+    const TileChoice tc = pick_tile(m, n, k, 1, b_major != 0, 0, 0);
+    const int64_t tiles = ((m + BM - 1) / BM) * ((n + tc.bn - 1) / tc.bn);
+    return (int)(tiles < g_num_sms ? tiles : g_num_sms);
+}
+
+// all-gather -> GEMM over the rows of A (see FusedComm mode 2).  The gathered matrix (world * rows x K, pitch K) lives in
+// `gathered[rank]`; desc->a must point at it and desc->m = world * rows.  rows must be a multiple of 128.
+extern "C" int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row,
+                                   unsigned int epoch, const void* src, int64_t ld_src, int64_t rows, void* const* gathered,
+                                   void* const* counters, int comm_ctas, void* status_i32, double timeout_s, void* stream) {
+    if (world < 2 || world > 8 || desc->m != rows * world || rows % BM != 0 || desc->a_major != 0) return -42;
+    if (desc->k % 8 != 0 || desc->lda != desc->k) return -43;
+    FusedComm f;
+    memset(&f, 0, sizeof(f));
+    f.mode = 2; f.world = world; f.rank = rank; f.free_row = free_row; f.epoch = epoch;
+    f.status = (int*)status_i32; f.limit_ns = (uint64_t)(timeout_s * 1e9);
+    for (int j = 0; j < world; ++j) { f.flags[j] = (unsigned int*)flags[j]; f.ag_dst[j] = gathered[j]; f.ag_count[j] = (unsigned int*)counters[j]; }
+    f.ag_ctas = comm_ctas; f.ag_src = src; f.ag_ld_src = ld_src; f.ag_rows = rows; f.ag_piece_rows = 16;
+    BmtGemmDesc g = *desc;
+    g.batch_inner = g.batch_outer = g.b_inner_div = 1;
+    return launch_gemm(g, (cudaStream_t)stream, &f);
 }
 
 // Status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out.  Reading clears it.

@@ -1,0 +1,120 @@
+"""Python side of the fused tensor-parallel kernels (``csrc/gemm_sm100.cu``, FusedComm modes 1 and 2).
+
+Buffers that peers write into (the reduce-scatter inbox, the gathered activation matrix and its arrival counters) are
+symmetric buffers of the communicator's :class:`~bmtrain_b200.parallel.symm.PeerRuntime`, keyed by problem shape and
+used as a ring of two, so that a call may start while the previous result is still being consumed.  Each call takes
+one epoch on its flag rows; "free" (this rank's buffer may be overwritten) is published by the kernel when it starts,
+i.e. after everything queued earlier on the stream has finished.
+
+A gathered matrix returned by :func:`ag_gemm` aliases ring memory: it is valid until the second following call with
+the same shape.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..comm import Communicator
+from ..ops import _native
+from ..ops.gpt_block import _i64, _int, _f32, _c_void_p
+from . import symm
+
+_COMM_CTAS = 16
+_ring: Dict[Tuple, int] = {}
+_counters: Dict[Tuple, torch.Tensor] = {}
+
+
+class _GemmDesc(ctypes.Structure):
+    _fields_ = [
+        ("m", _i64), ("n", _i64), ("k", _i64),
+        ("a", _c_void_p), ("lda", _i64), ("a_major", _int), ("a_bs0", _i64), ("a_bs1", _i64),
+        ("b", _c_void_p), ("ldb", _i64), ("b_major", _int), ("b_bs0", _i64), ("b_bs1", _i64),
+        ("c", _c_void_p), ("ldc", _i64), ("c_dtype", _int), ("c_bs0", _i64), ("c_bs1", _i64),
+        ("batch_inner", _i64), ("batch_outer", _i64), ("b_inner_div", _i64),
+        ("bias", _c_void_p), ("act", _int), ("accumulate", _int), ("alpha", _f32), ("ab_dtype", _int),
+        ("residual", _c_void_p), ("ldr", _i64), ("aux", _c_void_p), ("ld_aux", _i64), ("aux_mode", _int),
+    ]
+
+
+_DT = {torch.float16: 0, torch.bfloat16: 1}
+
+
+def _next_parity(key: Tuple) -> int:
+    _ring[key] = (_ring.get(key, -1) + 1) % 2
+    return _ring[key]
+
+
+def _tma_ok(t: torch.Tensor) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def gemm_rs(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], comm: Communicator, b_is_kn: bool) -> Optional[torch.Tensor]:
+    """``reduce_scatter_rows(x @ W^T)`` (+ bias) in one kernel; None when the shapes do not fit the fused kernel."""
+    rt = symm.peer_runtime(comm)
+    M, K = x.shape
+    N = weight.shape[1] if b_is_kn else weight.shape[0]
+    W = comm.size
+    if rt is None or x.dtype not in _DT or M % W or N % 8 or K % 8 or not _tma_ok(x) or not _tma_ok(weight):
+        return None
+    lib = _native.cuda_lib()
+    rows = M // W
+    es = x.element_size()
+    base = ("rs", M, N, K, x.dtype, b_is_kn)
+    key = base + (_next_parity(base),)
+    inbox = rt.slot(key, W * rows * N * es)
+    free_row, done_row = rt.row(key + ("free",)), rt.row(key + ("done",))
+    epoch = rt.next_epoch(free_row)
+    rt.epochs[done_row] = epoch
+    if key not in _counters:
+        _counters[key] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    out = torch.empty(rows, N, dtype=x.dtype, device=x.device)
+    d = _GemmDesc()
+    d.m, d.n, d.k = M, N, K
+    d.a, d.lda, d.a_major = x.data_ptr(), x.stride(0), 0
+    d.b, d.ldb, d.b_major = weight.data_ptr(), weight.stride(0), 1 if b_is_kn else 0
+    d.ab_dtype, d.alpha = _DT[x.dtype], 1.0
+    slots = (ctypes.c_void_p * W)(*[p + comm.rank * rows * N * es for p in inbox.ptrs])
+    _native.check(lib.bmt_gemm_reduce_scatter(
+        ctypes.byref(d), ctypes.c_int(W), ctypes.c_int(comm.rank), rt.flag_ptrs, ctypes.c_int(free_row), ctypes.c_int(done_row),
+        ctypes.c_uint(epoch), slots, ctypes.c_void_p(inbox.local_ptr), ctypes.c_int64(rows), _native.ptr(_counters[key]),
+        _native.ptr(out), _native.ptr(bias), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s), _native.stream_handle()),
+        "fused GEMM -> reduce-scatter kernel")
+    return out
+
+
+def ag_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], comm: Communicator, b_is_kn: bool,
+            return_gathered: bool):
+    """``all_gather_rows(x_local) @ W^T`` in one kernel; None when the shapes do not fit the fused kernel."""
+    rt = symm.peer_runtime(comm)
+    m, K = x_local.shape
+    N = weight.shape[1] if b_is_kn else weight.shape[0]
+    W = comm.size
+    if (rt is None or x_local.dtype not in _DT or m % 128 or K % 8 or N % 8 or x_local.stride(1) != 1
+            or x_local.stride(0) % 8 or x_local.data_ptr() % 16 or not _tma_ok(weight)):
+        return None
+    lib = _native.cuda_lib()
+    es = x_local.element_size()
+    base = ("ag", m, K, x_local.dtype)
+    key = base + (_next_parity(base),)
+    gathered = rt.slot(key, W * m * K * es)
+    counters = rt.slot(key + ("cnt",), max(256, W * (m // 128) * 4))
+    free_row = rt.row(key + ("free",))
+    epoch = rt.next_epoch(free_row)
+    out = torch.empty(W * m, N, dtype=x_local.dtype, device=x_local.device)
+    d = _GemmDesc()
+    d.m, d.n, d.k = W * m, N, K
+    d.a, d.lda, d.a_major = gathered.local_ptr, K, 0
+    d.b, d.ldb, d.b_major = weight.data_ptr(), weight.stride(0), 1 if b_is_kn else 0
+    d.c, d.ldc, d.c_dtype = out.data_ptr(), N, _DT[x_local.dtype]
+    d.bias = None if bias is None else bias.data_ptr()
+    d.ab_dtype, d.alpha = _DT[x_local.dtype], 1.0
+    _native.check(lib.bmt_all_gather_gemm(
+        ctypes.byref(d), ctypes.c_int(W), ctypes.c_int(comm.rank), rt.flag_ptrs, ctypes.c_int(free_row), ctypes.c_uint(epoch),
+        _native.ptr(x_local), ctypes.c_int64(x_local.stride(0)), ctypes.c_int64(m), gathered.ptr_table(), counters.ptr_table(),
+        ctypes.c_int(_COMM_CTAS), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s), _native.stream_handle()),
+        "fused all-gather -> GEMM kernel")
+    if return_gathered:
+        return out, gathered.tensor(x_local.dtype, W * m * K).view(W * m, K)
+    return out

@@ -34,7 +34,9 @@ def all_gather_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[
     if _fused_available(x_local, comm):
         from . import fused_ops
 
-        return fused_ops.ag_gemm(x_local, weight, bias, comm, b_is_kn, return_gathered)
+        res = fused_ops.ag_gemm(x_local, weight, bias, comm, b_is_kn, return_gathered)
+        if res is not None:
+            return res
     x_local = x_local.contiguous()
     x_all = torch.empty((comm.size * x_local.shape[0], x_local.shape[1]), dtype=x_local.dtype, device=x_local.device)
     comm.all_gather_into(x_all, x_local)
@@ -48,7 +50,9 @@ def gemm_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, bias: Optional[to
     if _fused_available(x, comm):
         from . import fused_ops
 
-        return fused_ops.gemm_rs(x, weight, bias, comm, b_is_kn)
+        res = fused_ops.gemm_rs(x, weight, bias, comm, b_is_kn)
+        if res is not None:
+            return res
     full = _gemm.gemm_nn(x, weight) if b_is_kn else _gemm.gemm_nt(x, weight)
     out = torch.empty((full.shape[0] // comm.size, full.shape[1]), dtype=full.dtype, device=full.device)
     comm.reduce_scatter_into(out, full, "sum")

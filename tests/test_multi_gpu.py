@@ -71,3 +71,57 @@ def test_zero3_fused_reduce_scatter_2gpu(fused, monkeypatch):
     _need(2)
     monkeypatch.setenv("BMT_PEER", "1" if fused else "0")
     run_distributed("test_multi_gpu", "body_fused_rs", 2, device="cuda", fused=fused)
+
+
+def body_tp_fused():
+    """Fused all-gather->GEMM and GEMM->reduce-scatter against NCCL + plain GEMM on the same data (2 ranks)."""
+    import bmtrain_b200 as bmt
+    from bmtrain_b200.ops import gemm as G
+    from bmtrain_b200.parallel import fused_ops, symm
+
+    comm = bmt.config["comm"]
+    rank, W = comm.rank, comm.size
+    rt = symm.peer_runtime(comm)
+    assert rt is not None
+    for dtype in (torch.float16, torch.bfloat16):
+        tol = 2e-2 if dtype == torch.bfloat16 else 3e-3
+        for (m, K, N) in ((256, 512, 1024), (1024, 2560, 3840), (128, 8192, 2560)):
+            for rep in range(3):  # ring of two buffers: the third call reuses the first slot
+                torch.manual_seed(1000 * rep + rank)
+                x_local = torch.randn(m, K, device="cuda", dtype=dtype)
+                torch.manual_seed(5)
+                w = (torch.randn(N, K, device="cuda") * 0.05).to(dtype)
+                bias = torch.randn(N, device="cuda").to(dtype)
+                x_all = torch.empty(W * m, K, device="cuda", dtype=dtype)
+                comm.all_gather_into(x_all, x_local)
+                ref = G.gemm_nt(x_all, w, bias).float()
+                got = fused_ops.ag_gemm(x_local, w, bias, comm, False, True)
+                assert got is not None
+                out, gathered = got
+                assert torch.equal(gathered, x_all)
+                assert ((out.float() - ref).abs().max() / ref.abs().max()).item() < tol
+                # GEMM -> reduce-scatter: every rank holds different activations, same weight
+                xs = torch.randn(W * m, K, device="cuda", dtype=dtype)
+                full = G.gemm_nt(xs, w).float()
+                comm.all_reduce(full, "sum")
+                ref_rs = full[rank * m:(rank + 1) * m] + bias.float()
+                got_rs = fused_ops.gemm_rs(xs, w, bias, comm, False)
+                assert got_rs is not None
+                assert ((got_rs.float() - ref_rs).abs().max() / ref_rs.abs().max()).item() < tol, (m, K, N, rep)
+                # K x N weight layout (dgrad form)
+                wkn = (torch.randn(K, N, device="cuda") * 0.05).to(dtype) if rank >= 0 else None
+                torch.manual_seed(6)
+                wkn = (torch.randn(K, N, device="cuda") * 0.05).to(dtype)
+                full = G.gemm_nn(xs, wkn).float()
+                comm.all_reduce(full, "sum")
+                got_kn = fused_ops.gemm_rs(xs, wkn, None, comm, True)
+                assert ((got_kn.float() - full[rank * m:(rank + 1) * m]).abs().max() / full.abs().max()).item() < tol
+    torch.cuda.synchronize()
+    rt.check()
+    from bmtrain_b200.ops import _native
+    assert _native.cuda_lib().bmt_gemm_status() == 0
+
+
+def test_tp_fused_kernels_2gpu():
+    _need(2)
+    run_distributed("test_multi_gpu", "body_tp_fused", 2, device="cuda")
