@@ -8,6 +8,24 @@ from ..parameter import DistributedParameter
 from .parallel_linear_func import OpParallelLinear, ReduceType
 
 
+class _AddReplicatedBias(torch.autograd.Function):
+    """``out + bias`` where ``out`` holds only this rank's share of the tokens but ``bias`` is replicated over the
+    tensor-parallel group: the bias gradient is the sum over *all* tokens, so it is all-reduced over the group
+    (the reference leaves the per-rank partial sums: ``bmtrain/nn/row_parallel_linear.py:81-82``)."""
+
+    @staticmethod
+    def forward(ctx, out, bias):
+        return out + bias
+
+    @staticmethod
+    def backward(ctx, grad):
+        gb = grad.reshape(-1, grad.shape[-1]).sum(0)
+        comm = config["tp_comm"]
+        if comm is not None:
+            comm.all_reduce(gb, "sum")
+        return grad, gb
+
+
 class RowParallelLinear(DistributedModule):
     """``y = reduce(x_r W_r^T) + b`` with ``W_r`` = columns ``[r*in/tp, (r+1)*in/tp)`` of the full weight.
 
@@ -43,7 +61,10 @@ class RowParallelLinear(DistributedModule):
         out = OpParallelLinear.apply(input, self.weight, None, gather_input, False, self.split_input,
                                      reduce_type, self.async_chunks)
         if self.bias is not None:
-            out = out + self.bias
+            if config["tp_size"] > 1 and not self.all_reduce_output:
+                out = _AddReplicatedBias.apply(out, self.bias)
+            else:
+                out = out + self.bias
         return out
 
     def extra_repr(self) -> str:
