@@ -22,7 +22,8 @@ def _partition_bounds(p):
     owner = getattr(p, "_bmt_bounds", None)
     if owner is not None:
         return owner
-    if getattr(p, "_start_partition", None) is not None and not getattr(p, "_in_block", False):
+    if getattr(p, "_start_partition", None) is not None:
+        # stand-alone parameters and parameters inside a block alike: the local slice of the flattened full tensor
         return (p._start_partition, p._end_partition)
     return None
 
