@@ -169,7 +169,7 @@ class _BlockFunction(torch.autograd.Function):
         ctx.arg_spec = arg_spec
         ctx.req = [t.requires_grad for t in tensors]
         ctx.checkpoint = block._use_checkpoint and not debug.get("_inspect_tensor", False)
-        block._enter_forward()
+        block._enter_forward(_fill(arg_spec, tensors))
         if ctx.checkpoint:
             ctx.rng = _rng_state()
             ctx.inputs = tensors
@@ -193,7 +193,7 @@ class _BlockFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grad_outs):
         block: Block = ctx.block
-        block._enter_backward()
+        block._enter_backward(_fill(ctx.arg_spec, ctx.inputs) if ctx.checkpoint else None)
         if ctx.checkpoint:
             detached = [t.detach().requires_grad_(r) for t, r in zip(ctx.inputs, ctx.req)]
             with _restore_rng(ctx.rng), torch.enable_grad():
@@ -368,7 +368,65 @@ class Block(torch.nn.Module):
             b.full = torch.empty(b.total, dtype=b.dtype, device=b.storage.device)
             b.work = b.comm.all_gather_into(b.full, b.storage.data, async_op=True)
 
-    def _ensure_gathered(self) -> None:
+    def _try_deferred_gather(self, args) -> bool:
+        """ZeRO gather for a block nobody prefetched, when the inner module can pull its first GEMM's weight itself.
+
+        The small parameters (norms, biases) and then the remaining big ones are pushed to all ranks by two kernels on the
+        peer stream; the first GEMM's weight is left to the module, whose fused kernel gathers it while multiplying
+        (``parallel/fused_ops.zero_gather_gemm``).  Returns False when the conditions are not met.
+        """
+        import os
+
+        mod = self._module
+        name = getattr(mod, "_bmt_first_gemm", None)
+        if name is None or os.environ.get("BMT_FUSED_GATHER", "1") == "0" or self._ref_block is not None:
+            return False
+        if any(b.full is not None for b in self._buckets.values()) or not mod._bmt_can_fuse_first_gemm(*args):
+            return False
+        target = [(b, s) for b in self._buckets.values() for s in b.slots if s.name == name]
+        if not target:
+            return False
+        b, slot = target[0]
+        rt = self._peer_runtime(b)
+        if rt is None or len(slot.shape) != 2 or slot.shape[1] % 8 or any(s.numel % 8 for s in b.slots):
+            return False
+        es = b.storage.element_size()
+        key = ("zg", self._slot_parity, b.key, b.total, id(self) if self._mode == "PIPE" else 0)
+        first_use = key not in rt.slots
+        buf = rt.slot(key, b.total * es)
+        free_row, done_a, done_b = rt.row(key + ("free",)), rt.row(key + ("doneA",)), rt.row(key + ("doneB",))
+        if first_use:
+            rt.signal_wait(free_row, 1, signal=True, wait=False)
+        epoch = rt.next_epoch(free_row)
+        small, big = [], []
+        for s in b.slots:
+            lo, hi = max(s.offset, b.begin), min(s.offset + s.numel, b.end)
+            if hi <= lo or s is slot:
+                continue
+            rng = (b.storage.data_ptr() + (lo - b.begin) * es, lo * es, (hi - lo) * es)
+            (small if s.numel <= 65536 else big).append(rng)
+        if len(small) > 16 or len(big) > 16:
+            return False
+        cur = torch.cuda.current_stream()
+        rt.stream.wait_stream(cur)
+        with torch.cuda.stream(rt.stream):
+            rt.push_ranges(buf, small, free_row, done_a, epoch, key + ("A",))
+            rt.signal_wait(done_a, epoch, signal=False, wait=True)
+            ev_small = torch.cuda.Event()
+            ev_small.record(rt.stream)
+            rt.push_ranges(buf, big, free_row, done_b, epoch, key + ("B",))
+            rt.signal_wait(done_b, epoch, signal=False, wait=True)
+            ev_rest = torch.cuda.Event()
+            ev_rest.record(rt.stream)
+        b.full = buf.tensor(b.dtype, b.total)
+        b.full_sym = (rt, free_row, epoch)
+        mod._bmt_deferred_gather = dict(rt=rt, buf=buf, bucket=b, slot=slot, epoch=epoch, key=key, free_row=free_row,
+                                        ev_small=ev_small, ev_rest=ev_rest)
+        return True
+
+    def _ensure_gathered(self, args=None) -> None:
+        if args is not None:
+            self._try_deferred_gather(args)
         self._begin_gather()
         for b in self._buckets.values():
             if b.work is not None:
@@ -387,8 +445,16 @@ class Block(torch.nn.Module):
     def _release_params(self) -> None:
         self._point_to_local()
         for b in self._buckets.values():
+            sym = getattr(b, "full_sym", None)
+            if sym is not None and b.full is not None:
+                # the gathered copy lives in a peer-visible ring slot: tell the peers it may be overwritten by the next gather
+                rt, free_row, epoch = sym
+                rt.signal_wait(free_row, epoch + 1, signal=True, wait=False)
+                b.full_sym = None
             b.full = None
             b.work = None
+        if getattr(self._module, "_bmt_deferred_gather", None) is not None:
+            self._module._bmt_deferred_gather = None
         self._resident = False
 
     def _peer_runtime(self, b: _Bucket):
@@ -482,8 +548,8 @@ class Block(torch.nn.Module):
                     hook(holder, None if accumulate else work)
 
     # ------------------------------------------------------------- scheduling
-    def _enter_forward(self) -> None:
-        self._ensure_gathered()
+    def _enter_forward(self, args=None) -> None:
+        self._ensure_gathered(args)
         nxt = self.next_module()
         if nxt is not None and nxt._mode != "PIPE":
             nxt._begin_gather()
@@ -498,8 +564,8 @@ class Block(torch.nn.Module):
         else:
             self._release_params()
 
-    def _enter_backward(self) -> None:
-        self._ensure_gathered()
+    def _enter_backward(self, args=None) -> None:
+        self._ensure_gathered(args)
         self._prepare_grads()
         pre = self.pre_module()
         if pre is not None and pre._mode != "PIPE" and pre._zero_level == 3:

@@ -132,6 +132,7 @@ typedef struct {
 } BmtGptBlockGrad;
 
 int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream);
+int bmt_gpt_block_forward_steps(const BmtGptBlock* blk, int first_step, int last_step, void* stream);
 int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockGrad* g, void* stream);
 
 // ---- peer memory (one NVLink domain) ------------------------------------------------------------------------------
@@ -144,6 +145,9 @@ int bmt_ipc_handle_size(void);
 int bmt_fused_reduce_scatter(const void* const* peers, void* const* peer_flags, int world, int rank, int slot,
                              unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
                              void* overflow_u8, void* status_i32, double timeout_s, void* stream);
+int bmt_push_ranges(const void* const* src, const int64_t* dst_off, const int64_t* nbytes, int nranges, void* const* dst,
+                    void* const* peer_flags, int world, int rank, int free_row, int done_row, unsigned int epoch,
+                    void* counter_u32, void* status_i32, double timeout_s, int grid, void* stream);
 int bmt_symm_signal_wait(void* device_flag_table, int world, int rank, int slot, unsigned int epoch, int do_signal,
                          int do_wait, void* status_i32, double timeout_s, void* stream);
 
@@ -155,6 +159,11 @@ int bmt_gemm_rs_grid(int64_t m, int64_t n, int64_t k, int b_major);
 int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, unsigned int epoch,
                         const void* src, int64_t ld_src, int64_t rows, void* const* gathered, void* const* counters,
                         int comm_ctas, void* status_i32, double timeout_s, void* stream);
+
+int bmt_zero_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, unsigned int epoch,
+                         const void* src, int64_t first, int64_t count, void* const* weight_on_rank, void* const* counters,
+                         const void* expected_u32, int comm_ctas, void* status_i32, double timeout_s, void* stream);
+int bmt_zero_gather_expected(int64_t n, int64_t k, int world, const int64_t* first, const int64_t* count, unsigned int* out);
 
 // number of kernel launches issued by this library since load (for launch accounting)
 int64_t bmt_launch_count(void);

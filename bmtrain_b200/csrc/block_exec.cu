@@ -43,21 +43,25 @@ char* off(void* p, int64_t elems) { return (char*)p + elems * 2; }
 
 }  // namespace
 
-extern "C" int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream) {
+// Steps [first_step, last_step] of the forward (1 = LN1, 2 = QKV projection, 3..5 attention core, 6 = output
+// projection + residual, 7 = LN2, 8 = first FFN GEMM, 9 = second FFN GEMM + residual).  Running a sub-range lets the
+// caller put its own QKV GEMM (fused with the parameter gather) or a stream wait between the steps.
+extern "C" int bmt_gpt_block_forward_steps(const BmtGptBlock* blk, int first_step, int last_step, void* stream) {
     const BmtGptBlock& k = *blk;
     const Dims q = dims_of(k);
     const int dt = k.dtype;
+#define STEP(n) if (first_step <= (n) && (n) <= last_step)
     // 1. LN1
-    RUN(bmt_norm_fwd(q.T, q.d, k.x, k.ln1_w, k.ln1_b, k.eps, 0, dt, k.ln1, k.stats1, stream));
+    STEP(1) RUN(bmt_norm_fwd(q.T, q.d, k.x, k.ln1_w, k.ln1_b, k.eps, 0, dt, k.ln1, k.stats1, stream));
     // 2. fused QKV projection (+ bias): qkv laid out (token, head, {q,k,v}, d_head)
-    {
+    STEP(2) {
         BmtGemmDesc g = plain(q.T, 3 * q.hd, q.d, k.ln1, q.d, 0, k.qkv_w, q.d, 0, k.qkv, 3 * q.hd, dt);
         g.bias = k.qkv_b;
         RUN(bmt_gemm_ex(&g, stream));
     }
     const int64_t tok = 3 * q.hd, head = 3 * q.dh;
     // 3. scores = q k^T / sqrt(d_head)   -> probs (b, h, s, ld)
-    {
+    STEP(3) {
         BmtGemmDesc g = plain(q.s, q.s, q.dh, k.qkv, tok, 0, off(k.qkv, q.dh), tok, 0, k.probs, k.probs_ld, dt);
         g.a_bs0 = head; g.a_bs1 = q.s * tok; g.b_bs0 = head; g.b_bs1 = q.s * tok;
         g.c_bs0 = q.s * k.probs_ld; g.c_bs1 = q.h * q.s * k.probs_ld;
@@ -65,9 +69,9 @@ extern "C" int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream) {
         RUN(bmt_gemm_ex(&g, stream));
     }
     // 4. masked softmax in place
-    RUN(bmt_masked_softmax(q.b, q.h, q.s, q.s, k.probs_ld, k.probs, dt, k.causal, k.mask, nullptr, stream));
+    STEP(4) RUN(bmt_masked_softmax(q.b, q.h, q.s, q.s, k.probs_ld, k.probs, dt, k.causal, k.mask, nullptr, stream));
     // 5. ctx = probs v  -> (token, head, d_head)
-    {
+    STEP(5) {
         BmtGemmDesc g = plain(q.s, q.dh, q.s, k.probs, k.probs_ld, 0, off(k.qkv, 2 * q.dh), tok, 1, k.ctx, q.hd, dt);
         g.a_bs0 = q.s * k.probs_ld; g.a_bs1 = q.h * q.s * k.probs_ld; g.b_bs0 = head; g.b_bs1 = q.s * tok;
         g.c_bs0 = q.dh; g.c_bs1 = q.s * q.hd;
@@ -75,28 +79,31 @@ extern "C" int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream) {
         RUN(bmt_gemm_ex(&g, stream));
     }
     // 6. h1 = ctx W_o^T + b_o + x
-    {
+    STEP(6) {
         BmtGemmDesc g = plain(q.T, q.d, q.hd, k.ctx, q.hd, 0, k.out_w, q.hd, 0, k.h1, q.d, dt);
         g.bias = k.out_b; g.residual = k.x; g.ldr = q.d;
         RUN(bmt_gemm_ex(&g, stream));
     }
     // 7. LN2
-    RUN(bmt_norm_fwd(q.T, q.d, k.h1, k.ln2_w, k.ln2_b, k.eps, 0, dt, k.ln2, k.stats2, stream));
+    STEP(7) RUN(bmt_norm_fwd(q.T, q.d, k.h1, k.ln2_w, k.ln2_b, k.eps, 0, dt, k.ln2, k.stats2, stream));
     // 8. ff = act(ln2 W_1^T + b_1)
-    {
+    STEP(8) {
         BmtGemmDesc g = plain(q.T, q.dff, q.d, k.ln2, q.d, 0, k.fc1_w, q.d, 0, k.act == 2 ? k.pre : k.ff, q.dff, dt);
         g.bias = k.fc1_b; g.act = k.act == 1 ? 1 : 0;
         RUN(bmt_gemm_ex(&g, stream));
         if (k.act == 2) RUN(bmt_gelu_fwd(q.T * q.dff, k.pre, dt, k.ff, stream));
     }
     // 9. y = ff W_2^T + b_2 + h1
-    {
+    STEP(9) {
         BmtGemmDesc g = plain(q.T, q.d, q.dff, k.ff, q.dff, 0, k.fc2_w, q.dff, 0, k.y, q.d, dt);
         g.bias = k.fc2_b; g.residual = k.h1; g.ldr = q.d;
         RUN(bmt_gemm_ex(&g, stream));
     }
+#undef STEP
     return 0;
 }
+
+extern "C" int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream) { return bmt_gpt_block_forward_steps(blk, 1, 9, stream); }
 
 extern "C" int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockGrad* grad, void* stream) {
     const BmtGptBlock& k = *blk;

@@ -339,7 +339,16 @@ struct FusedComm {
     void* ag_dst[8];          // every rank's gathered buffer (world * ag_rows x K, pitch K)
     unsigned int* ag_count[8];// every rank's per-row-block counters
     int ag_piece_rows;        // rows copied per piece; BM / ag_piece_rows pieces per row block
+    // mode 3 (ZeRO weight gather -> GEMM): the B operand (N x K, rows contiguous) is cut over the ranks as a flat element
+    // range; every rank pushes its part to all ranks in pieces and the TMA producer waits for the 128-row chunks it needs
+    const char* bg_src;       // this rank's part (local shard memory)
+    int64_t bg_first, bg_count;   // flat element range [bg_first, bg_first + bg_count) of the N*K weight elements
+    void* bg_dst[8];          // start of the weight inside every rank's gathered buffer
+    unsigned int* bg_cnt[8];  // every rank's per-chunk counters (chunk = 128 rows)
+    const unsigned int* bg_expected;  // pieces a chunk receives in total, per chunk
+    int bg_first_block;       // n-block at which this rank's own rows start (tile order is rotated to begin there)
 };
+constexpr int64_t BG_PIECE = 8192;  // elements per pushed piece (16 KiB)
 
 __device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -381,8 +390,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int k_blocks = (int)((p.K + BK - 1) / BK);
     const int64_t tiles_per_batch = (int64_t)p.m_blocks * p.n_blocks;   // m_blocks counts (BM * NCTA)-row tiles
     const int64_t num_tiles = tiles_per_batch * p.batch_inner * p.batch_outer;
-    const int compute_ctas = FUSED == 2 ? (int)gridDim.x - f.ag_ctas : (int)gridDim.x;
-    const bool comm_cta = FUSED == 2 && (int)blockIdx.x >= compute_ctas;
+    const int compute_ctas = (FUSED == 2 || FUSED == 3) ? (int)gridDim.x - f.ag_ctas : (int)gridDim.x;
+    const bool comm_cta = (FUSED == 2 || FUSED == 3) && (int)blockIdx.x >= compute_ctas;
     const int64_t first_tile = comm_cta ? num_tiles : blockIdx.x / NCTA, tile_step = compute_ctas / NCTA;
     const int blocks_per_rank = FUSED == 2 ? (int)(f.ag_rows / BM) : 0;
     const uint32_t tmem_cols = 2 * p.bn <= 32 ? 32 : 2 * p.bn <= 64 ? 64 : 2 * p.bn <= 128 ? 128 : 2 * p.bn <= 256 ? 256 : 512;
@@ -408,7 +417,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         st_release_sys_u32(f.flags[threadIdx.x] + f.free_row * f.world + f.rank, f.epoch);
     }
 
-    if (comm_cta) {
+    if (comm_cta && FUSED == 3) {
+        // ------------------------------------------------------------------ weight pusher (whole CTA)
+        const int n_pushers = f.ag_ctas, me = (int)blockIdx.x - compute_ctas;
+        const int64_t CK = (int64_t)BM * p.K;                       // elements per 128-row chunk
+        const int64_t lo_all = f.bg_first, hi_all = f.bg_first + f.bg_count;
+        bool ok = f.bg_count > 0;
+        for (int di = 0; di < f.world && ok; ++di) {
+            const int dst = (f.rank + di) % f.world;
+            if (dst != f.rank) {
+                __shared__ int free_ok3;
+                if (threadIdx.x == 0) free_ok3 = wait_counter(f.flags[f.rank] + f.free_row * f.world + dst, f.epoch, f.limit_ns) ? 1 : 0;
+                __syncthreads();
+                if (!free_ok3) { if (threadIdx.x == 0) { atomicCAS(f.status, 0, 0x800 | f.rank); atomicCAS(&g_gemm_status, 0, (9 << 16) | (blockIdx.x & 0xffff)); } ok = false; break; }
+            }
+            int64_t g = 0;
+            for (int64_t c = lo_all / CK; c * CK < hi_all; ++c) {
+                const int64_t lo = lo_all > c * CK ? lo_all : c * CK;
+                const int64_t hi = hi_all < (c + 1) * CK ? hi_all : (c + 1) * CK;
+                for (int64_t e0 = lo; e0 < hi; e0 += BG_PIECE, ++g) {
+                    if (g % n_pushers != me) continue;
+                    const int64_t n = ((hi - e0 < BG_PIECE ? hi - e0 : BG_PIECE) * 2) / 16;
+                    const int4* sp = reinterpret_cast<const int4*>(f.bg_src + (e0 - lo_all) * 2);
+                    int4* dp = reinterpret_cast<int4*>((char*)f.bg_dst[dst] + e0 * 2);
+                    for (int64_t v = threadIdx.x; v < n; v += NUM_THREADS * 4) {
+                        int4 t[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) if (v + u * NUM_THREADS < n) t[u] = sp[v + u * NUM_THREADS];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) if (v + u * NUM_THREADS < n) dp[v + u * NUM_THREADS] = t[u];
+                    }
+                    __syncthreads();
+                    if (threadIdx.x == 0) { __threadfence_system(); atomicAdd_system(f.bg_cnt[dst] + c, 1u); }
+                }
+            }
+        }
+    } else if (comm_cta) {
         // ------------------------------------------------------------------ all-gather pusher (whole CTA)
         const int n_pushers = f.ag_ctas, me = (int)blockIdx.x - compute_ctas;
         const int pieces_per_block = BM / f.ag_piece_rows;
@@ -467,7 +511,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 const int64_t batch = tile / tiles_per_batch;
                 const int64_t rem = tile % tiles_per_batch;
                 int m_blk = (int)(rem % p.m_blocks);
-                const int n_blk = (int)(rem / p.m_blocks);
+                int n_blk = (int)(rem / p.m_blocks);
+                if (FUSED == 3) {
+                    // this rank's own rows first; wait for every 128-row chunk the B tile touches
+                    n_blk = (n_blk + f.bg_first_block) % p.n_blocks;
+                    const int64_t r0 = (int64_t)n_blk * p.bn;
+                    const int64_t r1 = (r0 + p.bn < p.N ? r0 + p.bn : p.N) - 1;
+                    for (int64_t c = r0 / BM; c <= r1 / BM && ok; ++c) {
+                        const unsigned int target = f.epoch * f.bg_expected[c];
+                        if (!wait_counter(f.bg_cnt[f.rank] + c, target, f.limit_ns)) {
+                            ok = false; atomicCAS(f.status, 0, 0x900 | f.rank); atomicCAS(&g_gemm_status, 0, (10 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1;
+                        }
+                    }
+                    if (!ok) break;
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                }
                 if (FUSED == 2) {
                     // local row blocks first, then the peers' blocks in the order in which they are pushed
                     m_blk = (m_blk + f.rank * blocks_per_rank) % p.m_blocks;
@@ -567,8 +625,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const int64_t batch = tile / tiles_per_batch;
             const int64_t rem = tile % tiles_per_batch;
             int m_blk = (int)(rem % p.m_blocks);
-            const int n_blk = (int)(rem / p.m_blocks);
+            int n_blk = (int)(rem / p.m_blocks);
             if (FUSED == 2) m_blk = (m_blk + f.rank * blocks_per_rank) % p.m_blocks;
+            if (FUSED == 3) n_blk = (n_blk + f.bg_first_block) % p.n_blocks;
             const int64_t bi = batch % p.batch_inner, bo = batch / p.batch_inner;
             const uint32_t acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1;
@@ -791,6 +850,7 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
         BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
         BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
         BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
     }
     static int force_bn = -1, force_cta2 = -2;
     if (force_bn < 0) { const char* e = getenv("BMT_GEMM_BN"); force_bn = e ? atoi(e) : 0; }
@@ -800,7 +860,7 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     memset(&p, 0, sizeof(p));
     p.M = m; p.N = n; p.K = k;
     p.a_mn = a_major; p.b_mn = b_major;
-    const int comm_ctas = (fused && fused->mode == 2) ? fused->ag_ctas : 0;
+    const int comm_ctas = (fused && (fused->mode == 2 || fused->mode == 3)) ? fused->ag_ctas : 0;
     if (fused) g_num_sms -= comm_ctas;  // tile choice for the CTAs that do math
     TileChoice tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, force_bn, fused ? 0 : force_cta2);
     if (fused) g_num_sms += comm_ctas;
@@ -840,8 +900,11 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
         if (tc.cta2) return -23;
         const int compute = g_num_sms - comm_ctas;
         const unsigned grid = (unsigned)(tiles < compute ? tiles : compute) + comm_ctas;
-        if (fused->mode == 1) gemm_tcgen05_kernel<false, 1><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, *fused);
-        else gemm_tcgen05_kernel<false, 2><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, *fused);
+        FusedComm fc = *fused;
+        if (fc.mode == 3) fc.bg_first_block = (int)(((fc.bg_first / k) / p.bn) % p.n_blocks);
+        if (fc.mode == 1) gemm_tcgen05_kernel<false, 1><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
+        else if (fc.mode == 2) gemm_tcgen05_kernel<false, 2><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
+        else gemm_tcgen05_kernel<false, 3><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
         bmt_count_launch(1);
         return (int)cudaGetLastError();
     }
@@ -945,6 +1008,46 @@ extern "C" int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank,
     BmtGemmDesc g = *desc;
     g.batch_inner = g.batch_outer = g.b_inner_div = 1;
     return launch_gemm(g, (cudaStream_t)stream, &f);
+}
+
+// ZeRO weight gather -> GEMM (FusedComm mode 3).  desc->b points at the weight inside this rank's gathered buffer (N x K,
+// rows contiguous, pitch K); this rank contributes the flat element range [first, first + count) of it, read from `src`.
+// `expected` is a device array with the number of pieces every 128-row chunk receives from all ranks together
+// (see bmt_zero_gather_expected).
+extern "C" int bmt_zero_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row,
+                                    unsigned int epoch, const void* src, int64_t first, int64_t count, void* const* weight_on_rank,
+                                    void* const* counters, const void* expected_u32, int comm_ctas, void* status_i32,
+                                    double timeout_s, void* stream) {
+    if (world < 2 || world > 8 || desc->b_major != 0 || desc->ldb != desc->k) return -44;
+    if ((first & 7) || (count & 7) || ((uintptr_t)src & 15)) return -45;
+    FusedComm f;
+    memset(&f, 0, sizeof(f));
+    f.mode = 3; f.world = world; f.rank = rank; f.free_row = free_row; f.epoch = epoch;
+    f.status = (int*)status_i32; f.limit_ns = (uint64_t)(timeout_s * 1e9);
+    for (int j = 0; j < world; ++j) { f.flags[j] = (unsigned int*)flags[j]; f.bg_dst[j] = weight_on_rank[j]; f.bg_cnt[j] = (unsigned int*)counters[j]; }
+    f.ag_ctas = comm_ctas; f.bg_src = (const char*)src; f.bg_first = first; f.bg_count = count;
+    f.bg_expected = (const unsigned int*)expected_u32;
+    BmtGemmDesc g = *desc;
+    g.batch_inner = g.batch_outer = g.b_inner_div = 1;
+    return launch_gemm(g, (cudaStream_t)stream, &f);
+}
+
+// Host helper: pieces each 128-row chunk of an (n x k) weight receives when rank j owns the flat element range
+// [first[j], first[j] + count[j]).  out has ceil(n / 128) entries.
+extern "C" int bmt_zero_gather_expected(int64_t n, int64_t k, int world, const int64_t* first, const int64_t* count, unsigned int* out) {
+    const int64_t CK = (int64_t)BM * k;
+    const int64_t chunks = (n + BM - 1) / BM;
+    for (int64_t c = 0; c < chunks; ++c) out[c] = 0;
+    for (int j = 0; j < world; ++j) {
+        const int64_t lo_all = first[j], hi_all = first[j] + count[j];
+        if (count[j] <= 0) continue;
+        for (int64_t c = lo_all / CK; c * CK < hi_all && c < chunks; ++c) {
+            const int64_t lo = lo_all > c * CK ? lo_all : c * CK;
+            const int64_t hi = hi_all < (c + 1) * CK ? hi_all : (c + 1) * CK;
+            out[c] += (unsigned int)((hi - lo + BG_PIECE - 1) / BG_PIECE);
+        }
+    }
+    return 0;
 }
 
 // Status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out.  Reading clears it.

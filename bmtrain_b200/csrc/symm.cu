@@ -145,7 +145,90 @@ __global__ void symm_signal_wait_kernel(unsigned int* const* peer_flags_table, u
     }
 }
 
+struct PushArgs {
+    const char* src[16];     // local source of every range
+    int64_t dst_off[16];     // byte offset inside every rank's destination buffer
+    int64_t nbytes[16];      // multiple of 16
+    int nranges;
+    char* dst[8];            // destination buffer of every rank (own included)
+    unsigned int* peer_flags[8];
+    int world, rank, free_row, done_row;
+    unsigned int epoch;
+    unsigned int* counter;   // local, monotonic: CTAs finished
+    int* status;
+    uint64_t limit_ns;
+};
+
+// Push-style all-gather of a list of byte ranges: every rank writes its ranges to the same offsets of every rank's
+// buffer (own first, then the peers in ring order).  A destination is only written after it published "free" for this
+// epoch; when the whole grid is done the last CTA publishes "delivered" to every rank.
+__global__ void __launch_bounds__(256) push_ranges_kernel(PushArgs a) {
+    __shared__ int ok_s;
+    const int64_t piece = 16384;
+    for (int di = 0; di < a.world; ++di) {
+        const int dst = (a.rank + di) % a.world;
+        if (dst != a.rank) {
+            if (threadIdx.x == 0) {
+                const bool ok = wait_flags(a.peer_flags[a.rank] + a.free_row * a.world + dst, 1, a.epoch, a.limit_ns);
+                if (!ok) atomicCAS(a.status, 0, 0x700 | a.rank);
+                ok_s = ok ? 1 : 0;
+            }
+            __syncthreads();
+            if (!ok_s) break;
+        }
+        int64_t g = 0;  // running piece index over all ranges
+        for (int r = 0; r < a.nranges; ++r) {
+            const int64_t np = (a.nbytes[r] + piece - 1) / piece;
+            for (int64_t pi = 0; pi < np; ++pi, ++g) {
+                if (g % gridDim.x != blockIdx.x) continue;
+                const int64_t b0 = pi * piece;
+                const int64_t n = (a.nbytes[r] - b0 < piece ? a.nbytes[r] - b0 : piece) / 16;
+                const int4* s = reinterpret_cast<const int4*>(a.src[r] + b0);
+                int4* d = reinterpret_cast<int4*>(a.dst[dst] + a.dst_off[r] + b0);
+                for (int64_t v = threadIdx.x; v < n; v += 256 * 4) {
+                    int4 t[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) if (v + u * 256 < n) t[u] = s[v + u * 256];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) if (v + u * 256 < n) d[v + u * 256] = t[u];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned int done = atomicAdd(a.counter, 1u) + 1u;
+        if (done == a.epoch * gridDim.x) {
+            __threadfence_system();
+            for (int j = 0; j < a.world; ++j) st_release_sys(a.peer_flags[j] + a.done_row * a.world + a.rank, a.epoch);
+        }
+    }
+}
+
 }  // namespace
+
+// Push-style all-gather of up to 16 byte ranges (see push_ranges_kernel).  `grid` CTAs; the caller's `counter` advances
+// by `grid` per call, so it has to be dedicated to one (ranges, grid) configuration.
+extern "C" int bmt_push_ranges(const void* const* src, const int64_t* dst_off, const int64_t* nbytes, int nranges,
+                               void* const* dst, void* const* peer_flags, int world, int rank, int free_row, int done_row,
+                               unsigned int epoch, void* counter_u32, void* status_i32, double timeout_s, int grid,
+                               void* stream) {
+    if (nranges < 0 || nranges > 16 || world < 1 || world > 8) return -33;
+    PushArgs a;
+    memset(&a, 0, sizeof(a));
+    for (int r = 0; r < nranges; ++r) {
+        if ((nbytes[r] & 15) || (dst_off[r] & 15) || ((uintptr_t)src[r] & 15)) return -34;
+        a.src[r] = (const char*)src[r]; a.dst_off[r] = dst_off[r]; a.nbytes[r] = nbytes[r];
+    }
+    a.nranges = nranges;
+    for (int j = 0; j < world; ++j) { a.dst[j] = (char*)dst[j]; a.peer_flags[j] = (unsigned int*)peer_flags[j]; }
+    a.world = world; a.rank = rank; a.free_row = free_row; a.done_row = done_row; a.epoch = epoch;
+    a.counter = (unsigned int*)counter_u32; a.status = (int*)status_i32; a.limit_ns = (uint64_t)(timeout_s * 1e9);
+    push_ranges_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}
 
 // Fused reduce-scatter: out[0..part) (+)= scale * sum_j peer_j[rank*part + i], with inf/nan detection.
 // peers / peer_flags: host arrays of `world` device pointers.  part must be a multiple of 8 elements and every

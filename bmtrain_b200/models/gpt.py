@@ -94,6 +94,13 @@ class TransformerEncoder(DistributedModule):
         self.ff = Feedforward(dim_model, dim_ff, bias=bias, dtype=dtype, activation=activation)
         self.causal = causal
 
+    # the ZeRO block may leave the gather of this weight to the GEMM that consumes it
+    _bmt_first_gemm = "attn.project_qkv.weight"
+    _bmt_deferred_gather = None
+
+    def _bmt_can_fuse_first_gemm(self, hidden, *rest) -> bool:
+        return torch.is_tensor(hidden) and self._fused_ok(hidden) and not bmt_inspect.tensor.debug.get("_inspect_tensor", False)
+
     def _fused_ok(self, hidden: torch.Tensor) -> bool:
         return (hidden.is_cuda and hidden.dim() == 3 and config["tp_size"] == 1 and _FUSED_BLOCK and self.attn.project_qkv.bias is not None
                 and hidden.dtype in (torch.float16, torch.bfloat16) and self.attn.dim_head % 8 == 0)
@@ -103,11 +110,12 @@ class TransformerEncoder(DistributedModule):
         if self._fused_ok(hidden):
             # one native call per direction for the whole block (csrc/block_exec.cu)
             a, f = self.attn, self.ff
+            deferred, self._bmt_deferred_gather = self._bmt_deferred_gather, None
             return _gpt_block.gpt_block(
                 hidden, mask, a.num_heads, a.dim_head, f.activation, self.ln_attn.eps, self.causal,
                 self.ln_attn.weight, self.ln_attn.bias, a.project_qkv.weight, a.project_qkv.bias,
                 a.project_out.weight, a.project_out.bias, self.ln_ff.weight, self.ln_ff.bias,
-                f.w_in.weight, f.w_in.bias, f.w_out.weight, f.w_out.bias)
+                f.w_in.weight, f.w_in.bias, f.w_out.weight, f.w_out.bias, deferred=deferred)
         x = self.ln_attn(hidden)
         x = self.attn(x, mask, self.causal)
         hidden = hidden + x

@@ -65,7 +65,7 @@ def _fill(blk: _Block, x, y, mask, params, saved, n_heads, d_head, act, eps, cau
 
 class GPTBlockFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, mask, n_heads, d_head, act, eps, causal, *params):
+    def forward(ctx, x, mask, n_heads, d_head, act, eps, causal, deferred, *params):
         lib = _native.cuda_lib()
         x = x.contiguous()
         b, s, d = x.shape
@@ -85,7 +85,19 @@ class GPTBlockFunction(torch.autograd.Function):
         y = torch.empty_like(x)
         blk = _Block()
         _fill(blk, x, y, mask8, params, saved, n_heads, d_head, act, eps, causal)
-        _native.check(lib.bmt_gpt_block_forward(ctypes.byref(blk), _native.stream_handle()), "GPT block forward")
+        if deferred is None:
+            _native.check(lib.bmt_gpt_block_forward(ctypes.byref(blk), _native.stream_handle()), "GPT block forward")
+        else:
+            # the block's parameters are still on their way: norms and biases first, the QKV weight is gathered by the GEMM
+            # that consumes it, everything else has to be there before the output projection
+            from ..parallel import fused_ops
+
+            cur = torch.cuda.current_stream()
+            cur.wait_event(deferred["ev_small"])
+            _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 1, 1, _native.stream_handle()), "GPT block forward")
+            fused_ops.zero_gather_gemm(saved["ln1"], saved["qkv"], params[3], deferred)
+            cur.wait_event(deferred["ev_rest"])
+            _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 3, 9, _native.stream_handle()), "GPT block forward")
         ctx.saved, ctx.x, ctx.mask8, ctx.params = saved, x, mask8, params
         ctx.cfg = (n_heads, d_head, act, eps, causal)
         return y
@@ -130,11 +142,12 @@ class GPTBlockFunction(torch.autograd.Function):
         _native.check(lib.bmt_gpt_block_backward(ctypes.byref(blk), ctypes.byref(g), _native.stream_handle()), "GPT block backward")
         ctx.saved = None
         out = [grads.get(name) if p.requires_grad else None for name, p in zip(_PARAM_NAMES, params)]
-        return (dx, None, None, None, None, None, None) + tuple(out)
+        return (dx, None, None, None, None, None, None, None) + tuple(out)
 
 
 def gpt_block(x: torch.Tensor, mask: Optional[torch.Tensor], n_heads: int, d_head: int, act: str, eps: float, causal: bool,
-              ln1_w, ln1_b, qkv_w, qkv_b, out_w, out_b, ln2_w, ln2_b, fc1_w, fc1_b, fc2_w, fc2_b) -> torch.Tensor:
-    """``x`` (batch, seq, d_model) -> same shape.  ``mask``: optional bool (batch, seq, seq), True = attend."""
-    return GPTBlockFunction.apply(x, mask, n_heads, d_head, act, eps, causal, ln1_w, ln1_b, qkv_w, qkv_b, out_w, out_b,
+              ln1_w, ln1_b, qkv_w, qkv_b, out_w, out_b, ln2_w, ln2_b, fc1_w, fc1_b, fc2_w, fc2_b, deferred=None) -> torch.Tensor:
+    """``x`` (batch, seq, d_model) -> same shape.  ``mask``: optional bool (batch, seq, seq), True = attend.
+    ``deferred``: gather-in-progress description from the owning ZeRO block (see ``Block._try_deferred_gather``)."""
+    return GPTBlockFunction.apply(x, mask, n_heads, d_head, act, eps, causal, deferred, ln1_w, ln1_b, qkv_w, qkv_b, out_w, out_b,
                                   ln2_w, ln2_b, fc1_w, fc1_b, fc2_w, fc2_b)

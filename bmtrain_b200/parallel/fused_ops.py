@@ -22,6 +22,7 @@ from ..ops.gpt_block import _i64, _int, _f32, _c_void_p
 from . import symm
 
 _COMM_CTAS = 16
+calls = {"gemm_rs": 0, "ag_gemm": 0, "zero_gather_gemm": 0}  # how often each fused kernel ran (tests and benchmarks read this)
 _ring: Dict[Tuple, int] = {}
 _counters: Dict[Tuple, torch.Tensor] = {}
 
@@ -81,6 +82,7 @@ def gemm_rs(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
         ctypes.c_uint(epoch), slots, ctypes.c_void_p(inbox.local_ptr), ctypes.c_int64(rows), _native.ptr(_counters[key]),
         _native.ptr(out), _native.ptr(bias), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s), _native.stream_handle()),
         "fused GEMM -> reduce-scatter kernel")
+    calls["gemm_rs"] += 1
     return out
 
 
@@ -115,6 +117,50 @@ def ag_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
         _native.ptr(x_local), ctypes.c_int64(x_local.stride(0)), ctypes.c_int64(m), gathered.ptr_table(), counters.ptr_table(),
         ctypes.c_int(_COMM_CTAS), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s), _native.stream_handle()),
         "fused all-gather -> GEMM kernel")
+    calls["ag_gemm"] += 1
     if return_gathered:
         return out, gathered.tensor(x_local.dtype, W * m * K).view(W * m, K)
     return out
+
+
+def zero_gather_gemm(x: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor], ctx: dict) -> None:
+    """``out = x @ W^T + bias`` where ``W`` is a ZeRO-sharded weight that nobody has gathered yet: the kernel's pusher
+    CTAs deliver every rank's part of ``W`` to all ranks while the tiles whose rows have arrived are already being
+    multiplied (``ctx`` comes from ``Block._try_deferred_gather``)."""
+    lib = _native.cuda_lib()
+    rt, buf, b, slot, epoch, key = ctx["rt"], ctx["buf"], ctx["bucket"], ctx["slot"], ctx["epoch"], ctx["key"]
+    N, K = slot.shape
+    W = b.comm.size
+    es = x.element_size()
+    w0, w1 = slot.offset, slot.offset + slot.numel
+    geo = rt.cache.get(key + ("geo",))
+    if geo is None:
+        first = (ctypes.c_int64 * W)()
+        count = (ctypes.c_int64 * W)()
+        for j in range(W):
+            lo, hi = max(w0, j * b.part), min(w1, (j + 1) * b.part)
+            first[j], count[j] = max(lo - w0, 0), max(hi - lo, 0)
+        chunks = (N + 127) // 128
+        exp_host = (ctypes.c_uint * chunks)()
+        lib.bmt_zero_gather_expected(ctypes.c_int64(N), ctypes.c_int64(K), ctypes.c_int(W), first, count, exp_host)
+        expected = torch.tensor(list(exp_host), dtype=torch.int32, device=x.device)
+        geo = (list(first), list(count), expected, chunks)
+        rt.cache[key + ("geo",)] = geo
+    first, count, expected, chunks = geo
+    counters = rt.slot(key + ("cnt",), max(256, chunks * 4))
+    d = _GemmDesc()
+    d.m, d.n, d.k = x.shape[0], N, K
+    d.a, d.lda, d.a_major = x.data_ptr(), x.stride(0), 0
+    d.b, d.ldb, d.b_major = buf.local_ptr + w0 * es, K, 0
+    d.c, d.ldc, d.c_dtype = out.data_ptr(), out.stride(0), _DT[x.dtype]
+    d.bias = None if bias is None else bias.data_ptr()
+    d.ab_dtype, d.alpha = _DT[x.dtype], 1.0
+    me = b.comm.rank
+    src = b.storage.data_ptr() + (w0 + first[me] - b.begin) * es if count[me] > 0 else b.storage.data_ptr()
+    weight_on_rank = (ctypes.c_void_p * W)(*[p + w0 * es for p in buf.ptrs])
+    _native.check(lib.bmt_zero_gather_gemm(
+        ctypes.byref(d), ctypes.c_int(W), ctypes.c_int(me), rt.flag_ptrs, ctypes.c_int(ctx["free_row"]), ctypes.c_uint(epoch),
+        ctypes.c_void_p(src), ctypes.c_int64(first[me]), ctypes.c_int64(count[me]), weight_on_rank, counters.ptr_table(),
+        _native.ptr(expected), ctypes.c_int(_COMM_CTAS), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s),
+        _native.stream_handle()), "fused ZeRO gather -> GEMM kernel")
+    calls["zero_gather_gemm"] += 1

@@ -105,6 +105,8 @@ class PeerRuntime:
         self.epochs: Dict[int, int] = {}
         self.rows: Dict[Tuple, int] = {}
         self.slots: Dict[Tuple, SymmetricBuffer] = {}
+        self._counters: Dict[Tuple, torch.Tensor] = {}
+        self.cache: Dict[Tuple, object] = {}
         self.timeout_s = float(os.environ.get("BMT_PEER_TIMEOUT", "10"))
         self.stream = torch.cuda.Stream(priority=-1)
 
@@ -147,6 +149,26 @@ class PeerRuntime:
             ctypes.c_void_p(self.flag_table_dev.data_ptr()), ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank),
             ctypes.c_int(row), ctypes.c_uint(epoch), ctypes.c_int(int(signal)), ctypes.c_int(int(wait)),
             _native.ptr(self.status), ctypes.c_double(self.timeout_s), _native.stream_handle()), "peer signal/wait kernel")
+
+    def push_ranges(self, dst: SymmetricBuffer, ranges, free_row: int, done_row: int, epoch: int, key: Tuple) -> None:
+        """Push-style all-gather on the current stream: ``ranges`` = [(src_ptr, dst_byte_offset, nbytes), ...] (at most 16)
+        are written to the same offsets of ``dst`` on every rank once that rank published "free" for ``epoch``; when this
+        rank's data is delivered everywhere it publishes ``epoch`` on ``done_row``."""
+        lib = _native.cuda_lib()
+        n = len(ranges)
+        assert n <= 16
+        grid = 32
+        ckey = key + ("push_counter", n)
+        if ckey not in self._counters:
+            self._counters[ckey] = torch.zeros(1, dtype=torch.int32, device=config["device"])
+        src = (ctypes.c_void_p * max(n, 1))(*[r[0] for r in ranges])
+        off = (ctypes.c_int64 * max(n, 1))(*[r[1] for r in ranges])
+        nb = (ctypes.c_int64 * max(n, 1))(*[r[2] for r in ranges])
+        _native.check(lib.bmt_push_ranges(
+            src, off, nb, ctypes.c_int(n), dst.ptr_table(), self.flag_ptrs, ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank),
+            ctypes.c_int(free_row), ctypes.c_int(done_row), ctypes.c_uint(epoch), _native.ptr(self._counters[ckey]),
+            _native.ptr(self.status), ctypes.c_double(self.timeout_s), ctypes.c_int(grid), _native.stream_handle()),
+            "push all-gather kernel")
 
     def reduce_scatter(self, full: SymmetricBuffer, row: int, part: int, out: torch.Tensor, accumulate: bool,
                        scale: float = 1.0) -> None:

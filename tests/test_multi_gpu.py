@@ -49,6 +49,10 @@ def body_fused_rs(fused: bool):
         loss = loss_fn(logits.view(-1, logits.shape[-1]), ids[:, 1:].contiguous().view(-1))
         (loss * scale / world).backward()
     bmt.synchronize()
+    from bmtrain_b200.parallel import fused_ops
+    if fused:
+        # first block in forward and last block in backward were not prefetched: their QKV weight came through the fused kernel
+        assert fused_ops.calls["zero_gather_gemm"] == 4, fused_ops.calls
     for rt in symm._runtimes.values():
         if rt is not None:
             rt.check()
