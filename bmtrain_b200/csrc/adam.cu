@@ -129,6 +129,12 @@ extern "C" int bmt_adam_fp16_multi(const BmtAdamTable* tab, float beta1, float b
     return launch<__half, __half, true>(tab, AdamArgs{beta1, beta2, eps, lr, scale, wd, bc1, bc2}, (cudaStream_t)stream);
 }
 
+// fp16 parameters with fp32 moments in true (unscaled) units: the layout of the host-offloaded optimizer state.
+extern "C" int bmt_adam_fp16_f32state_multi(const BmtAdamTable* tab, float beta1, float beta2, float eps, float lr, float scale,
+                                            float wd, float bc1, float bc2, void* stream) {
+    return launch<__half, float, false>(tab, AdamArgs{beta1, beta2, eps, lr, scale, wd, bc1, bc2}, (cudaStream_t)stream);
+}
+
 extern "C" int bmt_adam_bf16_multi(const BmtAdamTable* tab, float beta1, float beta2, float eps, float lr, float scale,
                                    float wd, float bc1, float bc2, void* stream) {
     return launch<__nv_bfloat16, float, false>(tab, AdamArgs{beta1, beta2, eps, lr, scale, wd, bc1, bc2}, (cudaStream_t)stream);

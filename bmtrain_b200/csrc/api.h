@@ -31,6 +31,8 @@ typedef struct {
 // dtype codes: 0 = fp16, 1 = bf16, 2 = fp32
 int bmt_adam_fp16_multi(const BmtAdamTable* tab, float beta1, float beta2, float eps, float lr, float scale, float wd,
                         float bc1, float bc2, void* stream);
+int bmt_adam_fp16_f32state_multi(const BmtAdamTable* tab, float beta1, float beta2, float eps, float lr, float scale, float wd,
+                                 float bc1, float bc2, void* stream);
 int bmt_adam_bf16_multi(const BmtAdamTable* tab, float beta1, float beta2, float eps, float lr, float scale, float wd,
                         float bc1, float bc2, void* stream);
 

@@ -71,7 +71,10 @@ def adam_half_multi(entries: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Te
         return
     lib = _native.cuda_lib()
     fp16 = entries[0][1].dtype == torch.float16
-    fn = lib.bmt_adam_fp16_multi if fp16 else lib.bmt_adam_bf16_multi
+    if fp16 and entries[0][3].dtype == torch.float32:
+        fn = lib.bmt_adam_fp16_f32state_multi  # offloaded-state layout: fp32 moments in true units
+    else:
+        fn = lib.bmt_adam_fp16_multi if fp16 else lib.bmt_adam_bf16_multi
     for i in range(0, len(entries), _MAX_TENSORS):
         chunk = entries[i:i + _MAX_TENSORS]
         table = _AdamTable()

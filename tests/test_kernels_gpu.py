@@ -270,3 +270,38 @@ def test_fused_gpt_block_matches_oracle(dev, dtype, act):
         got = mine[name].grad
         assert got is not None, name
         assert _rel(got.cpu().view(p.shape), p.grad) < gtol, name
+
+
+@pytest.mark.parametrize("math", ["gpu", "auto"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_offload_adam_gpu_streamed_matches_host_math(dev, dtype, math):
+    """AdamOffloadOptimizer: the GPU-streamed step (state chunks host -> HBM -> host) and the host AVX step give the same
+    parameters and the same host-resident state; both follow an fp32 AdamW run."""
+    import bmtrain_b200 as bmt
+
+    torch.manual_seed(12)
+    shapes = [(1 << 24) + 4096, 2560, (3000, 512), (1 << 23)]
+    w0 = [torch.randn(s, device=dev) * 0.1 for s in shapes]
+    ref = [w.clone().requires_grad_() for w in w0]
+    o_ref = torch.optim.AdamW(ref, lr=1e-2, weight_decay=1e-2)
+    pa = [torch.nn.Parameter(w.to(dtype)) for w in w0]
+    pb = [torch.nn.Parameter(w.to(dtype)) for w in w0]
+    oa = bmt.optim.AdamOffloadOptimizer(pa, lr=1e-2, weight_decay=1e-2, math=math)
+    ob = bmt.optim.AdamOffloadOptimizer(pb, lr=1e-2, weight_decay=1e-2, math="cpu")
+    scale = 64.0
+    for step in range(4):
+        for r, a, b in zip(ref, pa, pb):
+            g = torch.randn_like(r)
+            r.grad = g.clone()
+            a.grad = (g * scale).to(dtype)
+            b.grad = (g * scale).to(dtype)
+        o_ref.step(); oa.step(scale=scale); ob.step(scale=scale)
+    torch.cuda.synchronize()
+    sa, sb = oa.state_dict(), ob.state_dict()
+    tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
+    for i, (r, a, b) in enumerate(zip(ref, pa, pb)):
+        assert (a.float() - b.float()).abs().max().item() <= (1e-2 if dtype == torch.bfloat16 else 2e-3)
+        assert (a.float() - r).abs().max().item() < tol
+        for key in ("exp_avg", "exp_avg_sq", "_param_fp32"):
+            assert not sa["state"][i][key].is_cuda
+            assert torch.allclose(sa["state"][i][key], sb["state"][i][key], atol=1e-5, rtol=1e-4), (i, key)
