@@ -58,6 +58,8 @@ struct GemmParams {
     const void* aux;       // optional (M x N, operand dtype, row pitch ld_aux) for the multiplicative epilogues
     int64_t ld_aux;
     int aux_mode;          // 0 none, 1: out *= (aux > 0)  (ReLU backward), 2: out *= gelu'(aux)
+    int group_m;           // tile raster: consecutive tiles walk down `group_m` row blocks before moving to the next column block
+    int debug;             // measurement only (BMT_GEMM_DEBUG): 1 = no TMA loads, 2 = no MMAs, 4 = no epilogue stores
 };
 
 // ------------------------------------------------------------------------------------------ PTX wrappers
@@ -165,6 +167,18 @@ template <typename T> __device__ __forceinline__ void load8(const T* src, float*
     bmt::Vec16<T> o = bmt::ld16(src);
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = bmt::Cvt<T>::to_f(o.v[i]);
+}
+
+// Grouped raster: the CTAs that run at the same time cover a compact (group_m x ~#SM/group_m) patch of output tiles, so
+// every k-slice of A and B that one of them pulls from DRAM is found in L2 by the others.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int64_t rem, int& m_blk, int& n_blk) {
+    const int64_t per_group = (int64_t)p.group_m * p.n_blocks;
+    const int64_t group = rem / per_group;
+    const int first_m = (int)(group * p.group_m);
+    const int rows = p.m_blocks - first_m < p.group_m ? p.m_blocks - first_m : p.group_m;
+    const int64_t in_group = rem % per_group;
+    m_blk = first_m + (int)(in_group % rows);
+    n_blk = (int)(in_group / rows);
 }
 
 struct SharedHeader {
@@ -510,8 +524,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
                 const int64_t batch = tile / tiles_per_batch;
                 const int64_t rem = tile % tiles_per_batch;
-                int m_blk = (int)(rem % p.m_blocks);
-                int n_blk = (int)(rem / p.m_blocks);
+                int m_blk, n_blk;
+                tile_coords(p, rem, m_blk, n_blk);
                 if (FUSED == 3) {
                     // this rank's own rows first; wait for every 128-row chunk the B tile touches
                     n_blk = (n_blk + f.bg_first_block) % p.n_blocks;
@@ -545,7 +559,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     if (!mbar_wait(&hdr->empty[s], ph ^ 1)) { ok = false; atomicCAS(&g_gemm_status, 0, (1 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
                     uint8_t* sa = smem + (size_t)s * stage_bytes;
                     uint8_t* sb = sa + a_bytes;
-                    if (!CTA2) {
+                    if (p.debug & 1) {
+                        if (rank == 0) mbar_arrive(&hdr->full[s]);
+                    } else if (!CTA2) {
                         mbar_expect_tx(&hdr->full[s], stage_bytes);
                         if (!p.a_mn) {
                             tma_load_4d(&tma_a, &hdr->full[s], sa, kb * BK, m0, bi, bo);
@@ -606,6 +622,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                                                    : make_smem_desc(sa + k * (UMMA_K * 2), 0, 1024);
                         const uint64_t bd = p.b_mn ? make_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
                                                    : make_smem_desc(sb + k * (UMMA_K * 2), 0, 1024);
+                        if (p.debug & 2) continue;
                         if (CTA2) umma_f16_2cta(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
                         else umma_f16(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
                     }
@@ -624,8 +641,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++tcount) {
             const int64_t batch = tile / tiles_per_batch;
             const int64_t rem = tile % tiles_per_batch;
-            int m_blk = (int)(rem % p.m_blocks);
-            int n_blk = (int)(rem / p.m_blocks);
+            int m_blk, n_blk;
+            tile_coords(p, rem, m_blk, n_blk);
             if (FUSED == 2) m_blk = (m_blk + f.rank * blocks_per_rank) % p.m_blocks;
             if (FUSED == 3) n_blk = (n_blk + f.bg_first_block) % p.n_blocks;
             const int64_t bi = batch % p.batch_inner, bo = batch / p.batch_inner;
@@ -658,6 +675,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 uint32_t r[32];
                 tmem_ld32(taddr + c0, r);
                 tmem_ld_wait();
+                if (p.debug & 4) continue;
                 if (p.c_dtype == BMT_DT_F16) epilogue_chunk<__half>(p, (__half*)cbase + coff, row, col0, col_end, r, row_ok);
                 else if (p.c_dtype == BMT_DT_BF16) epilogue_chunk<__nv_bfloat16>(p, (__nv_bfloat16*)cbase + coff, row, col0, col_end, r, row_ok);
                 else epilogue_chunk<float>(p, (float*)cbase + coff, row, col0, col_end, r, row_ok);
@@ -852,7 +870,8 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
         BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
         BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
     }
-    static int force_bn = -1, force_cta2 = -2;
+    static int force_bn = -1, force_cta2 = -2, debug_flags = -1;
+    if (debug_flags < 0) { const char* e = getenv("BMT_GEMM_DEBUG"); debug_flags = e ? atoi(e) : 0; }
     if (force_bn < 0) { const char* e = getenv("BMT_GEMM_BN"); force_bn = e ? atoi(e) : 0; }
     if (force_cta2 == -2) { const char* e = getenv("BMT_GEMM_CTA2"); force_cta2 = e ? atoi(e) : -1; }
 
@@ -876,6 +895,11 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     p.batch_inner = batch_inner; p.batch_outer = batch_outer; p.b_inner_div = b_inner_div > 0 ? b_inner_div : 1;
     p.c = c; p.ldc = ldc; p.c_bs0 = c_bs0; p.c_bs1 = c_bs1; p.c_dtype = c_dtype;
     p.bias = bias; p.bias_dtype = ab_dtype; p.act = act; p.accumulate = accumulate; p.alpha = alpha;
+    p.debug = debug_flags;
+    static int group_env = -1;
+    if (group_env < 0) { const char* e = getenv("BMT_GEMM_GROUP_M"); group_env = e ? atoi(e) : 0; }
+    p.group_m = group_env > 0 ? group_env : 16;
+    if (p.group_m > p.m_blocks || fused) p.group_m = p.m_blocks;  // the fused modes rotate whole rows / columns of tiles
     p.residual = g.residual; p.ldr = g.ldr; p.aux = g.aux; p.ld_aux = g.ld_aux; p.aux_mode = g.aux ? g.aux_mode : 0;
     if ((p.residual || p.aux_mode) && batch_inner * batch_outer != 1) return -21;  // fused extras are for plain (unbatched) GEMMs
     const uint32_t fmt = ab_dtype == BMT_DT_F16 ? 0u : 1u;
