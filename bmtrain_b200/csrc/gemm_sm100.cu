@@ -79,6 +79,25 @@ __device__ __forceinline__ uint64_t global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// Non-suspending variant: test_wait in a tight loop (measurement knob).
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    uint64_t start = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 65535u) == 65535u) {
+            const uint64_t now = global_ns();
+            if (start == 0) start = now;
+            else if (now - start > 2000000000ull) return false;
+        }
+    }
+}
 // Bounded wait: true when the phase completed, false when about two seconds passed without it.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
@@ -98,6 +117,61 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         }
     }
 }
+// The two single-thread loops (TMA producer, MMA issuer) are latency chains of scalar instructions: they work on raw
+// 32-bit shared addresses and pre-built descriptor halves so that one pipeline step costs a few dozen clocks.
+__device__ __forceinline__ bool mbar_wait_u32(uint32_t addr, uint32_t parity) {
+    uint64_t start = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 1023u) == 1023u) {
+            const uint64_t now = global_ns();
+            if (start == 0) start = now;
+            else if (now - start > 2000000000ull) return false;
+        }
+    }
+}
+__device__ __forceinline__ void mbar_expect_tx_u32(uint32_t addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_u32(uint32_t addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_u32(const CUtensorMap* map, uint32_t bar, uint32_t dst, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_2cta_u32(const CUtensorMap* map, uint32_t bar_cluster, uint32_t dst, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_u32(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_commit_2cta_u32(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+// high word of a 128-byte-swizzle descriptor: SBO (16-byte units), version 1, SWIZZLE_128B
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes) { return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29); }
+// low word: start address and LBO (16-byte units)
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return ((saddr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16); }
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -519,8 +593,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     } else if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one per CTA)
         if (lane == 0) {
-            uint32_t it = 0;
             bool ok = true;
+            uint32_t ps = 0, pph = 0;   // ring position and phase, carried across tiles
+            const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(&hdr->full[0]), empty0 = smem_u32(&hdr->empty[0]);
+            const uint32_t full_leader0 = CTA2 ? map_to_cta(full0, 0) : full0;
             for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
                 const int64_t batch = tile / tiles_per_batch;
                 const int64_t rem = tile % tiles_per_batch;
@@ -553,81 +629,80 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 const int bib = (int)(bi / p.b_inner_div);
                 const int m0 = m_blk * (BM * NCTA) + (int)rank * BM;            // this CTA's rows of A
                 const int n0 = n_blk * p.bn + (int)(rank * bn_local);           // this CTA's rows of the B tile
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % p.stages;
-                    const uint32_t ph = (it / p.stages) & 1;
-                    if (!mbar_wait(&hdr->empty[s], ph ^ 1)) { ok = false; atomicCAS(&g_gemm_status, 0, (1 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
-                    uint8_t* sa = smem + (size_t)s * stage_bytes;
-                    uint8_t* sb = sa + a_bytes;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait_u32(empty0 + 8 * ps, pph ^ 1)) { ok = false; atomicCAS(&g_gemm_status, 0, (1 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
+                    const uint32_t sa = smem0 + ps * stage_bytes, sb = sa + a_bytes;
+                    const int kx = kb * BK;
                     if (p.debug & 1) {
-                        if (rank == 0) mbar_arrive(&hdr->full[s]);
+                        if (rank == 0) mbar_arrive_u32(full0 + 8 * ps);
                     } else if (!CTA2) {
-                        mbar_expect_tx(&hdr->full[s], stage_bytes);
+                        const uint32_t bar = full0 + 8 * ps;
+                        mbar_expect_tx_u32(bar, stage_bytes);
                         if (!p.a_mn) {
-                            tma_load_4d(&tma_a, &hdr->full[s], sa, kb * BK, m0, bi, bo);
+                            tma_load_4d_u32(&tma_a, bar, sa, kx, m0, bi, bo);
                         } else {
 #pragma unroll
-                            for (int c = 0; c < BM / 64; ++c)
-                                tma_load_4d(&tma_a, &hdr->full[s], sa + c * (64 * BK * 2), m0 + c * 64, kb * BK, bi, bo);
+                            for (int c = 0; c < BM / 64; ++c) tma_load_4d_u32(&tma_a, bar, sa + c * (64 * BK * 2), m0 + c * 64, kx, bi, bo);
                         }
                         if (!p.b_mn) {
-                            tma_load_4d(&tma_b, &hdr->full[s], sb, kb * BK, n0, bib, bo);
+                            tma_load_4d_u32(&tma_b, bar, sb, kx, n0, bib, bo);
                         } else {
-                            for (int c = 0; c < (int)bn_local / 64; ++c)
-                                tma_load_4d(&tma_b, &hdr->full[s], sb + c * (64 * BK * 2), n0 + c * 64, kb * BK, bib, bo);
+                            for (int c = 0; c < (int)bn_local / 64; ++c) tma_load_4d_u32(&tma_b, bar, sb + c * (64 * BK * 2), n0 + c * 64, kx, bib, bo);
                         }
                     } else {
                         // both CTAs report to the leader's barrier; the leader announces the bytes of the pair
-                        const uint32_t bar = map_to_cta(smem_u32(&hdr->full[s]), 0);
-                        if (rank == 0) mbar_expect_tx(&hdr->full[s], 2 * stage_bytes);
+                        const uint32_t bar = full_leader0 + 8 * ps;
+                        if (rank == 0) mbar_expect_tx_u32(full0 + 8 * ps, 2 * stage_bytes);
                         if (!p.a_mn) {
-                            tma_load_4d_2cta(&tma_a, bar, sa, kb * BK, m0, bi, bo);
+                            tma_load_4d_2cta_u32(&tma_a, bar, sa, kx, m0, bi, bo);
                         } else {
 #pragma unroll
-                            for (int c = 0; c < BM / 64; ++c)
-                                tma_load_4d_2cta(&tma_a, bar, sa + c * (64 * BK * 2), m0 + c * 64, kb * BK, bi, bo);
+                            for (int c = 0; c < BM / 64; ++c) tma_load_4d_2cta_u32(&tma_a, bar, sa + c * (64 * BK * 2), m0 + c * 64, kx, bi, bo);
                         }
                         if (!p.b_mn) {
-                            tma_load_4d_2cta(&tma_b, bar, sb, kb * BK, n0, bib, bo);
+                            tma_load_4d_2cta_u32(&tma_b, bar, sb, kx, n0, bib, bo);
                         } else {
-                            for (int c = 0; c < (int)bn_local / 64; ++c)
-                                tma_load_4d_2cta(&tma_b, bar, sb + c * (64 * BK * 2), n0 + c * 64, kb * BK, bib, bo);
+                            for (int c = 0; c < (int)bn_local / 64; ++c) tma_load_4d_2cta_u32(&tma_b, bar, sb + c * (64 * BK * 2), n0 + c * 64, kx, bib, bo);
                         }
                     }
+                    if (++ps == (uint32_t)p.stages) { ps = 0; pph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only in pair mode)
         if (lane == 0 && rank == 0) {
-            uint32_t it = 0, tcount = 0;
+            uint32_t tcount = 0;
             bool ok = true;
+            uint32_t cs = 0, cph = 0;
+            const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(&hdr->full[0]), empty0 = smem_u32(&hdr->empty[0]);
+            // descriptor halves that never change; per MMA only the start address moves: K-major steps 32 bytes inside
+            // the 128-byte swizzle row, MN-major steps 16 K rows (2 KiB)
+            const uint32_t a_hi = desc_hi(1024), b_hi = desc_hi(1024);
+            const uint32_t a_lbo = p.a_mn ? 64 * BK * 2 : 0, b_lbo = p.b_mn ? 64 * BK * 2 : 0;
+            const uint32_t a_kstep = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4, b_kstep = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
             for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++tcount) {
                 const uint32_t acc = tcount & 1;
                 const uint32_t acc_ph = (tcount >> 1) & 1;
                 if (!mbar_wait(&hdr->tmem_empty[acc], acc_ph ^ 1)) { ok = false; atomicCAS(&g_gemm_status, 0, (2 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
                 tc_fence_after();
                 const uint32_t tmem_c = tmem_base + acc * p.bn;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % p.stages;
-                    const uint32_t ph = (it / p.stages) & 1;
-                    if (!mbar_wait(&hdr->full[s], ph)) { ok = false; atomicCAS(&g_gemm_status, 0, (3 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait_u32(full0 + 8 * cs, cph)) { ok = false; atomicCAS(&g_gemm_status, 0, (3 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
-                    const uint32_t sb = sa + a_bytes;
+                    const uint32_t sa = smem0 + cs * stage_bytes;
+                    const uint32_t a_lo = desc_lo(sa, a_lbo), b_lo = desc_lo(sa + a_bytes, b_lbo);
+                    if (!(p.debug & 2)) {
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // K-major: step 32 bytes inside the 128-byte swizzle row; MN-major: step 16 K rows (2 KiB)
-                        const uint64_t ad = p.a_mn ? make_smem_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                                                   : make_smem_desc(sa + k * (UMMA_K * 2), 0, 1024);
-                        const uint64_t bd = p.b_mn ? make_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                                                   : make_smem_desc(sb + k * (UMMA_K * 2), 0, 1024);
-                        if (p.debug & 2) continue;
-                        if (CTA2) umma_f16_2cta(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
-                        else umma_f16(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t ad = pack_desc(a_lo + k * a_kstep, a_hi), bd = pack_desc(b_lo + k * b_kstep, b_hi);
+                            if (CTA2) umma_f16_2cta(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                            else umma_f16(tmem_c, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
                     // frees the smem stage (in both CTAs) once these MMAs have read it
-                    if (CTA2) umma_commit_2cta(&hdr->empty[s]); else umma_commit(&hdr->empty[s]);
+                    if (CTA2) umma_commit_2cta_u32(empty0 + 8 * cs); else umma_commit_u32(empty0 + 8 * cs);
+                    if (++cs == (uint32_t)p.stages) { cs = 0; cph ^= 1; }
                 }
                 if (ok) { if (CTA2) umma_commit_2cta(&hdr->tmem_full[acc]); else umma_commit(&hdr->tmem_full[acc]); }
             }
@@ -648,7 +723,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const int64_t bi = batch % p.batch_inner, bo = batch / p.batch_inner;
             const uint32_t acc = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1;
-            if (!mbar_wait(&hdr->tmem_full[acc], acc_ph)) { ok = false; atomicCAS(&g_gemm_status, 0, (4 << 16) | (blockIdx.x & 0xffff)); break; }
+            // one lane per warp polls the barrier (128 pollers would compete with the producer / MMA threads for the
+            // barrier unit during the whole main loop); the warp then re-converges
+            int got = 1;
+            if (lane == 0) got = mbar_wait(&hdr->tmem_full[acc], acc_ph) ? 1 : 0;
+            got = __shfl_sync(0xffffffffu, got, 0);
+            if (!got) { ok = false; if (lane == 0) atomicCAS(&g_gemm_status, 0, (4 << 16) | (blockIdx.x & 0xffff)); break; }
             tc_fence_after();
             const int64_t row = (int64_t)m_blk * (BM * NCTA) + rank * BM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
