@@ -28,6 +28,30 @@ def _partition_bounds(p):
     return None
 
 
+def _zero_grad(optimizer, set_to_none: bool) -> None:
+    """``zero_grad`` that does not touch memory for parameters owned by a ZeRO block.
+
+    A block's reduce-scatter produces a fresh partition gradient every step, so its old gradient is simply dropped
+    (the next reduction then writes instead of accumulating) -- no zero-fill kernel per parameter and no read-modify-
+    write in the reduction.  Other parameters are zeroed (or set to None) as ``torch.optim.Optimizer.zero_grad`` does."""
+    for group in optimizer.param_groups:
+        for p in group["params"]:
+            if p.grad is None:
+                continue
+            if getattr(p, "_bmt_bucket", None) is not None:
+                p.grad = None
+            elif getattr(p, "_in_block", False):
+                p.grad = None
+                bucket, _ = p._block_owner()._slot_of[id(p)]
+                bucket.storage.grad = None
+            elif set_to_none:
+                p.grad = None
+            else:
+                p.grad.detach_()
+                p.grad.requires_grad_(False)
+                p.grad.zero_()
+
+
 class AdamOptimizer(torch.optim.Optimizer):
     """Adam for fp32 / fp16 / bf16 parameters living on the device."""
 
@@ -165,4 +189,4 @@ class AdamOptimizer(torch.optim.Optimizer):
         self.__setstate__({"state": state, "param_groups": param_groups})
 
     def zero_grad(self, set_to_none: bool = False):
-        super().zero_grad(set_to_none=set_to_none)
+        _zero_grad(self, set_to_none)

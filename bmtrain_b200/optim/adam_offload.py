@@ -21,7 +21,7 @@ import torch
 
 from ..ops import adam as _adam
 from ._distributed import state_dict_gather
-from .adam import _partition_bounds
+from .adam import _partition_bounds, _zero_grad
 
 _CHUNK = 1 << 23  # elements per pipeline stage (16 MiB of half data)
 
@@ -470,4 +470,4 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
             for ev in self._staged.values():
                 ev.synchronize()
             self._staged.clear()
-        super().zero_grad(set_to_none=set_to_none)
+        _zero_grad(self, set_to_none)
