@@ -1,0 +1,203 @@
+"""Timings of the four fused compute+collective paths against the same work done as NCCL collective + separate kernels.
+
+Run on W GPUs of one NVLink domain::
+
+    python -m torch.distributed.run --nproc-per-node W --master-addr 127.0.0.1 -m bmtrain_b200.benchmark.fused
+
+Every number is device-timed with CUDA events after warm-up, the maximum over ranks, with a large scratch write between
+iterations so the operands do not sit in L2.  For each path the report gives
+
+* ``fused``: the single kernel working on peer memory,
+* ``split``: NCCL collective followed by (or following) this package's plain kernels,
+* ``roofline``: the slower of the arithmetic at the measured sustained GEMM rate and the bytes that have to cross
+  NVLink at the measured peer-copy bandwidth (both overridable on the command line),
+* ``fraction`` = roofline / fused.
+
+(The reference has no counterpart: its collectives and GEMMs are separate NCCL / cuBLAS calls.)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+import bmtrain_b200 as bmt
+from bmtrain_b200.global_var import config
+
+
+def _timer(fn, iters: int, warmup: int, flush) -> float:
+    comm = config["comm"]
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    comm.barrier()
+    total = 0.0
+    for _ in range(iters):
+        flush.add_(1.0)
+        comm.barrier()  # ranks enter together: a fused kernel's waits then measure transfer, not skew
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        total += start.elapsed_time(end)
+    t = torch.tensor([total / iters], dtype=torch.float32, device=config["device"])
+    comm.all_reduce(t, "max")
+    return float(t.item())
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192, help="tokens of the whole tensor-parallel group")
+    ap.add_argument("--hidden", type=int, default=5120)
+    ap.add_argument("--ffn", type=int, default=13824)
+    ap.add_argument("--block-dim", type=int, default=2560, help="hidden size of the ZeRO block (paths 1 and 2)")
+    ap.add_argument("--block-ffn", type=int, default=8192)
+    ap.add_argument("--block-tokens", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--gemm-tflops", type=float, default=1355.4, help="sustained dense bf16 rate used for the roofline")
+    ap.add_argument("--link-gbs", type=float, default=770.0, help="peer-copy bandwidth per direction per GPU")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    args = ap.parse_args()
+    os.environ.setdefault("BMT_QUIET", "1")
+    bmt.init_distributed(seed=0)
+    comm, dev = config["comm"], config["device"]
+    W, rank = comm.size, comm.rank
+    dt = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    from bmtrain_b200.ops import gemm as G
+    from bmtrain_b200.ops import infnan
+    from bmtrain_b200.parallel import fused_ops, symm, tp_fused
+
+    rt = symm.peer_runtime(comm)
+    if rt is None:
+        raise SystemExit("peer memory is not available between these ranks")
+    flush = torch.zeros(96 * 1024 * 1024, dtype=torch.float32, device=dev)  # 384 MiB > L2
+    rows = []
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+
+    def rnd(*shape):
+        return (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * 0.05).to(dt)
+
+    def report(name, shape, fused_ms, split_ms, flops, link_bytes, extra=None):
+        roof_ms = max(flops / (args.gemm_tflops * 1e9), link_bytes / (args.link_gbs * 1e6))
+        row = {"path": name, "ranks": W, "shape": shape, "fused_ms": round(fused_ms, 4), "split_ms": round(split_ms, 4),
+               "roofline_ms": round(roof_ms, 4), "fraction_of_roofline": round(roof_ms / fused_ms, 3),
+               "speedup_vs_split": round(split_ms / fused_ms, 3)}
+        if extra:
+            row.update(extra)
+        rows.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+
+    # ---------------------------------------------------------- (3) all-gather -> GEMM (column-parallel input gather)
+    M, K, N = args.tokens, args.hidden, 3 * args.hidden // W
+    x_loc, w = rnd(M // W, K), rnd(N, K)
+    x_all = torch.empty(M, K, dtype=dt, device=dev)
+
+    def split_ag():
+        comm.all_gather_into(x_all, x_loc)
+        return G.gemm_nt(x_all, w)
+
+    def lib_ag():
+        comm.all_gather_into(x_all, x_loc)
+        return x_all @ w.t()
+
+    before = fused_ops.calls["ag_gemm"]
+    t_f = _timer(lambda: tp_fused.all_gather_gemm(x_loc, w, None, comm), args.iters, args.warmup, flush)
+    assert fused_ops.calls["ag_gemm"] > before, "fused all-gather -> GEMM did not run"
+    t_s = _timer(split_ag, args.iters, args.warmup, flush)
+    t_l = _timer(lib_ag, args.iters, args.warmup, flush)
+    report("(3) all-gather -> GEMM", [M, N, K], t_f, t_s, 2.0 * M * N * K, (W - 1) * (M // W) * K * 2,
+           {"nccl_plus_library_gemm_ms": round(t_l, 4)})
+
+    # ------------------------------------------------------- (4) GEMM -> reduce-scatter (row-parallel output scatter)
+    M, K, N = args.tokens, args.ffn // W // 8 * 8, args.hidden
+    x, w = rnd(M, K), rnd(N, K)
+    out = torch.empty(M // W, N, dtype=dt, device=dev)
+
+    def split_rs():
+        full = G.gemm_nt(x, w)
+        comm.reduce_scatter_into(out, full, "sum")
+
+    def lib_rs():
+        full = x @ w.t()
+        comm.reduce_scatter_into(out, full, "sum")
+
+    before = fused_ops.calls["gemm_rs"]
+    t_f = _timer(lambda: tp_fused.gemm_reduce_scatter(x, w, None, comm), args.iters, args.warmup, flush)
+    assert fused_ops.calls["gemm_rs"] > before, "fused GEMM -> reduce-scatter did not run"
+    t_s = _timer(split_rs, args.iters, args.warmup, flush)
+    t_l = _timer(lib_rs, args.iters, args.warmup, flush)
+    report("(4) GEMM -> reduce-scatter", [M, N, K], t_f, t_s, 2.0 * M * N * K, (W - 1) * (M // W) * N * 2,
+           {"nccl_plus_library_gemm_ms": round(t_l, 4)})
+
+    # --------------------------- (2) gradient reduce-scatter + fp32 accumulate + scale + inf/nan (one block's gradients)
+    d, f = args.block_dim, args.block_ffn
+    block_params = 4 * d * d + 2 * d * f + 9 * d + f
+    part = (block_params + W - 1) // W // 256 * 256
+    full = rt.slot(("bench_rs",), W * part * 2)
+    full.tensor(dt, W * part).copy_(rnd(W * part))
+    acc = rnd(part)
+    row = rt.row(("bench_rs", "row"))
+    plain_full = full.tensor(dt, W * part).clone()
+    tmp = torch.empty(part, dtype=dt, device=dev)
+    flag = torch.zeros(1, dtype=torch.uint8, device=dev)
+
+    def fused_rs():
+        rt.reduce_scatter(full, row, part, acc, accumulate=True, scale=1.0)
+
+    def split_grad_rs():
+        comm.reduce_scatter_into(tmp, plain_full, "sum")
+        acc.add_(tmp)
+        infnan.has_inf_nan(acc, flag)
+
+    t_f = _timer(fused_rs, args.iters, args.warmup, flush)
+    t_s = _timer(split_grad_rs, args.iters, args.warmup, flush)
+    report("(2) grad reduce-scatter + accumulate + inf/nan", [W, part], t_f, t_s, 0.0, (W - 1) * part * 2)
+    rt.check()
+
+    # ------------------------------------------------- (1) ZeRO-3 gather fused with the block's first GEMM (forward)
+    from bmtrain_b200.block_layer import Block, TransformerBlockList
+    from bmtrain_b200.models.gpt import TransformerEncoder
+
+    def make(zero_level):
+        torch.manual_seed(0)
+        blk = Block(TransformerEncoder(d, d // 32, 32, f, bias=True, dtype=dt), use_checkpoint=True, zero_level=zero_level)
+        lst = TransformerBlockList([blk])
+        bmt.init_parameters(lst)
+        return lst
+
+    hidden = rnd(2, args.block_tokens // 2, d)
+    mask = torch.ones(2, args.block_tokens // 2, dtype=torch.bool, device=dev)
+
+    def fwd(lst):
+        return lst(hidden, mask)  # grad mode on: a ZeRO-2 block then keeps its gathered parameters between calls
+
+    z3 = make(3)
+    before = fused_ops.calls["zero_gather_gemm"]
+    os.environ["BMT_FUSED_GATHER"] = "1"
+    t_f = _timer(lambda: fwd(z3), args.iters, args.warmup, flush)
+    ran_fused = fused_ops.calls["zero_gather_gemm"] > before
+    os.environ["BMT_FUSED_GATHER"] = "0"
+    t_s = _timer(lambda: fwd(z3), args.iters, args.warmup, flush)
+    os.environ["BMT_FUSED_GATHER"] = "1"
+    z2 = make(2)
+    t_res = _timer(lambda: fwd(z2), args.iters, args.warmup, flush)  # parameters stay gathered: compute only
+    tok = args.block_tokens
+    flops = 2.0 * tok * (4 * d * d + 2 * d * f) + 4.0 * tok * (tok // 2) * d
+    report("(1) ZeRO-3 gather + block forward (first GEMM fused with the gather)", [tok, d, f], t_f, t_s, flops,
+           (W - 1) * part * 2, {"fused_kernel_ran": ran_fused, "compute_only_ms": round(t_res, 4),
+                                "roofline_note": "roofline uses max(link time, arithmetic); compute_only_ms is the same "
+                                                 "block with resident parameters"})
+    rt.check()
+    bmt.synchronize()
+    if rank == 0:
+        print(json.dumps({"summary": rows}))
+    bmt.shutdown()
+
+
+if __name__ == "__main__":
+    main()
