@@ -149,19 +149,29 @@ def build_reference(opt_kind="offload"):
 def main():
     args = parse()
     setup_env(args)
+    # stdout carries exactly one line, the JSON result: everything libraries print (NCCL banner, loss-scale notices of
+    # either arm) goes to stderr instead
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        sys.stdout.flush()
+        os.write(result_fd, (json.dumps(obj) + "\n").encode())
+
     if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "bmtrain")):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"}))
+        emit({"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"})
         return
     import torch
 
     if not torch.cuda.is_available():
-        print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
+        emit({"impl": args.impl, "unavailable": "no CUDA device"})
         return
     try:
         bmt, model, om, loss_of, launch_count = (build_reference if args.impl == "reference" else build_ours)(args.optimizer)
     except Exception as exc:  # the reference may fail to import/run on this image
         if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}))
+            emit({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"})
             return
         raise
     rank, world = bmt.rank(), bmt.world_size()
@@ -249,7 +259,7 @@ def main():
             "gpu_launches": launches,
             "overflow_skipped_steps": {"device_timed": skip_dev, "e2e": skip_e2e},
         }
-        print(json.dumps(out))
+        emit(out)
     try:
         if torch.distributed.is_initialized():
             torch.distributed.destroy_process_group()

@@ -41,6 +41,7 @@ struct GemmParams {
     int64_t M, N, K;
     int bn;           // tile N
     int stages;
+    uint32_t hdr_off;      // byte offset of the barrier header behind the tile stages (pusher CTAs need room for their ring)
     int a_mn, b_mn;   // 1 = MN-major operand
     int m_blocks, n_blocks;
     int64_t batch_inner, batch_outer, b_inner_div;
@@ -426,7 +427,8 @@ struct FusedComm {
     int64_t ag_ld_src, ag_rows;
     void* ag_dst[8];          // every rank's gathered buffer (world * ag_rows x K, pitch K)
     unsigned int* ag_count[8];// every rank's per-row-block counters
-    int ag_piece_rows;        // rows copied per piece; BM / ag_piece_rows pieces per row block
+    int ag_piece_bytes;       // bytes per pushed piece: divides the bytes of a 128-row block, at most PUSH_PIECE_BYTES
+    int ag_pieces_per_block;  // pieces per 128-row block = what a block's counter grows by per epoch
     // mode 3 (ZeRO weight gather -> GEMM): the B operand (N x K, rows contiguous) is cut over the ranks as a flat element
     // range; every rank pushes its part to all ranks in pieces and the TMA producer waits for the 128-row chunks it needs
     const char* bg_src;       // this rank's part (local shard memory)
@@ -436,7 +438,7 @@ struct FusedComm {
     const unsigned int* bg_expected;  // pieces a chunk receives in total, per chunk
     int bg_first_block;       // n-block at which this rank's own rows start (tile order is rotated to begin there)
 };
-constexpr int64_t BG_PIECE = 8192;  // elements per pushed piece (16 KiB)
+constexpr int64_t BG_PIECE = 16384;  // elements per pushed piece (32 KiB = one stage of the push pipeline)
 
 __device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -459,6 +461,77 @@ __device__ __forceinline__ bool wait_counter(const unsigned int* p, unsigned int
     }
 }
 
+// ---- push pipeline of a pusher CTA ---------------------------------------------------------------------------------
+// One thread moves pieces of local global memory to a (peer or local) destination through a ring of shared-memory
+// stages with bulk asynchronous copies: global -> shared completes on an mbarrier, shared -> global is tracked in bulk
+// groups.  Up to PUSH_AHEAD loads and PUSH_PENDING + 1 stores are in flight at a time; a piece's counter on the
+// destination is bumped only after its store has completed (full wait_group, proxy fence, system fence).
+constexpr int PUSH_STAGES = 6, PUSH_AHEAD = 3, PUSH_PENDING = 3;
+constexpr uint32_t PUSH_PIECE_BYTES = 32768;
+
+struct PushMeta {
+    char* dst[PUSH_STAGES];
+    unsigned int* cnt[PUSH_STAGES];
+    uint32_t bytes[PUSH_STAGES];
+};
+
+struct PushPipe {
+    uint32_t buf0, bar0;     // shared addresses: first stage, first mbarrier (8 bytes apart)
+    PushMeta* meta;          // in shared memory
+    int64_t n_loaded, n_stored, n_sig;
+
+    __device__ __forceinline__ void init(uint32_t buf, uint32_t bar, PushMeta* m) {
+        buf0 = buf; bar0 = bar; meta = m; n_loaded = n_stored = n_sig = 0;
+    }
+    __device__ __forceinline__ void retire(int64_t upto) {
+        if (upto <= n_sig) return;
+        asm volatile("fence.proxy.async.global;" ::: "memory");  // the stores went through the async proxy
+        __threadfence_system();
+        for (; n_sig < upto; ++n_sig) {
+            unsigned int* c = meta->cnt[n_sig % PUSH_STAGES];
+            if (c) atomicAdd_system(c, 1u);
+        }
+    }
+    // Issue the store of the oldest loaded piece (if any) and retire stores beyond the pending limit.
+    __device__ __forceinline__ bool advance() {
+        if (n_stored < n_loaded) {
+            const int s = (int)(n_stored % PUSH_STAGES);
+            if (!mbar_wait_u32(bar0 + 8 * s, (uint32_t)((n_stored / PUSH_STAGES) & 1))) return false;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                         ::"l"(meta->dst[s]), "r"(buf0 + s * PUSH_PIECE_BYTES), "r"(meta->bytes[s]) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            ++n_stored;
+        }
+        if (n_stored - n_sig > PUSH_PENDING) {
+            asm volatile("cp.async.bulk.wait_group %0;" ::"n"(PUSH_PENDING) : "memory");
+            retire(n_stored - PUSH_PENDING);
+        }
+        return true;
+    }
+    // Queue one piece: bytes is a multiple of 16 and at most PUSH_PIECE_BYTES, both addresses are 16-byte aligned.
+    __device__ __forceinline__ bool submit(const char* src, char* dst, unsigned int* cnt, uint32_t bytes) {
+        while (n_loaded - n_sig >= PUSH_STAGES || n_loaded - n_stored >= PUSH_AHEAD) {
+            if (!advance()) return false;
+        }
+        const int s = (int)(n_loaded % PUSH_STAGES);
+        meta->dst[s] = dst; meta->cnt[s] = cnt; meta->bytes[s] = bytes;
+        mbar_expect_tx_u32(bar0 + 8 * s, bytes);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(buf0 + s * PUSH_PIECE_BYTES), "l"(src), "r"(bytes), "r"(bar0 + 8 * s) : "memory");
+        ++n_loaded;
+        return true;
+    }
+    // Store what is loaded, wait for every store, signal the rest.  On a failed load wait the stores already issued are
+    // still waited for (they read this CTA's shared memory).
+    __device__ __forceinline__ bool drain() {
+        bool ok = true;
+        while (ok && n_stored < n_loaded) ok = advance();
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        retire(n_stored);
+        return ok;
+    }
+};
+
 template <bool CTA2, int FUSED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p,
@@ -472,7 +545,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const uint32_t a_bytes = BM * BK * 2;
     const uint32_t b_bytes = bn_local * BK * 2;
     const uint32_t stage_bytes = a_bytes + b_bytes;
-    SharedHeader* hdr = (SharedHeader*)(smem + (size_t)p.stages * stage_bytes);
+    SharedHeader* hdr = (SharedHeader*)(smem + p.hdr_off);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (int)((p.K + BK - 1) / BK);
@@ -485,7 +558,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const uint32_t tmem_cols = 2 * p.bn <= 32 ? 32 : 2 * p.bn <= 64 ? 64 : 2 * p.bn <= 128 ? 128 : 2 * p.bn <= 256 ? 256 : 512;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) { mbar_init(&hdr->full[s], 1); mbar_init(&hdr->empty[s], 1); }
+        for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(&hdr->full[s], 1); mbar_init(&hdr->empty[s], 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(&hdr->tmem_full[a], 1); mbar_init(&hdr->tmem_empty[a], 4 * NCTA); }
         hdr->failed = 0;
         fence_barrier_init();
@@ -505,91 +578,67 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         st_release_sys_u32(f.flags[threadIdx.x] + f.free_row * f.world + f.rank, f.epoch);
     }
 
-    if (comm_cta && FUSED == 3) {
-        // ------------------------------------------------------------------ weight pusher (whole CTA)
+    if (comm_cta && threadIdx.x == 0) {
+        // ------------------------------------------------------------------ pusher (one thread drives bulk copies)
+        __shared__ PushMeta push_meta;
+        PushPipe pipe;
+        pipe.init(smem_u32(smem), smem_u32(&hdr->full[0]), &push_meta);
         const int n_pushers = f.ag_ctas, me = (int)blockIdx.x - compute_ctas;
-        const int64_t CK = (int64_t)BM * p.K;                       // elements per 128-row chunk
-        const int64_t lo_all = f.bg_first, hi_all = f.bg_first + f.bg_count;
-        bool ok = f.bg_count > 0;
-        for (int di = 0; di < f.world && ok; ++di) {
-            const int dst = (f.rank + di) % f.world;
-            if (dst != f.rank) {
-                __shared__ int free_ok3;
-                if (threadIdx.x == 0) free_ok3 = wait_counter(f.flags[f.rank] + f.free_row * f.world + dst, f.epoch, f.limit_ns) ? 1 : 0;
-                __syncthreads();
-                if (!free_ok3) { if (threadIdx.x == 0) { atomicCAS(f.status, 0, 0x800 | f.rank); atomicCAS(&g_gemm_status, 0, (9 << 16) | (blockIdx.x & 0xffff)); } ok = false; break; }
+        bool ok = true;
+        unsigned int free_seen = 1u << f.rank;   // destinations whose "free for this epoch" flag has been observed
+        auto dst_free = [&](int dst) -> bool {
+            if (free_seen & (1u << dst)) return true;
+            if (!wait_counter(f.flags[f.rank] + f.free_row * f.world + dst, f.epoch, f.limit_ns)) {
+                atomicCAS(f.status, 0, (FUSED == 3 ? 0x800 : 0x300) | f.rank);
+                atomicCAS(&g_gemm_status, 0, ((FUSED == 3 ? 9 : 5) << 16) | (blockIdx.x & 0xffff));
+                return false;
             }
-            int64_t g = 0;
-            for (int64_t c = lo_all / CK; c * CK < hi_all; ++c) {
-                const int64_t lo = lo_all > c * CK ? lo_all : c * CK;
-                const int64_t hi = hi_all < (c + 1) * CK ? hi_all : (c + 1) * CK;
-                for (int64_t e0 = lo; e0 < hi; e0 += BG_PIECE, ++g) {
-                    if (g % n_pushers != me) continue;
-                    const int64_t n = ((hi - e0 < BG_PIECE ? hi - e0 : BG_PIECE) * 2) / 16;
-                    const int4* sp = reinterpret_cast<const int4*>(f.bg_src + (e0 - lo_all) * 2);
-                    int4* dp = reinterpret_cast<int4*>((char*)f.bg_dst[dst] + e0 * 2);
-                    for (int64_t v = threadIdx.x; v < n; v += NUM_THREADS * 4) {
-                        int4 t[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) if (v + u * NUM_THREADS < n) t[u] = sp[v + u * NUM_THREADS];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) if (v + u * NUM_THREADS < n) dp[v + u * NUM_THREADS] = t[u];
+            free_seen |= 1u << dst;
+            return true;
+        };
+        if (FUSED == 3) {
+            // weight pusher: this rank's flat element range, cut at 128-row chunk boundaries, to every rank (own first)
+            const int64_t CK = (int64_t)BM * p.K;                       // elements per 128-row chunk
+            const int64_t lo_all = f.bg_first, hi_all = f.bg_first + f.bg_count;
+            for (int di = 0; di < f.world && ok && f.bg_count > 0; ++di) {
+                // own copy first, then rank-1, rank-2, ...: a rank multiplies its own rows first and continues with the
+                // rows of rank+1, rank+2, ..., so it should receive from those sources in that order
+                const int dst = (f.rank - di + f.world) % f.world;
+                int64_t g = 0;
+                for (int64_t c = lo_all / CK; c * CK < hi_all && ok; ++c) {
+                    const int64_t lo = lo_all > c * CK ? lo_all : c * CK;
+                    const int64_t hi = hi_all < (c + 1) * CK ? hi_all : (c + 1) * CK;
+                    for (int64_t e0 = lo; e0 < hi && ok; e0 += BG_PIECE, ++g) {
+                        if (g % n_pushers != me) continue;
+                        if (!dst_free(dst)) { ok = false; break; }
+                        const uint32_t bytes = (uint32_t)((hi - e0 < BG_PIECE ? hi - e0 : BG_PIECE) * 2);
+                        ok = pipe.submit(f.bg_src + (e0 - lo_all) * 2, (char*)f.bg_dst[dst] + e0 * 2, f.bg_cnt[dst] + c, bytes);
                     }
-                    __syncthreads();
-                    if (threadIdx.x == 0) { __threadfence_system(); atomicAdd_system(f.bg_cnt[dst] + c, 1u); }
                 }
             }
+        } else {
+            // all-gather pusher: this rank's rows (contiguous) to every rank's gathered matrix, destination-major
+            // starting with this rank itself, then rank-1, rank-2, ... (the order in which the consumers get to them)
+            const int64_t block_bytes = (int64_t)BM * p.K * 2;
+            const int64_t ppb = f.ag_pieces_per_block, per_dst = (int64_t)blocks_per_rank * ppb;
+            const int64_t total_pieces = (int64_t)f.world * per_dst;
+            for (int64_t g = me; g < total_pieces && ok; g += n_pushers) {
+                const int dst = (f.rank - (int)(g / per_dst) + f.world) % f.world;
+                const int64_t rem = g % per_dst;
+                const int64_t blk = rem / ppb, piece = rem % ppb;
+                if (!dst_free(dst)) { ok = false; break; }
+                const int64_t off = blk * block_bytes + piece * (int64_t)f.ag_piece_bytes;
+                ok = pipe.submit((const char*)f.ag_src + off, (char*)f.ag_dst[dst] + (int64_t)f.rank * f.ag_rows * p.K * 2 + off,
+                                 f.ag_count[dst] + (f.rank * blocks_per_rank + blk), (uint32_t)f.ag_piece_bytes);
+            }
+        }
+        if (!pipe.drain()) ok = false;
+        if (!ok) {
+            hdr->failed = 1;
+            atomicCAS(&g_gemm_status, 0, (11 << 16) | (blockIdx.x & 0xffff));
         }
     } else if (comm_cta) {
-        // ------------------------------------------------------------------ all-gather pusher (whole CTA)
-        const int n_pushers = f.ag_ctas, me = (int)blockIdx.x - compute_ctas;
-        const int pieces_per_block = BM / f.ag_piece_rows;
-        const int64_t row_bytes = p.K * 2;
-        const int64_t total_pieces = (int64_t)f.world * blocks_per_rank * pieces_per_block;
-        bool ok = true;
-        for (int64_t g = me; g < total_pieces && ok; g += n_pushers) {
-            // destination-major order starting with this rank itself, then the peers in ring order
-            const int dsti = (int)(g / ((int64_t)blocks_per_rank * pieces_per_block));
-            const int dst = (f.rank + dsti) % f.world;
-            const int64_t rem = g % ((int64_t)blocks_per_rank * pieces_per_block);
-            const int blk = (int)(rem / pieces_per_block), piece = (int)(rem % pieces_per_block);
-            if (dst != f.rank) {
-                __shared__ int free_ok;
-                if (threadIdx.x == 0) free_ok = wait_counter(f.flags[f.rank] + f.free_row * f.world + dst, f.epoch, f.limit_ns) ? 1 : 0;
-                __syncthreads();
-                if (!free_ok) { if (threadIdx.x == 0) { atomicCAS(f.status, 0, 0x300 | f.rank); atomicCAS(&g_gemm_status, 0, (5 << 16) | (blockIdx.x & 0xffff)); } ok = false; break; }
-            }
-            const int64_t src_row0 = (int64_t)blk * BM + (int64_t)piece * f.ag_piece_rows;
-            const int64_t dst_row0 = (int64_t)f.rank * f.ag_rows + src_row0;
-            const int64_t vec_per_row = row_bytes / 16;
-            const int64_t nvec = (int64_t)f.ag_piece_rows * vec_per_row;
-            const char* src = (const char*)f.ag_src;
-            char* dstp = (char*)f.ag_dst[dst];
-            for (int64_t v = threadIdx.x; v < nvec; v += NUM_THREADS * 4) {
-                int4 buf[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int64_t vv = v + (int64_t)u * NUM_THREADS;
-                    if (vv < nvec) {
-                        const int64_t r = vv / vec_per_row, cidx = vv % vec_per_row;
-                        buf[u] = *reinterpret_cast<const int4*>(src + (src_row0 + r) * f.ag_ld_src * 2 + cidx * 16);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int64_t vv = v + (int64_t)u * NUM_THREADS;
-                    if (vv < nvec) {
-                        const int64_t r = vv / vec_per_row, cidx = vv % vec_per_row;
-                        *reinterpret_cast<int4*>(dstp + (dst_row0 + r) * row_bytes + cidx * 16) = buf[u];
-                    }
-                }
-            }
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                __threadfence_system();
-                atomicAdd_system(f.ag_count[dst] + (f.rank * blocks_per_rank + blk), 1u);
-            }
-        }
+        // the other threads of a pusher CTA have nothing to do
     } else if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one per CTA)
         if (lane == 0) {
@@ -619,7 +668,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 if (FUSED == 2) {
                     // local row blocks first, then the peers' blocks in the order in which they are pushed
                     m_blk = (m_blk + f.rank * blocks_per_rank) % p.m_blocks;
-                    const unsigned int target = f.epoch * (unsigned int)(BM / f.ag_piece_rows);
+                    const unsigned int target = f.epoch * (unsigned int)f.ag_pieces_per_block;
                     if (!wait_counter(f.ag_count[f.rank] + m_blk, target, f.limit_ns)) {
                         ok = false; atomicCAS(f.status, 0, 0x400 | f.rank); atomicCAS(&g_gemm_status, 0, (6 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break;
                     }
@@ -997,7 +1046,9 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     if (rc) return rc;
 
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * batch_inner * batch_outer;
-    const size_t smem = (size_t)p.stages * stage_bytes + sizeof(SharedHeader) + 1024;
+    p.hdr_off = (uint32_t)p.stages * stage_bytes;
+    if (comm_ctas > 0 && p.hdr_off < PUSH_STAGES * PUSH_PIECE_BYTES) p.hdr_off = PUSH_STAGES * PUSH_PIECE_BYTES;
+    const size_t smem = (size_t)p.hdr_off + sizeof(SharedHeader) + 1024;
     FusedComm none;
     memset(&none, 0, sizeof(none));
     if (fused) {
@@ -1102,13 +1153,17 @@ extern "C" int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank,
                                    unsigned int epoch, const void* src, int64_t ld_src, int64_t rows, void* const* gathered,
                                    void* const* counters, int comm_ctas, void* status_i32, double timeout_s, void* stream) {
     if (world < 2 || world > 8 || desc->m != rows * world || rows % BM != 0 || desc->a_major != 0) return -42;
-    if (desc->k % 8 != 0 || desc->lda != desc->k) return -43;
+    if (desc->k % 8 != 0 || desc->lda != desc->k || ld_src != desc->k || ((uintptr_t)src & 15)) return -43;
     FusedComm f;
     memset(&f, 0, sizeof(f));
     f.mode = 2; f.world = world; f.rank = rank; f.free_row = free_row; f.epoch = epoch;
     f.status = (int*)status_i32; f.limit_ns = (uint64_t)(timeout_s * 1e9);
     for (int j = 0; j < world; ++j) { f.flags[j] = (unsigned int*)flags[j]; f.ag_dst[j] = gathered[j]; f.ag_count[j] = (unsigned int*)counters[j]; }
-    f.ag_ctas = comm_ctas; f.ag_src = src; f.ag_ld_src = ld_src; f.ag_rows = rows; f.ag_piece_rows = 16;
+    f.ag_ctas = comm_ctas; f.ag_src = src; f.ag_ld_src = ld_src; f.ag_rows = rows;
+    // a 128-row block has 256 * K bytes = 2048 * (K / 8): pieces of 2048 * d bytes with d the largest divisor of K / 8 up to 16
+    int d = 16;
+    while ((desc->k / 8) % d) --d;
+    f.ag_piece_bytes = 2048 * d; f.ag_pieces_per_block = (int)(desc->k / 8) / d;
     BmtGemmDesc g = *desc;
     g.batch_inner = g.batch_outer = g.b_inner_div = 1;
     return launch_gemm(g, (cudaStream_t)stream, &f);

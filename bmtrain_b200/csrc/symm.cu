@@ -80,8 +80,10 @@ struct RsArgs {
     uint64_t limit_ns;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256) fused_rs_kernel(RsArgs a) {
+// WMAX: upper bound of the group size (loads of all ranks are issued before the first add); U: vectors per thread per
+// trip.  WMAX * U independent 16-byte loads are in flight per thread, which is what hides the NVLink round trip.
+template <typename T, int WMAX, int U>
+__global__ void __launch_bounds__(256, 2) fused_rs_kernel(RsArgs a) {
     __shared__ int ok_s;
     // 1. tell every rank that this rank's buffer (written by earlier kernels of this stream) is complete
     if (blockIdx.x == 0 && threadIdx.x < a.world) {
@@ -99,38 +101,58 @@ __global__ void __launch_bounds__(256) fused_rs_kernel(RsArgs a) {
     // 3. this rank's partition: sum over ranks in rank order (fp32), scale, accumulate, inf/nan, write
     const int64_t base = (int64_t)a.rank * a.part;
     const int64_t nvec = a.part / 8;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     T* __restrict__ out = (T*)a.out;
     bool bad = false;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        bmt::Vec16<T> v[8];
+    for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+        bmt::Vec16<T> v[U][WMAX];
+        bmt::Vec16<T> old[U];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (j < a.world) v[j] = bmt::ld16((const T*)a.peer[j] + base + i * 8);
+        for (int u = 0; u < U; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i < nvec) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (j < a.world) {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) acc[k] += bmt::Cvt<T>::to_f(v[j].v[k]);
+                for (int j = 0; j < WMAX; ++j)
+                    if (j < a.world) v[u][j] = bmt::ld16((const T*)a.peer[j] + base + i * 8);
+                if (a.accumulate) old[u] = bmt::ld16(out + i * 8);
             }
-        bmt::Vec16<T> o;
-        if (a.accumulate) {
-            bmt::Vec16<T> old = bmt::ld16(out + i * 8);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = acc[k] * a.scale + bmt::Cvt<T>::to_f(old.v[k]);
-        } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] *= a.scale;
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            bad |= !(fabsf(acc[k]) <= 3.402823466e38f);
-            o.v[k] = bmt::Cvt<T>::from_f(acc[k]);
-            bad |= !(fabsf(bmt::Cvt<T>::to_f(o.v[k])) <= 3.402823466e38f);
+        for (int u = 0; u < U; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i >= nvec) continue;
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < WMAX; ++j)
+                if (j < a.world) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[k] += bmt::Cvt<T>::to_f(v[u][j].v[k]);
+                }
+            bmt::Vec16<T> o;
+            if (a.accumulate) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = acc[k] * a.scale + bmt::Cvt<T>::to_f(old[u].v[k]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] *= a.scale;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                bad |= !(fabsf(acc[k]) <= 3.402823466e38f);
+                o.v[k] = bmt::Cvt<T>::from_f(acc[k]);
+                bad |= !(fabsf(bmt::Cvt<T>::to_f(o.v[k])) <= 3.402823466e38f);
+            }
+            bmt::st16(out + i * 8, o);
         }
-        bmt::st16(out + i * 8, o);
     }
     if (__syncthreads_or(bad) && threadIdx.x == 0 && a.overflow) *a.overflow = 1;
+}
+
+template <typename T>
+static void launch_fused_rs(const RsArgs& a, unsigned blocks, cudaStream_t s) {
+    if (a.world <= 2) fused_rs_kernel<T, 2, 4><<<blocks, 256, 0, s>>>(a);
+    else if (a.world <= 4) fused_rs_kernel<T, 4, 2><<<blocks, 256, 0, s>>>(a);
+    else fused_rs_kernel<T, 8, 1><<<blocks, 256, 0, s>>>(a);
 }
 
 __global__ void symm_signal_wait_kernel(unsigned int* const* peer_flags_table, unsigned int** unused, int world, int rank, int slot,
@@ -164,7 +186,7 @@ struct PushArgs {
 // epoch; when the whole grid is done the last CTA publishes "delivered" to every rank.
 __global__ void __launch_bounds__(256) push_ranges_kernel(PushArgs a) {
     __shared__ int ok_s;
-    const int64_t piece = 16384;
+    const int64_t piece = 32768;
     for (int di = 0; di < a.world; ++di) {
         const int dst = (a.rank + di) % a.world;
         if (dst != a.rank) {
@@ -185,12 +207,12 @@ __global__ void __launch_bounds__(256) push_ranges_kernel(PushArgs a) {
                 const int64_t n = (a.nbytes[r] - b0 < piece ? a.nbytes[r] - b0 : piece) / 16;
                 const int4* s = reinterpret_cast<const int4*>(a.src[r] + b0);
                 int4* d = reinterpret_cast<int4*>(a.dst[dst] + a.dst_off[r] + b0);
-                for (int64_t v = threadIdx.x; v < n; v += 256 * 4) {
-                    int4 t[4];
+                for (int64_t v = threadIdx.x; v < n; v += 256 * 8) {
+                    int4 t[8];   // 128 bytes in flight per thread: the copy is bound by load latency, not by issue rate
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) if (v + u * 256 < n) t[u] = s[v + u * 256];
+                    for (int u = 0; u < 8; ++u) if (v + u * 256 < n) t[u] = s[v + u * 256];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) if (v + u * 256 < n) d[v + u * 256] = t[u];
+                    for (int u = 0; u < 8; ++u) if (v + u * 256 < n) d[v + u * 256] = t[u];
                 }
             }
         }
@@ -248,8 +270,8 @@ extern "C" int bmt_fused_reduce_scatter(const void* const* peers, void* const* p
     if (blocks > 148 * 4) blocks = 148 * 4;
     if (blocks < 1) blocks = 1;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == BMT_DT_F16) fused_rs_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>(a);
-    else if (dtype == BMT_DT_BF16) fused_rs_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(a);
+    if (dtype == BMT_DT_F16) launch_fused_rs<__half>(a, (unsigned)blocks, s);
+    else if (dtype == BMT_DT_BF16) launch_fused_rs<__nv_bfloat16>(a, (unsigned)blocks, s);
     else return -32;
     bmt_count_launch(1);
     return (int)cudaGetLastError();

@@ -93,9 +93,10 @@ def ag_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     m, K = x_local.shape
     N = weight.shape[1] if b_is_kn else weight.shape[0]
     W = comm.size
-    if (rt is None or x_local.dtype not in _DT or m % 128 or K % 8 or N % 8 or x_local.stride(1) != 1
-            or x_local.stride(0) % 8 or x_local.data_ptr() % 16 or not _tma_ok(weight)):
+    if rt is None or x_local.dtype not in _DT or m % 128 or K % 8 or N % 8 or not _tma_ok(weight):
         return None
+    if not x_local.is_contiguous() or x_local.data_ptr() % 16:
+        x_local = x_local.contiguous()  # the pushers copy flat 32 KiB pieces
     lib = _native.cuda_lib()
     es = x_local.element_size()
     base = ("ag", m, K, x_local.dtype)

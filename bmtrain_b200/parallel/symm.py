@@ -157,7 +157,7 @@ class PeerRuntime:
         lib = _native.cuda_lib()
         n = len(ranges)
         assert n <= 16
-        grid = 32
+        grid = 96
         ckey = key + ("push_counter", n)
         if ckey not in self._counters:
             self._counters[ckey] = torch.zeros(1, dtype=torch.int32, device=config["device"])
