@@ -27,8 +27,17 @@ import bmtrain_b200 as bmt
 from bmtrain_b200.global_var import config
 
 
-def _timer(fn, iters: int, warmup: int, flush) -> float:
+_busy = {}
+
+
+def _timer(fn, iters: int, warmup: int, flush, host_ahead: bool = False) -> float:
+    """Device time of ``fn`` (CUDA events, mean over ``iters``, maximum over ranks).  ``host_ahead``: a long matrix product
+    is queued in front of the start event, so ``fn`` is enqueued while the device is still busy and its host-side cost
+    does not show (the situation of a training step once the host runs ahead of the device)."""
     comm = config["comm"]
+    if host_ahead and not _busy:
+        _busy["a"] = torch.randn(8192, 8192, device=config["device"], dtype=torch.bfloat16)
+        _busy["b"] = torch.randn(8192, 8192, device=config["device"], dtype=torch.bfloat16)
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -38,6 +47,9 @@ def _timer(fn, iters: int, warmup: int, flush) -> float:
         flush.add_(1.0)
         comm.barrier()  # ranks enter together: a fused kernel's waits then measure transfer, not skew
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if host_ahead:
+            for _ in range(3):
+                torch.mm(_busy["a"], _busy["b"])   # about 2.5 ms of device work
         start.record()
         fn()
         end.record()
@@ -45,6 +57,23 @@ def _timer(fn, iters: int, warmup: int, flush) -> float:
         total += start.elapsed_time(end)
     t = torch.tensor([total / iters], dtype=torch.float32, device=config["device"])
     comm.all_reduce(t, "max")
+    return float(t.item())
+
+
+def _host_ms(fn, iters: int) -> float:
+    """Host time to enqueue ``fn`` (no device sync inside the timed part), maximum over ranks."""
+    import time
+
+    total = 0.0
+    for _ in range(iters):
+        torch.cuda.synchronize()
+        config["comm"].barrier()
+        t0 = time.perf_counter()
+        fn()
+        total += time.perf_counter() - t0
+        torch.cuda.synchronize()
+    t = torch.tensor([total / iters * 1e3], dtype=torch.float32, device=config["device"])
+    config["comm"].all_reduce(t, "max")
     return float(t.item())
 
 
@@ -106,12 +135,14 @@ def main() -> None:
         return x_all @ w.t()
 
     before = fused_ops.calls["ag_gemm"]
+    fused_ops.kernel_stats()
     t_f = _timer(lambda: tp_fused.all_gather_gemm(x_loc, w, None, comm), args.iters, args.warmup, flush)
+    stats3 = fused_ops.kernel_stats()
     assert fused_ops.calls["ag_gemm"] > before, "fused all-gather -> GEMM did not run"
     t_s = _timer(split_ag, args.iters, args.warmup, flush)
     t_l = _timer(lib_ag, args.iters, args.warmup, flush)
     report("(3) all-gather -> GEMM", [M, N, K], t_f, t_s, 2.0 * M * N * K, (W - 1) * (M // W) * K * 2,
-           {"nccl_plus_library_gemm_ms": round(t_l, 4)})
+           {"nccl_plus_library_gemm_ms": round(t_l, 4), "kernel_stats": stats3})
 
     # ------------------------------------------------------- (4) GEMM -> reduce-scatter (row-parallel output scatter)
     M, K, N = args.tokens, args.ffn // W // 8 * 8, args.hidden
@@ -127,12 +158,14 @@ def main() -> None:
         comm.reduce_scatter_into(out, full, "sum")
 
     before = fused_ops.calls["gemm_rs"]
+    fused_ops.kernel_stats()
     t_f = _timer(lambda: tp_fused.gemm_reduce_scatter(x, w, None, comm), args.iters, args.warmup, flush)
+    stats4 = fused_ops.kernel_stats()
     assert fused_ops.calls["gemm_rs"] > before, "fused GEMM -> reduce-scatter did not run"
     t_s = _timer(split_rs, args.iters, args.warmup, flush)
     t_l = _timer(lib_rs, args.iters, args.warmup, flush)
     report("(4) GEMM -> reduce-scatter", [M, N, K], t_f, t_s, 2.0 * M * N * K, (W - 1) * (M // W) * N * 2,
-           {"nccl_plus_library_gemm_ms": round(t_l, 4)})
+           {"nccl_plus_library_gemm_ms": round(t_l, 4), "kernel_stats": stats4})
 
     # --------------------------- (2) gradient reduce-scatter + fp32 accumulate + scale + inf/nan (one block's gradients)
     d, f = args.block_dim, args.block_ffn
@@ -159,6 +192,24 @@ def main() -> None:
     report("(2) grad reduce-scatter + accumulate + inf/nan", [W, part], t_f, t_s, 0.0, (W - 1) * part * 2)
     rt.check()
 
+    # ------------------------------- push all-gather kernel alone (moves the block's other parameters in path 1) vs NCCL
+    gbuf = rt.slot(("bench_push",), W * part * 2)
+    p_free, p_done = rt.row(("bench_push", "free")), rt.row(("bench_push", "done"))
+    rt.signal_wait(p_free, 1, signal=True, wait=False)
+    shard = rnd(part)
+    gathered = torch.empty(W * part, dtype=dt, device=dev)
+
+    def push_gather():
+        epoch = rt.next_epoch(p_free)
+        rt.push_ranges(gbuf, [(shard.data_ptr(), rank * part * 2, part * 2)], p_free, p_done, epoch, ("bench_push",))
+        rt.signal_wait(p_done, epoch, signal=False, wait=True)
+        rt.signal_wait(p_free, epoch + 1, signal=True, wait=False)
+
+    t_f = _timer(push_gather, args.iters, args.warmup, flush)
+    t_s = _timer(lambda: comm.all_gather_into(gathered, shard), args.iters, args.warmup, flush)
+    report("(0) push all-gather kernel vs NCCL all-gather", [W, part], t_f, t_s, 0.0, (W - 1) * part * 2)
+    rt.check()
+
     # ------------------------------------------------- (1) ZeRO-3 gather fused with the block's first GEMM (forward)
     from bmtrain_b200.block_layer import Block, TransformerBlockList
     from bmtrain_b200.models.gpt import TransformerEncoder
@@ -179,17 +230,31 @@ def main() -> None:
     z3 = make(3)
     before = fused_ops.calls["zero_gather_gemm"]
     os.environ["BMT_FUSED_GATHER"] = "1"
+    fused_ops.kernel_stats()
     t_f = _timer(lambda: fwd(z3), args.iters, args.warmup, flush)
+    stats1 = fused_ops.kernel_stats()
+    host_f = _host_ms(lambda: fwd(z3), args.iters)
+    t_f_ahead = _timer(lambda: fwd(z3), args.iters, 1, flush, host_ahead=True)
     ran_fused = fused_ops.calls["zero_gather_gemm"] > before
     os.environ["BMT_FUSED_GATHER"] = "0"
     t_s = _timer(lambda: fwd(z3), args.iters, args.warmup, flush)
+    host_s = _host_ms(lambda: fwd(z3), args.iters)
+    t_s_ahead = _timer(lambda: fwd(z3), args.iters, 1, flush, host_ahead=True)
     os.environ["BMT_FUSED_GATHER"] = "1"
     z2 = make(2)
     t_res = _timer(lambda: fwd(z2), args.iters, args.warmup, flush)  # parameters stay gathered: compute only
+    t_res_ahead = _timer(lambda: fwd(z2), args.iters, 1, flush, host_ahead=True)
     tok = args.block_tokens
     flops = 2.0 * tok * (4 * d * d + 2 * d * f) + 4.0 * tok * (tok // 2) * d
     report("(1) ZeRO-3 gather + block forward (first GEMM fused with the gather)", [tok, d, f], t_f, t_s, flops,
-           (W - 1) * part * 2, {"fused_kernel_ran": ran_fused, "compute_only_ms": round(t_res, 4),
+           (W - 1) * part * 2, {"fused_kernel_ran": ran_fused,
+                                "host_ahead_ms": {"fused": round(t_f_ahead, 4), "split": round(t_s_ahead, 4),
+                                                  "compute_only": round(t_res_ahead, 4),
+                                                  "note": "same measurement with the device kept busy while the block is "
+                                                          "enqueued (backward of a training step); fused_ms / split_ms are "
+                                                          "cold starts where the host-side cost of enqueueing shows"},
+                                "host_enqueue_ms": {"fused": round(host_f, 4), "split": round(host_s, 4)},
+                                "kernel_stats": stats1, "compute_only_ms": round(t_res, 4),
                                 "roofline_note": "roofline uses max(link time, arithmetic); compute_only_ms is the same "
                                                  "block with resident parameters"})
     rt.check()

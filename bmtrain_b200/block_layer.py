@@ -368,7 +368,7 @@ class Block(torch.nn.Module):
             b.full = torch.empty(b.total, dtype=b.dtype, device=b.storage.device)
             b.work = b.comm.all_gather_into(b.full, b.storage.data, async_op=True)
 
-    def _try_deferred_gather(self, args) -> bool:
+    def _try_deferred_gather(self, args, backward: bool = False) -> bool:
         """ZeRO gather for a block nobody prefetched, when the inner module can pull its first GEMM's weight itself.
 
         The small parameters (norms, biases) and then the remaining big ones are pushed to all ranks by two kernels on the
@@ -379,7 +379,11 @@ class Block(torch.nn.Module):
 
         mod = self._module
         name = getattr(mod, "_bmt_first_gemm", None)
-        if name is None or os.environ.get("BMT_FUSED_GATHER", "1") == "0" or self._ref_block is not None:
+        # BMT_FUSED_GATHER: "0" never, "1" whenever possible, "auto" (default) only for the recomputation in backward.  The
+        # fused path needs more host work before the first kernel can start; that is hidden while the host runs ahead of
+        # the device (backward) and exposed at the cold start of a forward pass, where the plain all-gather is faster.
+        policy = os.environ.get("BMT_FUSED_GATHER", "auto")
+        if name is None or policy == "0" or (policy == "auto" and not backward) or self._ref_block is not None:
             return False
         if any(b.full is not None for b in self._buckets.values()) or not mod._bmt_can_fuse_first_gemm(*args):
             return False
@@ -414,19 +418,31 @@ class Block(torch.nn.Module):
             rt.signal_wait(done_a, epoch, signal=False, wait=True)
             ev_small = torch.cuda.Event()
             ev_small.record(rt.stream)
-            rt.push_ranges(buf, big, free_row, done_b, epoch, key + ("B",))
-            rt.signal_wait(done_b, epoch, signal=False, wait=True)
-            ev_rest = torch.cuda.Event()
-            ev_rest.record(rt.stream)
+        state = {"ev_rest": None}
+
+        def push_rest(after: Optional[torch.cuda.Event] = None) -> torch.cuda.Event:
+            """Start the push of the remaining big parameters on the peer stream (once); ``after``: an event of the
+            compute stream the push waits for, so it does not compete for NVLink with the first GEMM's own gather."""
+            if state["ev_rest"] is None:
+                with torch.cuda.stream(rt.stream):
+                    if after is not None:
+                        rt.stream.wait_event(after)
+                    rt.push_ranges(buf, big, free_row, done_b, epoch, key + ("B",))
+                    rt.signal_wait(done_b, epoch, signal=False, wait=True)
+                    ev = torch.cuda.Event()
+                    ev.record(rt.stream)
+                state["ev_rest"] = ev
+            return state["ev_rest"]
+
         b.full = buf.tensor(b.dtype, b.total)
         b.full_sym = (rt, free_row, epoch)
         mod._bmt_deferred_gather = dict(rt=rt, buf=buf, bucket=b, slot=slot, epoch=epoch, key=key, free_row=free_row,
-                                        ev_small=ev_small, ev_rest=ev_rest)
+                                        ev_small=ev_small, push_rest=push_rest)
         return True
 
-    def _ensure_gathered(self, args=None) -> None:
+    def _ensure_gathered(self, args=None, backward: bool = False) -> None:
         if args is not None:
-            self._try_deferred_gather(args)
+            self._try_deferred_gather(args, backward)
         self._begin_gather()
         for b in self._buckets.values():
             if b.work is not None:
@@ -565,7 +581,7 @@ class Block(torch.nn.Module):
             self._release_params()
 
     def _enter_backward(self, args=None) -> None:
-        self._ensure_gathered(args)
+        self._ensure_gathered(args, backward=True)
         self._prepare_grads()
         pre = self.pre_module()
         if pre is not None and pre._mode != "PIPE" and pre._zero_level == 3:

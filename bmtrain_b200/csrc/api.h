@@ -160,18 +160,33 @@ int bmt_gemm_reduce_scatter(const BmtGemmDesc* desc, int world, int rank, void* 
 int bmt_gemm_rs_grid(int64_t m, int64_t n, int64_t k, int b_major);
 int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, unsigned int epoch,
                         const void* src, int64_t ld_src, int64_t rows, void* const* gathered, void* const* counters,
-                        int comm_ctas, void* status_i32, double timeout_s, void* stream);
+                        int comm_ctas, int skip_local, void* status_i32, double timeout_s, void* stream);
 
+// skip_local != 0 (both kernels): the caller has already copied this rank's own part into its gathered buffer, the pusher
+// CTAs only serve the peers and the math does not wait for the own part.  bmt_zero_gather_expected must then be given
+// count[rank] = 0 on that rank.
 int bmt_zero_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, unsigned int epoch,
                          const void* src, int64_t first, int64_t count, void* const* weight_on_rank, void* const* counters,
-                         const void* expected_u32, int comm_ctas, void* status_i32, double timeout_s, void* stream);
-int bmt_zero_gather_expected(int64_t n, int64_t k, int world, const int64_t* first, const int64_t* count, unsigned int* out);
+                         const void* expected_u32, int comm_ctas, int skip_local, void* status_i32, double timeout_s,
+                         void* stream);
+int bmt_zero_gather_expected(int64_t n, int64_t k, int world, const int64_t* first, const int64_t* count, int comm_ctas,
+                             unsigned int* out);
 
 // number of kernel launches issued by this library since load (for launch accounting)
 int64_t bmt_launch_count(void);
 void bmt_count_launch(int n);
 // status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out; reading clears it
+// SM copy of nbytes (multiple of 16) between device pointers, either of which may be a mapped peer buffer.
+int bmt_peer_copy(void* dst, const void* src, int64_t nbytes, int grid, void* stream);
+// Number of pusher CTAs that balances math and transfer of a fused all-gather -> GEMM / ZeRO gather -> GEMM kernel.
+int bmt_fused_comm_ctas(double flops, double push_bytes, double remote_bytes);
 int bmt_gemm_status(void);
+// Timing counters of the fused compute+collective GEMM kernels since the last call, in nanoseconds: out[0] sum over
+// compute CTAs of producer time spent waiting for other ranks' data, out[1] longest pusher CTA, out[2] longest CTA,
+// out[3] longest producer wait of one CTA, out[4] kernels counted, out[5] (GEMM -> reduce-scatter) longest wait for the
+// other ranks' deliveries, out[6] longest CTA including the reduce phase, out[7] sum over CTAs of the out[5] wait.
+// Reading clears the counters.
+int bmt_fused_stats(unsigned long long* out);
 
 #ifdef __cplusplus
 }

@@ -36,6 +36,12 @@ constexpr int MAX_STAGES = 8;
 constexpr uint32_t SMEM_BUDGET = 222 * 1024;  // tiles; header, alignment slack and the kernels' small static arrays fit below the 227 KiB limit
 
 __device__ int g_gemm_status = 0;  // 0 = fine; otherwise (code << 16) | blockIdx of the first CTA that gave up
+// Timing of the fused compute+collective kernels since the last read (nanoseconds of %globaltimer):
+// [0] sum over the compute CTAs of the time their producer spent waiting for remote data, [1] longest pusher CTA,
+// [2] longest CTA of any kind (main phase), [3] longest producer wait of one CTA, [4] kernels counted,
+// [5] GEMM -> reduce-scatter: longest wait for the other ranks' deliveries, [6] longest CTA including its reduce phase,
+// [7] sum over CTAs of that wait.
+__device__ unsigned long long g_fused_stats[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 
 struct GemmParams {
     int64_t M, N, K;
@@ -244,6 +250,59 @@ template <typename T> __device__ __forceinline__ void load8(const T* src, float*
     for (int i = 0; i < 8; ++i) v[i] = bmt::Cvt<T>::to_f(o.v[i]);
 }
 
+// Sum of `world` inbox slots (+ bias) for the vectors [v0, v0 + U * stride) step stride: all U * world loads are issued
+// before the first add so that enough bytes are in flight to stream from HBM.
+template <typename T, int U, int WMAX>
+__device__ __forceinline__ void rs_reduce_vectors(const T* inbox, int64_t slot_elems, int world, const T* bias, int64_t N, T* out,
+                                                  int64_t v0, int64_t stride, int64_t nvec) {
+    bmt::Vec16<T> t[U][WMAX];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t v = v0 + u * stride;
+        if (v < nvec) {
+#pragma unroll
+            for (int j = 0; j < WMAX; ++j)
+                if (j < world) t[u][j] = bmt::ld16(inbox + j * slot_elems + v * 8);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t v = v0 + u * stride;
+        if (v >= nvec) continue;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < WMAX; ++j)
+            if (j < world) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += bmt::Cvt<T>::to_f(t[u][j].v[i]);
+            }
+        if (bias) {
+            float b[8];
+            load8(bias + (v * 8) % N, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += b[i];
+        }
+        store8(out + v * 8, acc);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void rs_reduce_all(const void* inbox, int64_t slot_elems, int world, const void* bias, int64_t N, void* out,
+                                              int64_t nvec) {
+    const int64_t stride = (int64_t)gridDim.x * NUM_THREADS;
+    const int64_t first = (int64_t)blockIdx.x * NUM_THREADS + threadIdx.x;
+    if (world <= 2) {
+        for (int64_t v = first; v < nvec; v += stride * 8)
+            rs_reduce_vectors<T, 8, 2>((const T*)inbox, slot_elems, world, (const T*)bias, N, (T*)out, v, stride, nvec);
+    } else if (world <= 4) {
+        for (int64_t v = first; v < nvec; v += stride * 4)
+            rs_reduce_vectors<T, 4, 4>((const T*)inbox, slot_elems, world, (const T*)bias, N, (T*)out, v, stride, nvec);
+    } else {
+        for (int64_t v = first; v < nvec; v += stride * 2)
+            rs_reduce_vectors<T, 2, 8>((const T*)inbox, slot_elems, world, (const T*)bias, N, (T*)out, v, stride, nvec);
+    }
+}
+
 // Grouped raster: the CTAs that run at the same time cover a compact (group_m x ~#SM/group_m) patch of output tiles, so
 // every k-slice of A and B that one of them pulls from DRAM is found in L2 by the others.
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int64_t rem, int& m_blk, int& n_blk) {
@@ -422,13 +481,16 @@ struct FusedComm {
     void* rs_out;             // rs_rows x N
     const void* rs_bias;
     // mode 2
+    int skip_local;           // modes 2/3: this rank's own part is already in its gathered buffer (copied before the launch)
     int ag_ctas;
     const void* ag_src;       // this rank's rows (ag_rows x K, pitch ag_ld_src)
     int64_t ag_ld_src, ag_rows;
     void* ag_dst[8];          // every rank's gathered buffer (world * ag_rows x K, pitch K)
     unsigned int* ag_count[8];// every rank's per-row-block counters
     int ag_piece_bytes;       // bytes per pushed piece: divides the bytes of a 128-row block, at most PUSH_PIECE_BYTES
-    int ag_pieces_per_block;  // pieces per 128-row block = what a block's counter grows by per epoch
+    int ag_pieces_per_block;  // pieces per 128-row block
+    int ag_runs_per_block;    // a block is pushed as this many runs of consecutive pieces, each by one CTA, each ending with
+                              // one bump of the block's counter on the destination (what the counter grows by per epoch)
     // mode 3 (ZeRO weight gather -> GEMM): the B operand (N x K, rows contiguous) is cut over the ranks as a flat element
     // range; every rank pushes its part to all ranks in pieces and the TMA producer waits for the 128-row chunks it needs
     const char* bg_src;       // this rank's part (local shard memory)
@@ -437,6 +499,7 @@ struct FusedComm {
     unsigned int* bg_cnt[8];  // every rank's per-chunk counters (chunk = 128 rows)
     const unsigned int* bg_expected;  // pieces a chunk receives in total, per chunk
     int bg_first_block;       // n-block at which this rank's own rows start (tile order is rotated to begin there)
+    int bg_split;             // a rank's part of one 128-row chunk is pushed as up to this many runs (one counter bump each)
 };
 constexpr int64_t BG_PIECE = 16384;  // elements per pushed piece (32 KiB = one stage of the push pipeline)
 
@@ -484,12 +547,16 @@ struct PushPipe {
         buf0 = buf; bar0 = bar; meta = m; n_loaded = n_stored = n_sig = 0;
     }
     __device__ __forceinline__ void retire(int64_t upto) {
-        if (upto <= n_sig) return;
-        asm volatile("fence.proxy.async.global;" ::: "memory");  // the stores went through the async proxy
-        __threadfence_system();
+        bool fenced = false;
         for (; n_sig < upto; ++n_sig) {
             unsigned int* c = meta->cnt[n_sig % PUSH_STAGES];
-            if (c) atomicAdd_system(c, 1u);
+            if (!c) continue;
+            if (!fenced) {
+                asm volatile("fence.proxy.async.global;" ::: "memory");  // the stores went through the async proxy
+                __threadfence_system();
+                fenced = true;
+            }
+            atomicAdd_system(c, 1u);
         }
     }
     // Issue the store of the oldest loaded piece (if any) and retire stores beyond the pending limit.
@@ -554,7 +621,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int compute_ctas = (FUSED == 2 || FUSED == 3) ? (int)gridDim.x - f.ag_ctas : (int)gridDim.x;
     const bool comm_cta = (FUSED == 2 || FUSED == 3) && (int)blockIdx.x >= compute_ctas;
     const int64_t first_tile = comm_cta ? num_tiles : blockIdx.x / NCTA, tile_step = compute_ctas / NCTA;
-    const int blocks_per_rank = FUSED == 2 ? (int)(f.ag_rows / BM) : 0;
+    const int blocks_per_rank = FUSED == 2 ? (int)(f.ag_rows / (BM * NCTA)) : 0;   // in tile rows (256 rows for a CTA pair)
+    const int row_blocks_per_rank = FUSED == 2 ? (int)(f.ag_rows / BM) : 0;          // in 128-row blocks (counter granularity)
     const uint32_t tmem_cols = 2 * p.bn <= 32 ? 32 : 2 * p.bn <= 64 ? 64 : 2 * p.bn <= 128 ? 128 : 2 * p.bn <= 256 ? 256 : 512;
 
     if (threadIdx.x == 0) {
@@ -573,6 +641,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = hdr->tmem_base;
 
+    const uint64_t t_kernel0 = (FUSED != 0 && threadIdx.x == 0) ? global_ns() : 0;
+    if (FUSED != 0 && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_fused_stats[4], 1ull);
     if (FUSED != 0 && blockIdx.x == 0 && threadIdx.x < (unsigned)f.world) {
         // everything this rank did earlier on the stream is complete: peers may write into its buffers for this epoch
         st_release_sys_u32(f.flags[threadIdx.x] + f.free_row * f.world + f.rank, f.epoch);
@@ -600,19 +670,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             // weight pusher: this rank's flat element range, cut at 128-row chunk boundaries, to every rank (own first)
             const int64_t CK = (int64_t)BM * p.K;                       // elements per 128-row chunk
             const int64_t lo_all = f.bg_first, hi_all = f.bg_first + f.bg_count;
-            for (int di = 0; di < f.world && ok && f.bg_count > 0; ++di) {
+            for (int di = f.skip_local ? 1 : 0; di < f.world && ok && f.bg_count > 0; ++di) {
                 // own copy first, then rank-1, rank-2, ...: a rank multiplies its own rows first and continues with the
                 // rows of rank+1, rank+2, ..., so it should receive from those sources in that order
                 const int dst = (f.rank - di + f.world) % f.world;
-                int64_t g = 0;
+                int64_t g = 0;   // running index of runs
                 for (int64_t c = lo_all / CK; c * CK < hi_all && ok; ++c) {
                     const int64_t lo = lo_all > c * CK ? lo_all : c * CK;
                     const int64_t hi = hi_all < (c + 1) * CK ? hi_all : (c + 1) * CK;
-                    for (int64_t e0 = lo; e0 < hi && ok; e0 += BG_PIECE, ++g) {
+                    const int64_t np = (hi - lo + BG_PIECE - 1) / BG_PIECE;           // pieces of this rank in the chunk
+                    const int64_t per_run = (np + f.bg_split - 1) / f.bg_split;       // pieces per run
+                    for (int64_t r0 = 0; r0 < np && ok; r0 += per_run, ++g) {
                         if (g % n_pushers != me) continue;
                         if (!dst_free(dst)) { ok = false; break; }
-                        const uint32_t bytes = (uint32_t)((hi - e0 < BG_PIECE ? hi - e0 : BG_PIECE) * 2);
-                        ok = pipe.submit(f.bg_src + (e0 - lo_all) * 2, (char*)f.bg_dst[dst] + e0 * 2, f.bg_cnt[dst] + c, bytes);
+                        const int64_t r1 = r0 + per_run < np ? r0 + per_run : np;
+                        for (int64_t pi = r0; pi < r1 && ok; ++pi) {
+                            const int64_t e0 = lo + pi * BG_PIECE;
+                            const uint32_t bytes = (uint32_t)((hi - e0 < BG_PIECE ? hi - e0 : BG_PIECE) * 2);
+                            // only the last piece of a run carries the counter: no fence between the pieces of a run
+                            ok = pipe.submit(f.bg_src + (e0 - lo_all) * 2, (char*)f.bg_dst[dst] + e0 * 2,
+                                             pi + 1 == r1 ? f.bg_cnt[dst] + c : nullptr, bytes);
+                        }
                     }
                 }
             }
@@ -620,16 +698,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             // all-gather pusher: this rank's rows (contiguous) to every rank's gathered matrix, destination-major
             // starting with this rank itself, then rank-1, rank-2, ... (the order in which the consumers get to them)
             const int64_t block_bytes = (int64_t)BM * p.K * 2;
-            const int64_t ppb = f.ag_pieces_per_block, per_dst = (int64_t)blocks_per_rank * ppb;
-            const int64_t total_pieces = (int64_t)f.world * per_dst;
-            for (int64_t g = me; g < total_pieces && ok; g += n_pushers) {
-                const int dst = (f.rank - (int)(g / per_dst) + f.world) % f.world;
+            const int64_t rpb = f.ag_runs_per_block, per_run = f.ag_pieces_per_block / rpb;
+            const int64_t per_dst = (int64_t)row_blocks_per_rank * rpb;
+            const int skip = f.skip_local ? 1 : 0;
+            const int64_t total_runs = (int64_t)(f.world - skip) * per_dst;
+            for (int64_t g = me; g < total_runs && ok; g += n_pushers) {
+                const int dst = (f.rank - skip - (int)(g / per_dst) + 2 * f.world) % f.world;
                 const int64_t rem = g % per_dst;
-                const int64_t blk = rem / ppb, piece = rem % ppb;
+                const int64_t blk = rem / rpb, run = rem % rpb;
                 if (!dst_free(dst)) { ok = false; break; }
-                const int64_t off = blk * block_bytes + piece * (int64_t)f.ag_piece_bytes;
-                ok = pipe.submit((const char*)f.ag_src + off, (char*)f.ag_dst[dst] + (int64_t)f.rank * f.ag_rows * p.K * 2 + off,
-                                 f.ag_count[dst] + (f.rank * blocks_per_rank + blk), (uint32_t)f.ag_piece_bytes);
+                unsigned int* cnt = f.ag_count[dst] + (f.rank * row_blocks_per_rank + blk);
+                char* dbase = (char*)f.ag_dst[dst] + (int64_t)f.rank * f.ag_rows * p.K * 2;
+                for (int64_t pi = run * per_run; pi < (run + 1) * per_run && ok; ++pi) {
+                    const int64_t off = blk * block_bytes + pi * (int64_t)f.ag_piece_bytes;
+                    // only the last piece of a run carries the counter: no fence between the pieces of a run
+                    ok = pipe.submit((const char*)f.ag_src + off, dbase + off, pi + 1 == (run + 1) * per_run ? cnt : nullptr,
+                                     (uint32_t)f.ag_piece_bytes);
+                }
             }
         }
         if (!pipe.drain()) ok = false;
@@ -637,12 +722,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             hdr->failed = 1;
             atomicCAS(&g_gemm_status, 0, (11 << 16) | (blockIdx.x & 0xffff));
         }
+        atomicMax(&g_fused_stats[1], (unsigned long long)(global_ns() - t_kernel0));
     } else if (comm_cta) {
         // the other threads of a pusher CTA have nothing to do
     } else if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one per CTA)
         if (lane == 0) {
             bool ok = true;
+            uint64_t waited = 0;        // time spent waiting for data of other ranks (fused modes)
             uint32_t ps = 0, pph = 0;   // ring position and phase, carried across tiles
             const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(&hdr->full[0]), empty0 = smem_u32(&hdr->empty[0]);
             const uint32_t full_leader0 = CTA2 ? map_to_cta(full0, 0) : full0;
@@ -656,6 +743,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     n_blk = (n_blk + f.bg_first_block) % p.n_blocks;
                     const int64_t r0 = (int64_t)n_blk * p.bn;
                     const int64_t r1 = (r0 + p.bn < p.N ? r0 + p.bn : p.N) - 1;
+                    const uint64_t tw0 = global_ns();
                     for (int64_t c = r0 / BM; c <= r1 / BM && ok; ++c) {
                         const unsigned int target = f.epoch * f.bg_expected[c];
                         if (!wait_counter(f.bg_cnt[f.rank] + c, target, f.limit_ns)) {
@@ -663,16 +751,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                         }
                     }
                     if (!ok) break;
+                    waited += global_ns() - tw0;
                     asm volatile("fence.proxy.async.global;" ::: "memory");
                 }
                 if (FUSED == 2) {
                     // local row blocks first, then the peers' blocks in the order in which they are pushed
                     m_blk = (m_blk + f.rank * blocks_per_rank) % p.m_blocks;
-                    const unsigned int target = f.epoch * (unsigned int)f.ag_pieces_per_block;
-                    if (!wait_counter(f.ag_count[f.rank] + m_blk, target, f.limit_ns)) {
+                    const unsigned int target = f.epoch * (unsigned int)f.ag_runs_per_block;
+                    const int row_block = m_blk * NCTA + (int)rank;
+                    const bool mine = f.skip_local && row_block / row_blocks_per_rank == f.rank;   // copied before the launch
+                    const uint64_t tw0 = global_ns();
+                    if (!mine && !wait_counter(f.ag_count[f.rank] + row_block, target, f.limit_ns)) {
                         ok = false; atomicCAS(f.status, 0, 0x400 | f.rank); atomicCAS(&g_gemm_status, 0, (6 << 16) | (blockIdx.x & 0xffff)); hdr->failed = 1; break;
                     }
-                    asm volatile("fence.proxy.async.global;" ::: "memory");  // the block was written with ordinary stores, TMA reads it
+                    waited += global_ns() - tw0;
+                    asm volatile("fence.proxy.async.global;" ::: "memory");  // the block was written by a peer's copies, TMA reads it
                 }
                 const int bi = (int)(batch % p.batch_inner), bo = (int)(batch / p.batch_inner);
                 const int bib = (int)(bi / p.b_inner_div);
@@ -716,6 +809,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     }
                     if (++ps == (uint32_t)p.stages) { ps = 0; pph ^= 1; }
                 }
+            }
+            if (FUSED == 2 || FUSED == 3) {
+                atomicAdd(&g_fused_stats[0], (unsigned long long)waited);
+                atomicMax(&g_fused_stats[3], (unsigned long long)waited);
             }
         }
     } else if (warp == 1) {
@@ -820,6 +917,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
     // ---------------------------------------------------------------------- teardown
     __syncthreads();
+    if (FUSED != 0 && threadIdx.x == 0) atomicMax(&g_fused_stats[2], (unsigned long long)(global_ns() - t_kernel0));
     if (hdr->failed) {
         // a wait ran out: give copies that are still in flight time to land before the CTA's shared memory goes away
         const uint64_t t0 = global_ns();
@@ -842,7 +940,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 for (int j = 0; j < f.world; ++j) st_release_sys_u32(f.flags[j] + f.done_row * f.world + f.rank, f.epoch);
             }
             bool ok = true;
+            const uint64_t tw0 = global_ns();
             for (int j = 0; j < f.world && ok; ++j) ok = wait_counter(f.flags[f.rank] + f.done_row * f.world + j, f.epoch, f.limit_ns);
+            atomicMax(&g_fused_stats[5], (unsigned long long)(global_ns() - tw0));
+            atomicAdd(&g_fused_stats[7], (unsigned long long)(global_ns() - tw0));
             if (!ok) { atomicCAS(f.status, 0, 0x600 | f.rank); atomicCAS(&g_gemm_status, 0, (8 << 16) | (blockIdx.x & 0xffff)); }
             rs_ok = ok ? 1 : 0;
         }
@@ -850,27 +951,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         if (rs_ok) {
             const int64_t nvec = f.rs_rows * p.N / 8;
             const int64_t slot_elems = f.rs_rows * p.N;
-            for (int64_t v = (int64_t)blockIdx.x * NUM_THREADS + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * NUM_THREADS) {
-                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                const int64_t e = v * 8;
-                if (p.c_dtype == BMT_DT_F16) {
-                    for (int j = 0; j < f.world; ++j) { float t[8]; load8((const __half*)f.rs_inbox_local + j * slot_elems + e, t);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] += t[i]; }
-                    if (f.rs_bias) { float t[8]; load8((const __half*)f.rs_bias + e % p.N, t);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] += t[i]; }
-                    store8((__half*)f.rs_out + e, acc);
-                } else {
-                    for (int j = 0; j < f.world; ++j) { float t[8]; load8((const __nv_bfloat16*)f.rs_inbox_local + j * slot_elems + e, t);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] += t[i]; }
-                    if (f.rs_bias) { float t[8]; load8((const __nv_bfloat16*)f.rs_bias + e % p.N, t);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] += t[i]; }
-                    store8((__nv_bfloat16*)f.rs_out + e, acc);
-                }
-            }
+            if (p.c_dtype == BMT_DT_F16) rs_reduce_all<__half>(f.rs_inbox_local, slot_elems, f.world, f.rs_bias, p.N, f.rs_out, nvec);
+            else rs_reduce_all<__nv_bfloat16>(f.rs_inbox_local, slot_elems, f.world, f.rs_bias, p.N, f.rs_out, nvec);
+            if (threadIdx.x == 0) atomicMax(&g_fused_stats[6], (unsigned long long)(global_ns() - t_kernel0));
         }
     }
 }
@@ -998,6 +1081,9 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
         BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
         BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
         BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
+        BMT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET + 2048));
     }
     static int force_bn = -1, force_cta2 = -2, debug_flags = -1;
     if (debug_flags < 0) { const char* e = getenv("BMT_GEMM_DEBUG"); debug_flags = e ? atoi(e) : 0; }
@@ -1010,7 +1096,9 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     p.a_mn = a_major; p.b_mn = b_major;
     const int comm_ctas = (fused && (fused->mode == 2 || fused->mode == 3)) ? fused->ag_ctas : 0;
     if (fused) g_num_sms -= comm_ctas;  // tile choice for the CTAs that do math
-    TileChoice tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, force_bn, fused ? 0 : force_cta2);
+    // a fused kernel can run as CTA pairs when its pusher CTAs pair up too and (mode 2) a rank's rows fill whole 256-row tiles
+    const bool pair_ok = !fused || (comm_ctas % 2 == 0 && (fused->mode != 2 || fused->ag_rows % (2 * BM) == 0));
+    TileChoice tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, force_bn, pair_ok ? force_cta2 : 0);
     if (fused) g_num_sms += comm_ctas;
     if (tc.bn == 0) tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, 0, -1);  // forced shape not applicable here
     if (tc.bn == 0) return -22;
@@ -1028,7 +1116,13 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     static int group_env = -1;
     if (group_env < 0) { const char* e = getenv("BMT_GEMM_GROUP_M"); group_env = e ? atoi(e) : 0; }
     p.group_m = group_env > 0 ? group_env : 16;
-    if (p.group_m > p.m_blocks || fused) p.group_m = p.m_blocks;  // the fused modes rotate whole rows / columns of tiles
+    if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
+    if (fused && fused->mode == 3) p.group_m = p.m_blocks;  // all row tiles of one weight chunk in a row: chunks are needed in order
+    if (fused && fused->mode == 2) {
+        // groups must not straddle the rows of two ranks (the tile order is rotated rank by rank)
+        const int per_rank = (int)(fused->ag_rows / (BM * ncta));
+        while (per_rank % p.group_m) --p.group_m;
+    }
     p.residual = g.residual; p.ldr = g.ldr; p.aux = g.aux; p.ld_aux = g.ld_aux; p.aux_mode = g.aux ? g.aux_mode : 0;
     if ((p.residual || p.aux_mode) && batch_inner * batch_outer != 1) return -21;  // fused extras are for plain (unbatched) GEMMs
     const uint32_t fmt = ab_dtype == BMT_DT_F16 ? 0u : 1u;
@@ -1052,16 +1146,33 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     FusedComm none;
     memset(&none, 0, sizeof(none));
     if (fused) {
-        if (tc.cta2) return -23;
-        const int compute = g_num_sms - comm_ctas;
-        const unsigned grid = (unsigned)(tiles < compute ? tiles : compute) + comm_ctas;
+        const int compute = (g_num_sms - comm_ctas) / ncta;   // CTAs (or CTA pairs) that do math
+        const unsigned grid = (unsigned)(ncta * (tiles < compute ? tiles : compute)) + comm_ctas;
         FusedComm fc = *fused;
         if (fc.mode == 3) fc.bg_first_block = (int)(((fc.bg_first / k) / p.bn) % p.n_blocks);
-        if (fc.mode == 1) gemm_tcgen05_kernel<false, 1><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
-        else if (fc.mode == 2) gemm_tcgen05_kernel<false, 2><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
-        else gemm_tcgen05_kernel<false, 3><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
+        if (!tc.cta2) {
+            if (fc.mode == 1) gemm_tcgen05_kernel<false, 1><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
+            else if (fc.mode == 2) gemm_tcgen05_kernel<false, 2><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
+            else gemm_tcgen05_kernel<false, 3><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
+            bmt_count_launch(1);
+            return (int)cudaGetLastError();
+        }
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        cudaError_t e;
+        if (fc.mode == 1) e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<true, 1>, ma, mb, p, fc);
+        else if (fc.mode == 2) e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<true, 2>, ma, mb, p, fc);
+        else e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<true, 3>, ma, mb, p, fc);
         bmt_count_launch(1);
-        return (int)cudaGetLastError();
+        return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
     }
     if (!tc.cta2) {
         const unsigned grid = (unsigned)(tiles < g_num_sms ? tiles : g_num_sms);
@@ -1151,7 +1262,8 @@ extern "C" int bmt_gemm_rs_grid(int64_t m, int64_t n, int64_t k, int b_major) {
 // `gathered[rank]`; desc->a must point at it and desc->m = world * rows.  rows must be a multiple of 128.
 extern "C" int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row,
                                    unsigned int epoch, const void* src, int64_t ld_src, int64_t rows, void* const* gathered,
-                                   void* const* counters, int comm_ctas, void* status_i32, double timeout_s, void* stream) {
+                                   void* const* counters, int comm_ctas, int skip_local, void* status_i32, double timeout_s,
+                                   void* stream) {
     if (world < 2 || world > 8 || desc->m != rows * world || rows % BM != 0 || desc->a_major != 0) return -42;
     if (desc->k % 8 != 0 || desc->lda != desc->k || ld_src != desc->k || ((uintptr_t)src & 15)) return -43;
     FusedComm f;
@@ -1159,15 +1271,45 @@ extern "C" int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank,
     f.mode = 2; f.world = world; f.rank = rank; f.free_row = free_row; f.epoch = epoch;
     f.status = (int*)status_i32; f.limit_ns = (uint64_t)(timeout_s * 1e9);
     for (int j = 0; j < world; ++j) { f.flags[j] = (unsigned int*)flags[j]; f.ag_dst[j] = gathered[j]; f.ag_count[j] = (unsigned int*)counters[j]; }
-    f.ag_ctas = comm_ctas; f.ag_src = src; f.ag_ld_src = ld_src; f.ag_rows = rows;
+    f.ag_ctas = comm_ctas; f.ag_src = src; f.ag_ld_src = ld_src; f.ag_rows = rows; f.skip_local = skip_local;
     // a 128-row block has 256 * K bytes = 2048 * (K / 8): pieces of 2048 * d bytes with d the largest divisor of K / 8 up to 16
     int d = 16;
     while ((desc->k / 8) % d) --d;
     f.ag_piece_bytes = 2048 * d; f.ag_pieces_per_block = (int)(desc->k / 8) / d;
+    // runs: enough of them to keep every pusher CTA busy, otherwise one per block
+    int rpb = 1;
+    while ((int64_t)(world - (skip_local ? 1 : 0)) * (rows / BM) * rpb < 2 * (int64_t)comm_ctas && f.ag_pieces_per_block % (rpb * 2) == 0) rpb *= 2;
+    f.ag_runs_per_block = rpb;
     BmtGemmDesc g = *desc;
     g.batch_inner = g.batch_outer = g.b_inner_div = 1;
     return launch_gemm(g, (cudaStream_t)stream, &f);
 }
+
+// How many CTAs of a fused kernel should push instead of multiply: the kernel ends when both the math (on the remaining
+// SMs) and the pushes are done, so pick the even count that balances the two.  Rates are rough measured figures: a pusher
+// CTA moves about 14 GB/s, all pushers together at most about 550 GB/s to remote destinations, and the math runs at
+// about 1.1 PFLOP/s on a full GPU.  push_bytes counts every destination (own copy included), remote_bytes the peers only.
+extern "C" int bmt_fused_comm_ctas(double flops, double push_bytes, double remote_bytes) {
+    static int sms = 0;   // not g_num_sms: that one doubles as the "kernel attributes are set" marker of launch_gemm
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 16;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 64) { sms = 0; return 16; }
+    }
+    int best = 8;
+    double best_t = 1e30;
+    for (int c = 8; c <= sms - 32; c += 4) {
+        const double t_math = flops / (1.1e15 * (double)(sms - c) / (double)sms);
+        double t_push = push_bytes / (c * 14e9);
+        const double t_link = remote_bytes / 550e9;
+        if (t_link > t_push) t_push = t_link;
+        const double t = t_math > t_push ? t_math : t_push;
+        if (t < best_t * 0.98) { best_t = t; best = c; }
+    }
+    return best;
+}
+
+static int zero_gather_split(int64_t n, int world, int comm_ctas);
 
 // ZeRO weight gather -> GEMM (FusedComm mode 3).  desc->b points at the weight inside this rank's gathered buffer (N x K,
 // rows contiguous, pitch K); this rank contributes the flat element range [first, first + count) of it, read from `src`.
@@ -1175,8 +1317,8 @@ extern "C" int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank,
 // (see bmt_zero_gather_expected).
 extern "C" int bmt_zero_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row,
                                     unsigned int epoch, const void* src, int64_t first, int64_t count, void* const* weight_on_rank,
-                                    void* const* counters, const void* expected_u32, int comm_ctas, void* status_i32,
-                                    double timeout_s, void* stream) {
+                                    void* const* counters, const void* expected_u32, int comm_ctas, int skip_local,
+                                    void* status_i32, double timeout_s, void* stream) {
     if (world < 2 || world > 8 || desc->b_major != 0 || desc->ldb != desc->k) return -44;
     if ((first & 7) || (count & 7) || ((uintptr_t)src & 15)) return -45;
     FusedComm f;
@@ -1184,16 +1326,27 @@ extern "C" int bmt_zero_gather_gemm(const BmtGemmDesc* desc, int world, int rank
     f.mode = 3; f.world = world; f.rank = rank; f.free_row = free_row; f.epoch = epoch;
     f.status = (int*)status_i32; f.limit_ns = (uint64_t)(timeout_s * 1e9);
     for (int j = 0; j < world; ++j) { f.flags[j] = (unsigned int*)flags[j]; f.bg_dst[j] = weight_on_rank[j]; f.bg_cnt[j] = (unsigned int*)counters[j]; }
-    f.ag_ctas = comm_ctas; f.bg_src = (const char*)src; f.bg_first = first; f.bg_count = count;
+    f.ag_ctas = comm_ctas; f.bg_src = (const char*)src; f.bg_first = first; f.bg_count = count; f.skip_local = skip_local;
     f.bg_expected = (const unsigned int*)expected_u32;
+    f.bg_split = zero_gather_split(desc->n, world, comm_ctas);
     BmtGemmDesc g = *desc;
     g.batch_inner = g.batch_outer = g.b_inner_div = 1;
     return launch_gemm(g, (cudaStream_t)stream, &f);
 }
 
-// Host helper: pieces each 128-row chunk of an (n x k) weight receives when rank j owns the flat element range
-// [first[j], first[j] + count[j]).  out has ceil(n / 128) entries.
-extern "C" int bmt_zero_gather_expected(int64_t n, int64_t k, int world, const int64_t* first, const int64_t* count, unsigned int* out) {
+// Runs into which a rank's part of one chunk is cut: more when the weight has few chunks, so every pusher CTA has work.
+static int zero_gather_split(int64_t n, int world, int comm_ctas) {
+    const int64_t chunks = (n + BM - 1) / BM;
+    int split = 1;
+    while (chunks * world * split < 2 * (int64_t)comm_ctas && split < 8) split *= 2;
+    return split;
+}
+
+// Host helper: counter bumps each 128-row chunk of an (n x k) weight receives when rank j owns the flat element range
+// [first[j], first[j] + count[j]) and the kernel runs with `comm_ctas` pusher CTAs.  out has ceil(n / 128) entries.
+extern "C" int bmt_zero_gather_expected(int64_t n, int64_t k, int world, const int64_t* first, const int64_t* count, int comm_ctas,
+                                        unsigned int* out) {
+    const int split = zero_gather_split(n, world, comm_ctas);
     const int64_t CK = (int64_t)BM * k;
     const int64_t chunks = (n + BM - 1) / BM;
     for (int64_t c = 0; c < chunks; ++c) out[c] = 0;
@@ -1203,9 +1356,20 @@ extern "C" int bmt_zero_gather_expected(int64_t n, int64_t k, int world, const i
         for (int64_t c = lo_all / CK; c * CK < hi_all && c < chunks; ++c) {
             const int64_t lo = lo_all > c * CK ? lo_all : c * CK;
             const int64_t hi = hi_all < (c + 1) * CK ? hi_all : (c + 1) * CK;
-            out[c] += (unsigned int)((hi - lo + BG_PIECE - 1) / BG_PIECE);
+            const int64_t np = (hi - lo + BG_PIECE - 1) / BG_PIECE, per_run = (np + split - 1) / split;
+            out[c] += (unsigned int)((np + per_run - 1) / per_run);
         }
     }
+    return 0;
+}
+
+// Timing counters of the fused kernels launched on the current device since the last call (see g_fused_stats); the
+// counters are cleared.  out: 8 values.  Synchronises with the device.
+extern "C" int bmt_fused_stats(unsigned long long* out) {
+    unsigned long long v[8], zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (cudaMemcpyFromSymbol(v, g_fused_stats, sizeof(v)) != cudaSuccess) return -1;
+    if (cudaMemcpyToSymbol(g_fused_stats, zero, sizeof(zero)) != cudaSuccess) return -1;
+    for (int i = 0; i < 8; ++i) out[i] = v[i];
     return 0;
 }
 

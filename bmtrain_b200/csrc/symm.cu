@@ -198,11 +198,11 @@ __global__ void __launch_bounds__(256) push_ranges_kernel(PushArgs a) {
             __syncthreads();
             if (!ok_s) break;
         }
-        int64_t g = 0;  // running piece index over all ranges
+        int g0 = 0;  // (pieces of the earlier ranges) mod grid: pieces are dealt round-robin over the CTAs across ranges
         for (int r = 0; r < a.nranges; ++r) {
             const int64_t np = (a.nbytes[r] + piece - 1) / piece;
-            for (int64_t pi = 0; pi < np; ++pi, ++g) {
-                if (g % gridDim.x != blockIdx.x) continue;
+            // first piece of this range that belongs to this CTA, then every gridDim.x-th (no per-piece division)
+            for (int64_t pi = ((int)blockIdx.x - g0 + (int)gridDim.x) % (int)gridDim.x; pi < np; pi += gridDim.x) {
                 const int64_t b0 = pi * piece;
                 const int64_t n = (a.nbytes[r] - b0 < piece ? a.nbytes[r] - b0 : piece) / 16;
                 const int4* s = reinterpret_cast<const int4*>(a.src[r] + b0);
@@ -215,6 +215,7 @@ __global__ void __launch_bounds__(256) push_ranges_kernel(PushArgs a) {
                     for (int u = 0; u < 8; ++u) if (v + u * 256 < n) d[v + u * 256] = t[u];
                 }
             }
+            g0 = (int)((g0 + np) % (int64_t)gridDim.x);
         }
     }
     __syncthreads();
@@ -248,6 +249,26 @@ extern "C" int bmt_push_ranges(const void* const* src, const int64_t* dst_off, c
     a.world = world; a.rank = rank; a.free_row = free_row; a.done_row = done_row; a.epoch = epoch;
     a.counter = (unsigned int*)counter_u32; a.status = (int*)status_i32; a.limit_ns = (uint64_t)(timeout_s * 1e9);
     push_ranges_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}
+
+// Plain SM copy between two device pointers, either of which may be a mapped peer buffer (push: dst remote, pull: src remote).
+__global__ void __launch_bounds__(256) peer_copy_kernel(int4* __restrict__ dst, const int4* __restrict__ src, int64_t nvec) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t v0 = (int64_t)blockIdx.x * 256 + threadIdx.x; v0 < nvec; v0 += stride * 8) {
+        int4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) if (v0 + u * stride < nvec) t[u] = src[v0 + u * stride];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) if (v0 + u * stride < nvec) dst[v0 + u * stride] = t[u];
+    }
+}
+
+// Copies nbytes (multiple of 16, both pointers 16-byte aligned) with `grid` CTAs of 256 threads on `stream`.
+extern "C" int bmt_peer_copy(void* dst, const void* src, int64_t nbytes, int grid, void* stream) {
+    if ((nbytes & 15) || ((uintptr_t)dst & 15) || ((uintptr_t)src & 15) || grid < 1) return -35;
+    peer_copy_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((int4*)dst, (const int4*)src, nbytes / 16);
     bmt_count_launch(1);
     return (int)cudaGetLastError();
 }

@@ -88,16 +88,19 @@ class GPTBlockFunction(torch.autograd.Function):
         if deferred is None:
             _native.check(lib.bmt_gpt_block_forward(ctypes.byref(blk), _native.stream_handle()), "GPT block forward")
         else:
-            # the block's parameters are still on their way: norms and biases first, the QKV weight is gathered by the GEMM
-            # that consumes it, everything else has to be there before the output projection
+            # the block's parameters are still on their way: norms and biases first; the QKV weight is gathered by the GEMM
+            # that consumes it while the other big weights travel on the peer stream at the same time (measured faster than
+            # sending them after the GEMM); they have the attention core's duration to arrive before the output projection
             from ..parallel import fused_ops
 
             cur = torch.cuda.current_stream()
             cur.wait_event(deferred["ev_small"])
             _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 1, 1, _native.stream_handle()), "GPT block forward")
+            ev_rest = deferred["push_rest"]()
             fused_ops.zero_gather_gemm(saved["ln1"], saved["qkv"], params[3], deferred)
-            cur.wait_event(deferred["ev_rest"])
-            _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 3, 9, _native.stream_handle()), "GPT block forward")
+            _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 3, 5, _native.stream_handle()), "GPT block forward")
+            cur.wait_event(ev_rest)
+            _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 6, 9, _native.stream_handle()), "GPT block forward")
         ctx.saved, ctx.x, ctx.mask8, ctx.params = saved, x, mask8, params
         ctx.cfg = (n_heads, d_head, act, eps, causal)
         return y

@@ -12,6 +12,7 @@ the same shape.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -21,7 +22,14 @@ from ..ops import _native
 from ..ops.gpt_block import _i64, _int, _f32, _c_void_p
 from . import symm
 
-_COMM_CTAS = 16
+_COMM_CTAS = int(os.environ.get("BMT_COMM_CTAS", "0"))  # 0: balance math and transfer per call (bmt_fused_comm_ctas)
+
+
+def _comm_ctas(flops: float, push_bytes: float, remote_bytes: float) -> int:
+    if _COMM_CTAS > 0:
+        return _COMM_CTAS
+    lib = _native.cuda_lib()
+    return int(lib.bmt_fused_comm_ctas(ctypes.c_double(flops), ctypes.c_double(push_bytes), ctypes.c_double(remote_bytes)))
 calls = {"gemm_rs": 0, "ag_gemm": 0, "zero_gather_gemm": 0}  # how often each fused kernel ran (tests and benchmarks read this)
 _ring: Dict[Tuple, int] = {}
 _counters: Dict[Tuple, torch.Tensor] = {}
@@ -40,6 +48,16 @@ class _GemmDesc(ctypes.Structure):
 
 
 _DT = {torch.float16: 0, torch.bfloat16: 1}
+
+
+def kernel_stats() -> dict:
+    """Device-side timing of the fused GEMM kernels launched since the last call (cleared by reading; host sync)."""
+    out = (ctypes.c_ulonglong * 8)()
+    _native.check(_native.cuda_lib().bmt_fused_stats(out), "fused kernel statistics")
+    n = max(int(out[4]), 1)
+    return {"kernels": int(out[4]), "producer_wait_us_sum": out[0] / 1e3, "producer_wait_us_max": out[3] / 1e3,
+            "pusher_us_max": out[1] / 1e3, "cta_us_max": out[2] / 1e3, "producer_wait_us_per_kernel": out[0] / 1e3 / n,
+            "rs_wait_us_max": out[5] / 1e3, "rs_total_us_max": out[6] / 1e3, "rs_wait_us_sum": out[7] / 1e3}
 
 
 def _next_parity(key: Tuple) -> int:
@@ -113,10 +131,15 @@ def ag_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     d.c, d.ldc, d.c_dtype = out.data_ptr(), N, _DT[x_local.dtype]
     d.bias = None if bias is None else bias.data_ptr()
     d.ab_dtype, d.alpha = _DT[x_local.dtype], 1.0
+    # this rank's own rows go into place with a device-to-device copy (far faster than the pusher CTAs, which then only
+    # serve the peers); the kernel does not wait for them
+    mine = gathered.tensor(x_local.dtype, m * K, comm.rank * m * K * es).view(m, K)
+    mine.copy_(x_local)
+    ctas = _comm_ctas(2.0 * W * m * N * K, float((W - 1) * m * K * es), float((W - 1) * m * K * es))
     _native.check(lib.bmt_all_gather_gemm(
         ctypes.byref(d), ctypes.c_int(W), ctypes.c_int(comm.rank), rt.flag_ptrs, ctypes.c_int(free_row), ctypes.c_uint(epoch),
         _native.ptr(x_local), ctypes.c_int64(x_local.stride(0)), ctypes.c_int64(m), gathered.ptr_table(), counters.ptr_table(),
-        ctypes.c_int(_COMM_CTAS), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s), _native.stream_handle()),
+        ctypes.c_int(ctas), ctypes.c_int(1), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s), _native.stream_handle()),
         "fused all-gather -> GEMM kernel")
     calls["ag_gemm"] += 1
     if return_gathered:
@@ -142,13 +165,23 @@ def zero_gather_gemm(x: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Te
             lo, hi = max(w0, j * b.part), min(w1, (j + 1) * b.part)
             first[j], count[j] = max(lo - w0, 0), max(hi - lo, 0)
         chunks = (N + 127) // 128
+        # the number of pusher CTAs decides how the pushes are cut, so every rank has to pick the same one: agree on the
+        # largest token count (first use only; host sync)
+        rows = torch.tensor([x.shape[0]], dtype=torch.int64, device=x.device)
+        b.comm.all_reduce(rows, "max")
+        ctas = _comm_ctas(2.0 * int(rows.item()) * N * K, float((W - 1) * max(count) * es), float((W - 1) * max(count) * es))
         exp_host = (ctypes.c_uint * chunks)()
-        lib.bmt_zero_gather_expected(ctypes.c_int64(N), ctypes.c_int64(K), ctypes.c_int(W), first, count, exp_host)
+        others = (ctypes.c_int64 * W)(*[0 if j == b.comm.rank else count[j] for j in range(W)])  # the own part is copied, not pushed
+        lib.bmt_zero_gather_expected(ctypes.c_int64(N), ctypes.c_int64(K), ctypes.c_int(W), first, others, ctypes.c_int(ctas), exp_host)
         expected = torch.tensor(list(exp_host), dtype=torch.int32, device=x.device)
-        geo = (list(first), list(count), expected, chunks)
+        counters = rt.slot(key + ("cnt",), max(256, chunks * 4))
+        geo = dict(first=list(first), count=list(count), expected=expected, ctas=ctas, counters=counters.ptr_table(),
+                   weight_on_rank=(ctypes.c_void_p * W)(*[p + w0 * es for p in buf.ptrs]), buf=buf)
         rt.cache[key + ("geo",)] = geo
-    first, count, expected, chunks = geo
-    counters = rt.slot(key + ("cnt",), max(256, chunks * 4))
+    if geo["buf"] is not buf:   # the ring slot was reallocated
+        geo["weight_on_rank"] = (ctypes.c_void_p * W)(*[p + w0 * es for p in buf.ptrs])
+        geo["buf"] = buf
+    first, count = geo["first"], geo["count"]
     d = _GemmDesc()
     d.m, d.n, d.k = x.shape[0], N, K
     d.a, d.lda, d.a_major = x.data_ptr(), x.stride(0), 0
@@ -158,10 +191,13 @@ def zero_gather_gemm(x: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Te
     d.ab_dtype, d.alpha = _DT[x.dtype], 1.0
     me = b.comm.rank
     src = b.storage.data_ptr() + (w0 + first[me] - b.begin) * es if count[me] > 0 else b.storage.data_ptr()
-    weight_on_rank = (ctypes.c_void_p * W)(*[p + w0 * es for p in buf.ptrs])
+    if count[me] > 0:
+        # own part: plain device-to-device copy into this rank's gathered buffer; the pusher CTAs only serve the peers
+        lo = w0 + first[me]
+        buf.tensor(x.dtype, count[me], lo * es).copy_(b.storage.data[lo - b.begin:lo - b.begin + count[me]])
     _native.check(lib.bmt_zero_gather_gemm(
         ctypes.byref(d), ctypes.c_int(W), ctypes.c_int(me), rt.flag_ptrs, ctypes.c_int(ctx["free_row"]), ctypes.c_uint(epoch),
-        ctypes.c_void_p(src), ctypes.c_int64(first[me]), ctypes.c_int64(count[me]), weight_on_rank, counters.ptr_table(),
-        _native.ptr(expected), ctypes.c_int(_COMM_CTAS), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s),
+        ctypes.c_void_p(src), ctypes.c_int64(first[me]), ctypes.c_int64(count[me]), geo["weight_on_rank"], geo["counters"],
+        _native.ptr(geo["expected"]), ctypes.c_int(geo["ctas"]), ctypes.c_int(1), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s),
         _native.stream_handle()), "fused ZeRO gather -> GEMM kernel")
     calls["zero_gather_gemm"] += 1

@@ -74,6 +74,7 @@ def body_fused_rs(fused: bool):
 def test_zero3_fused_reduce_scatter_2gpu(fused, monkeypatch):
     _need(2)
     monkeypatch.setenv("BMT_PEER", "1" if fused else "0")
+    monkeypatch.setenv("BMT_FUSED_GATHER", "1")  # exercise the fused gather in forward as well (default: backward only)
     run_distributed("test_multi_gpu", "body_fused_rs", 2, device="cuda", fused=fused)
 
 
