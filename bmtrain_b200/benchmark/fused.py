@@ -30,7 +30,7 @@ from bmtrain_b200.global_var import config
 _busy = {}
 
 
-def _timer(fn, iters: int, warmup: int, flush, host_ahead: bool = False) -> float:
+def _timer(fn, iters: int, warmup: int, flush, host_ahead: bool = False, after_warmup=None) -> float:
     """Device time of ``fn`` (CUDA events, mean over ``iters``, maximum over ranks).  ``host_ahead``: a long matrix product
     is queued in front of the start event, so ``fn`` is enqueued while the device is still busy and its host-side cost
     does not show (the situation of a training step once the host runs ahead of the device)."""
@@ -41,6 +41,8 @@ def _timer(fn, iters: int, warmup: int, flush, host_ahead: bool = False) -> floa
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if after_warmup is not None:
+        after_warmup()   # e.g. clear the in-kernel timing counters so they cover the timed iterations only
     comm.barrier()
     total = 0.0
     for _ in range(iters):
@@ -136,7 +138,8 @@ def main() -> None:
 
     before = fused_ops.calls["ag_gemm"]
     fused_ops.kernel_stats()
-    t_f = _timer(lambda: tp_fused.all_gather_gemm(x_loc, w, None, comm), args.iters, args.warmup, flush)
+    t_f = _timer(lambda: tp_fused.all_gather_gemm(x_loc, w, None, comm), args.iters, args.warmup, flush,
+                 after_warmup=fused_ops.kernel_stats)
     stats3 = fused_ops.kernel_stats()
     assert fused_ops.calls["ag_gemm"] > before, "fused all-gather -> GEMM did not run"
     t_s = _timer(split_ag, args.iters, args.warmup, flush)
@@ -159,7 +162,8 @@ def main() -> None:
 
     before = fused_ops.calls["gemm_rs"]
     fused_ops.kernel_stats()
-    t_f = _timer(lambda: tp_fused.gemm_reduce_scatter(x, w, None, comm), args.iters, args.warmup, flush)
+    t_f = _timer(lambda: tp_fused.gemm_reduce_scatter(x, w, None, comm), args.iters, args.warmup, flush,
+                 after_warmup=fused_ops.kernel_stats)
     stats4 = fused_ops.kernel_stats()
     assert fused_ops.calls["gemm_rs"] > before, "fused GEMM -> reduce-scatter did not run"
     t_s = _timer(split_rs, args.iters, args.warmup, flush)
@@ -231,7 +235,7 @@ def main() -> None:
     before = fused_ops.calls["zero_gather_gemm"]
     os.environ["BMT_FUSED_GATHER"] = "1"
     fused_ops.kernel_stats()
-    t_f = _timer(lambda: fwd(z3), args.iters, args.warmup, flush)
+    t_f = _timer(lambda: fwd(z3), args.iters, args.warmup, flush, after_warmup=fused_ops.kernel_stats)
     stats1 = fused_ops.kernel_stats()
     host_f = _host_ms(lambda: fwd(z3), args.iters)
     t_f_ahead = _timer(lambda: fwd(z3), args.iters, 1, flush, host_ahead=True)

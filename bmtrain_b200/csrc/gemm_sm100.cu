@@ -48,6 +48,7 @@ struct GemmParams {
     int bn;           // tile N
     int stages;
     uint32_t hdr_off;      // byte offset of the barrier header behind the tile stages (pusher CTAs need room for their ring)
+    uint32_t out_stage_off;  // GEMM -> reduce-scatter: byte offset of the epilogue's row staging area (128 rows x OUT_PITCH)
     int a_mn, b_mn;   // 1 = MN-major operand
     int m_blocks, n_blocks;
     int64_t batch_inner, batch_outer, b_inner_div;
@@ -477,7 +478,11 @@ struct FusedComm {
     void* rs_inbox[8];        // destination j: base of slot `rank` inside j's inbox (rs_rows x N, pitch N)
     const void* rs_inbox_local;  // this rank's inbox: world slots of rs_rows x N
     int64_t rs_rows;          // rows per rank
-    unsigned int* rs_counter; // local, monotonic count of CTAs that finished their tiles
+    unsigned int* rs_counter; // local, monotonic: [0] epilogue warps that finished the tiles with rows of other ranks (early
+                              // mode) or CTAs that finished all tiles; [1] early mode: CTAs that finished all tiles
+    int rs_early;             // tiles with other ranks' rows come first and "delivered" is published when they are done
+    int rs_bpr;               // early mode: tile rows per rank
+    int64_t rs_remote_tiles;  // early mode: number of tiles (in raster order) that hold rows of other ranks
     void* rs_out;             // rs_rows x N
     const void* rs_bias;
     // mode 2
@@ -529,6 +534,10 @@ __device__ __forceinline__ bool wait_counter(const unsigned int* p, unsigned int
 // stages with bulk asynchronous copies: global -> shared completes on an mbarrier, shared -> global is tracked in bulk
 // groups.  Up to PUSH_AHEAD loads and PUSH_PENDING + 1 stores are in flight at a time; a piece's counter on the
 // destination is bumped only after its store has completed (full wait_group, proxy fence, system fence).
+// Epilogue staging of the GEMM -> reduce-scatter kernel: every thread packs up to OUT_CHUNK columns of its row into shared
+// memory and sends them with one bulk copy (256-byte writes keep NVLink packets full; 16-byte scattered stores do not).
+// The 16 bytes of padding per row spread the rows of a warp over all banks.
+constexpr int OUT_CHUNK = 128, OUT_PITCH = OUT_CHUNK * 2 + 16;
 constexpr int PUSH_STAGES = 6, PUSH_AHEAD = 3, PUSH_PENDING = 3;
 constexpr uint32_t PUSH_PIECE_BYTES = 32768;
 
@@ -738,6 +747,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 const int64_t rem = tile % tiles_per_batch;
                 int m_blk, n_blk;
                 tile_coords(p, rem, m_blk, n_blk);
+                if (FUSED == 1 && f.rs_early) m_blk = (m_blk + (f.rank + 1) * f.rs_bpr) % p.m_blocks;   // own rows last
                 if (FUSED == 3) {
                     // this rank's own rows first; wait for every 128-row chunk the B tile touches
                     n_blk = (n_blk + f.bg_first_block) % p.n_blocks;
@@ -859,11 +869,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         uint32_t tcount = 0;
         uint32_t rs_free_mask = 0;     // destinations whose inbox is known to be free (mode 1)
         bool ok = true;
+        bool remote_open = FUSED == 1 && f.rs_early;   // this warp has not yet reported its other-rank tiles as delivered
+        auto report_remote_done = [&]() {
+            // the warp's stores into other ranks' inboxes are all issued: make them visible and count the warp; the last
+            // warp of the rank publishes "delivered" to every rank while the tiles with own rows are still being computed
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // this thread's row copies have completed
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_system();
+                const unsigned int done = atomicAdd(f.rs_counter, 1u) + 1u;
+                if (done == f.epoch * gridDim.x * 4u) {
+                    __threadfence_system();
+                    for (int j = 0; j < f.world; ++j) st_release_sys_u32(f.flags[j] + f.done_row * f.world + f.rank, f.epoch);
+                }
+            }
+            remote_open = false;
+        };
         for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++tcount) {
             const int64_t batch = tile / tiles_per_batch;
             const int64_t rem = tile % tiles_per_batch;
             int m_blk, n_blk;
             tile_coords(p, rem, m_blk, n_blk);
+            if (FUSED == 1 && f.rs_early) {
+                if (remote_open && rem >= f.rs_remote_tiles) report_remote_done();
+                m_blk = (m_blk + (f.rank + 1) * f.rs_bpr) % p.m_blocks;   // own rows last
+            }
             if (FUSED == 2) m_blk = (m_blk + f.rank * blocks_per_rank) % p.m_blocks;
             if (FUSED == 3) n_blk = (n_blk + f.bg_first_block) % p.n_blocks;
             const int64_t bi = batch % p.batch_inner, bo = batch / p.batch_inner;
@@ -895,6 +927,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * p.bn;
             const int64_t tile_end = (int64_t)(n_blk + 1) * p.bn;
             const int64_t col_end = tile_end < p.N ? tile_end : p.N;
+            if (FUSED == 1) {
+                // staged bulk-store epilogue: pack OUT_CHUNK columns of the row in shared memory, one bulk copy to the owner
+                const uint32_t srow = smem_u32(smem) + p.out_stage_off + (uint32_t)((quarter * 32 + lane) * OUT_PITCH);
+                for (int c0 = 0; c0 < p.bn; c0 += OUT_CHUNK) {
+                    const int64_t col0 = (int64_t)n_blk * p.bn + c0;
+                    if (col0 >= col_end) break;
+                    const int ncols = (int)(col_end - col0 < OUT_CHUNK ? col_end - col0 : OUT_CHUNK);
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous copy has read the row buffer
+                    for (int sub = 0; sub < OUT_CHUNK; sub += 32) {
+                        if (c0 + sub >= p.bn || col0 + sub >= col_end) break;
+                        uint32_t r[32];
+                        tmem_ld32(taddr + c0 + sub, r);
+                        tmem_ld_wait();
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float a = __uint_as_float(r[2 * i]) * p.alpha, b = __uint_as_float(r[2 * i + 1]) * p.alpha;
+                            if (p.c_dtype == BMT_DT_F16) { __half2 h = __floats2half2_rn(a, b); pk[i] = *reinterpret_cast<uint32_t*>(&h); }
+                            else { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); pk[i] = *reinterpret_cast<uint32_t*>(&h); }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + sub * 2 + q * 16), "r"(pk[4 * q]),
+                                         "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3]) : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    if (row_ok && !(p.debug & 4))
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                     ::"l"(cbase + (coff + col0) * 2), "r"(srow), "r"(ncols * 2) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            } else
             for (int c0 = 0; c0 < p.bn; c0 += 32) {
                 const int64_t col0 = (int64_t)n_blk * p.bn + c0;
                 if (col0 >= col_end) break;
@@ -912,6 +976,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 if (CTA2) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->tmem_empty[acc]), 0));
                 else mbar_arrive(&hdr->tmem_empty[acc]);
             }
+        }
+        if (remote_open) report_remote_done();
+        if (FUSED == 1) {
+            // row copies read this CTA's shared memory and write the inboxes: complete them before the teardown barrier
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence_system();
         }
     }
 
@@ -932,14 +1003,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         // ---- reduce phase of GEMM -> reduce-scatter
         __shared__ int rs_ok;
         if (threadIdx.x == 0) {
-            __threadfence_system();  // this CTA's inbox stores (ordered before by the barrier above) become visible system-wide
-            const unsigned int done = atomicAdd(f.rs_counter, 1u) + 1u;
-            if (done == f.epoch * gridDim.x) {
-                // last CTA of this rank: everything is delivered
-                __threadfence_system();
-                for (int j = 0; j < f.world; ++j) st_release_sys_u32(f.flags[j] + f.done_row * f.world + f.rank, f.epoch);
-            }
             bool ok = true;
+            if (!f.rs_early) {
+                __threadfence_system();  // this CTA's inbox stores (ordered before by the barrier above) become visible system-wide
+                const unsigned int done = atomicAdd(f.rs_counter, 1u) + 1u;
+                if (done == f.epoch * gridDim.x) {
+                    // last CTA of this rank: everything is delivered
+                    __threadfence_system();
+                    for (int j = 0; j < f.world; ++j) st_release_sys_u32(f.flags[j] + f.done_row * f.world + f.rank, f.epoch);
+                }
+            } else {
+                // "delivered" went out when the other ranks' tiles were done; the tiles with own rows only have to be complete
+                // on this GPU: count the CTA and wait (bounded) for the rest of the grid, all of which is resident
+                __threadfence();
+                atomicAdd(f.rs_counter + 1, 1u);
+                ok = wait_counter(f.rs_counter + 1, f.epoch * gridDim.x, f.limit_ns);
+            }
             const uint64_t tw0 = global_ns();
             for (int j = 0; j < f.world && ok; ++j) ok = wait_counter(f.flags[f.rank] + f.done_row * f.world + j, f.epoch, f.limit_ns);
             atomicMax(&g_fused_stats[5], (unsigned long long)(global_ns() - tw0));
@@ -1105,7 +1184,8 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     p.bn = tc.bn;
     const int ncta = tc.cta2 ? 2 : 1;
     const uint32_t stage_bytes = BM * BK * 2 + (p.bn / ncta) * BK * 2;
-    int stages = (int)((SMEM_BUDGET - 1024) / stage_bytes);
+    const uint32_t out_stage_bytes = (fused && fused->mode == 1) ? BM * OUT_PITCH : 0;
+    int stages = (int)((SMEM_BUDGET - 1024 - out_stage_bytes) / stage_bytes);
     p.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
     p.m_blocks = (int)((m + BM * ncta - 1) / (BM * ncta));
     p.n_blocks = (int)((n + p.bn - 1) / p.bn);
@@ -1118,6 +1198,11 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     p.group_m = group_env > 0 ? group_env : 16;
     if (p.group_m > p.m_blocks) p.group_m = p.m_blocks;
     if (fused && fused->mode == 3) p.group_m = p.m_blocks;  // all row tiles of one weight chunk in a row: chunks are needed in order
+    const bool rs_early = fused && fused->mode == 1 && fused->rs_rows % (BM * ncta) == 0;
+    if (rs_early) {
+        const int per_rank = (int)(fused->rs_rows / (BM * ncta));
+        while (per_rank % p.group_m) --p.group_m;   // groups must not mix rows of this rank with rows of others
+    }
     if (fused && fused->mode == 2) {
         // groups must not straddle the rows of two ranks (the tile order is rotated rank by rank)
         const int per_rank = (int)(fused->ag_rows / (BM * ncta));
@@ -1140,7 +1225,8 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     if (rc) return rc;
 
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * batch_inner * batch_outer;
-    p.hdr_off = (uint32_t)p.stages * stage_bytes;
+    p.out_stage_off = (uint32_t)p.stages * stage_bytes;
+    p.hdr_off = p.out_stage_off + out_stage_bytes;
     if (comm_ctas > 0 && p.hdr_off < PUSH_STAGES * PUSH_PIECE_BYTES) p.hdr_off = PUSH_STAGES * PUSH_PIECE_BYTES;
     const size_t smem = (size_t)p.hdr_off + sizeof(SharedHeader) + 1024;
     FusedComm none;
@@ -1150,6 +1236,11 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
         const unsigned grid = (unsigned)(ncta * (tiles < compute ? tiles : compute)) + comm_ctas;
         FusedComm fc = *fused;
         if (fc.mode == 3) fc.bg_first_block = (int)(((fc.bg_first / k) / p.bn) % p.n_blocks);
+        if (fc.mode == 1) {
+            fc.rs_early = rs_early ? 1 : 0;
+            fc.rs_bpr = rs_early ? (int)(fc.rs_rows / (BM * ncta)) : 0;
+            fc.rs_remote_tiles = rs_early ? (int64_t)(p.m_blocks - fc.rs_bpr) * p.n_blocks : 0;
+        }
         if (!tc.cta2) {
             if (fc.mode == 1) gemm_tcgen05_kernel<false, 1><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);
             else if (fc.mode == 2) gemm_tcgen05_kernel<false, 2><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p, fc);

@@ -89,15 +89,25 @@ class GPTBlockFunction(torch.autograd.Function):
             _native.check(lib.bmt_gpt_block_forward(ctypes.byref(blk), _native.stream_handle()), "GPT block forward")
         else:
             # the block's parameters are still on their way: norms and biases first; the QKV weight is gathered by the GEMM
-            # that consumes it while the other big weights travel on the peer stream at the same time (measured faster than
-            # sending them after the GEMM); they have the attention core's duration to arrive before the output projection
+            # that consumes it; the other big weights travel on the peer stream and have the attention core's duration to
+            # arrive before the output projection.  They start together with the GEMM ("before") or when it is done
+            # ("after", so that the QKV weight has the links to itself): BMT_REST_PUSH, default by group size.
+            import os
+
             from ..parallel import fused_ops
 
             cur = torch.cuda.current_stream()
             cur.wait_event(deferred["ev_small"])
             _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 1, 1, _native.stream_handle()), "GPT block forward")
-            ev_rest = deferred["push_rest"]()
-            fused_ops.zero_gather_gemm(saved["ln1"], saved["qkv"], params[3], deferred)
+            when = os.environ.get("BMT_REST_PUSH") or ("before" if deferred["bucket"].comm.size <= 2 else "after")
+            if when == "before":
+                ev_rest = deferred["push_rest"]()
+                fused_ops.zero_gather_gemm(saved["ln1"], saved["qkv"], params[3], deferred)
+            else:
+                fused_ops.zero_gather_gemm(saved["ln1"], saved["qkv"], params[3], deferred)
+                ev_gemm = torch.cuda.Event()
+                ev_gemm.record(cur)
+                ev_rest = deferred["push_rest"](ev_gemm)
             _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 3, 5, _native.stream_handle()), "GPT block forward")
             cur.wait_event(ev_rest)
             _native.check(lib.bmt_gpt_block_forward_steps(ctypes.byref(blk), 6, 9, _native.stream_handle()), "GPT block forward")

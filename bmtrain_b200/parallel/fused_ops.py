@@ -87,7 +87,7 @@ def gemm_rs(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
     epoch = rt.next_epoch(free_row)
     rt.epochs[done_row] = epoch
     if key not in _counters:
-        _counters[key] = torch.zeros(1, dtype=torch.int32, device=x.device)
+        _counters[key] = torch.zeros(2, dtype=torch.int32, device=x.device)
     out = torch.empty(rows, N, dtype=x.dtype, device=x.device)
     d = _GemmDesc()
     d.m, d.n, d.k = M, N, K
