@@ -18,6 +18,7 @@ from .wrapper import BMTrainModelWrapper
 from .pipe_layer import PipelineTransformerBlockList
 from .utils import print_block, print_dict, print_rank, see_memory, load_nccl_pypi
 from . import debug
+from . import watchdog
 from .store import save, load
 
 from . import loss

@@ -242,6 +242,9 @@ def is_initialized() -> bool:
 
 def shutdown() -> None:
     """Tear the process groups down (tests call this between cases)."""
+    from . import watchdog
+
+    watchdog.stop()
     if config.get("device") is not None and config["device"].type == "cuda":
         from .parallel import symm
 

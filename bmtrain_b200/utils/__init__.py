@@ -101,3 +101,6 @@ class AverageRecorder:
         if self._steps <= 0:
             return self._value
         return self._value / (1 - pow(self.alpha, self._steps))
+
+
+from .profiling import StepTimer  # noqa: E402  (needs the helpers above)

@@ -177,3 +177,52 @@ def test_peer_failure_is_detected_not_hung():
         for p in procs:
             if p.is_alive():
                 p.kill()
+
+
+def body_heartbeat():
+    """A rank whose heartbeat stops is reported by the others within the timeout, and forgiven when it comes back."""
+    import time
+
+    import bmtrain_b200 as bmt
+
+    rank = bmt.rank()
+    fired = []
+    hb = bmt.watchdog.start(interval=0.1, timeout=0.8, on_failure=lambda lost: fired.extend(lost))
+    time.sleep(0.5)
+    bmt.watchdog.check()  # everybody alive
+    if rank == 1:
+        hb.pause()        # looks hung to the others; the process itself stays healthy
+        time.sleep(3.0)
+        hb.resume()
+        time.sleep(1.0)
+    else:
+        deadline = time.time() + 5.0
+        while not hb.lost_ranks() and time.time() < deadline:
+            time.sleep(0.05)
+        assert hb.lost_ranks() == [1], hb.lost_ranks()
+        assert fired == [1]
+        try:
+            bmt.watchdog.check()
+        except RuntimeError as exc:
+            assert "rank(s) [1]" in str(exc)
+        else:
+            raise AssertionError("check() did not raise")
+        deadline = time.time() + 6.0
+        while hb.lost_ranks() and time.time() < deadline:
+            time.sleep(0.05)
+        assert hb.lost_ranks() == []  # rank 1 resumed
+    x = torch.ones(1)
+    assert float(bmt.distributed.all_reduce(x, "sum")) == bmt.world_size()
+    # phases of a step, reduced as the maximum over ranks
+    timer = bmt.utils.StepTimer()
+    with timer.phase("a"):
+        time.sleep(0.02 * (rank + 1))
+    with timer.phase("b"):
+        time.sleep(0.01)
+    out = timer.finish_step()
+    assert out["a"] >= 0.02 * bmt.world_size() * 1e3 * 0.9 and abs(out["total"] - out["a"] - out["b"]) < 30.0
+    assert set(timer.averages()) == {"a", "b", "total"}
+
+
+def test_heartbeat_and_step_timer():
+    run_distributed("test_dist_cpu", "body_heartbeat", 2)
