@@ -38,3 +38,8 @@ def fused_sumexp(logits: torch.Tensor, max_logits: torch.Tensor) -> torch.Tensor
 def fused_softmax_inplace(logits: torch.Tensor, max_logits: torch.Tensor, sum_exp_logits: torch.Tensor) -> None:
     """``logits <- exp(logits - max) / sum`` in place."""
     logits.copy_(torch.exp(logits.float() - max_logits[:, None].float()) / sum_exp_logits[:, None].float())
+
+
+def is_bf16_supported() -> bool:
+    """bf16 kernels are always built here (the reference probes its CUDA version: ``csrc/cuda/has_inf_nan.cu:139-145``)."""
+    return True

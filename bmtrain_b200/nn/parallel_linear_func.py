@@ -65,6 +65,43 @@ def preprocess_input(input, gather_input, split_input):
     return input
 
 
+def async_all_gather_linear_func(input, weight, bias, async_chunks=2):
+    """``all_gather_tokens(input) @ weight^T + bias`` (reference: ``bmtrain/nn/parallel_linear_func.py:26-61``, which
+    overlaps by cutting the tokens into ``async_chunks`` rounds; here the fused kernel overlaps tile by tile)."""
+    tp = config["tp_size"]
+    x2 = input.reshape(-1, input.shape[-1])
+    out = tp_fused.all_gather_gemm(x2, weight, bias, config["tp_comm"])
+    return out.view(input.shape[0] * tp, *input.shape[1:-1], weight.shape[0])
+
+
+def async_reduce_scatter_linear_func(input, weight, bias, async_chunks=2):
+    """``reduce_scatter_tokens(input @ weight^T) + bias`` (reference: ``bmtrain/nn/parallel_linear_func.py:64-105``)."""
+    tp = config["tp_size"]
+    x2 = input.reshape(-1, input.shape[-1])
+    out = tp_fused.gemm_reduce_scatter(x2, weight, bias, config["tp_comm"])
+    return out.view(input.shape[0] // tp, *input.shape[1:-1], weight.shape[0])
+
+
+def async_all_gather_linear_backward_func(grad_out, input, weight, bias, async_chunks=2):
+    """Backward of the row-parallel GEMM -> reduce-scatter: the output gradient is all-gathered over the tokens, then
+    ``grad_input = G @ W``, ``grad_weight = G^T @ input``, ``grad_bias = sum(G)``
+    (reference: ``bmtrain/nn/parallel_linear_func.py:108-200``)."""
+    comm = config["tp_comm"]
+    x2 = input.reshape(-1, input.shape[-1])
+    g_local = grad_out.reshape(-1, grad_out.shape[-1])
+    grad_input = grad_weight = grad_bias = None
+    if input.requires_grad:
+        gx, g_all = tp_fused.all_gather_gemm(g_local, weight, None, comm, b_is_kn=True, return_gathered=True)
+        grad_input = gx.view(input.shape)
+    else:
+        g_all = _gather_tokens(g_local)
+    if weight.requires_grad:
+        grad_weight = _gemm.gemm_tn(g_all, x2)
+    if bias is not None and bias.requires_grad:
+        grad_bias = _gemm.bias_grad(g_all)
+    return grad_input, grad_weight, grad_bias
+
+
 class OpParallelLinear(torch.autograd.Function):
     """Linear layer with the tensor-parallel collectives folded in (see the module docstring)."""
 

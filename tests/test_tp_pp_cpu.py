@@ -137,3 +137,39 @@ def test_pipeline_gpt_cpu():
 
 def test_pipeline_with_zero_cpu():
     run_distributed("test_tp_pp_cpu", "body_pipe", 4, init_kwargs=dict(pipe_size=2, num_micro_batches=4))
+
+
+def body_tp_helpers():
+    """The reference-named helper functions of the tensor-parallel linear core against plain collectives + matmul."""
+    import bmtrain_b200 as bmt
+    from bmtrain_b200.nn import parallel_linear_func as P
+
+    comm = bmt.config["tp_comm"]
+    tp, r = comm.size, comm.rank
+    torch.manual_seed(3)
+    x_all = torch.randn(tp * 6, 10)
+    w = torch.randn(8, 10, requires_grad=True)
+    b = torch.randn(8, requires_grad=True)
+    x_loc = x_all[r * 6:(r + 1) * 6].clone().requires_grad_()
+    out = P.async_all_gather_linear_func(x_loc, w, b)
+    assert torch.allclose(out, x_all @ w.t() + b, atol=1e-5)
+    # row-parallel: every rank holds a slice of the features, the sum over ranks is scattered over the tokens
+    torch.manual_seed(5 + r)
+    xr = torch.randn(tp * 6, 10)
+    wr = torch.randn(8, 10)
+    full = xr @ wr.t()
+    tot = bmt.distributed.all_reduce(full.clone(), "sum")
+    got = P.async_reduce_scatter_linear_func(xr, wr, None)
+    assert torch.allclose(got, tot[r * 6:(r + 1) * 6], atol=1e-4)
+    # backward helper: gathers the output gradient
+    g_loc = torch.randn(6, 8)
+    g_all = torch.cat(bmt.distributed.all_gather(g_loc).unbind(0), dim=0)
+    xin = torch.randn(tp * 6, 10, requires_grad=True)
+    wk = torch.randn(8, 10, requires_grad=True)
+    gi, gw, gb = P.async_all_gather_linear_backward_func(g_loc, xin, wk, b)
+    assert torch.allclose(gi, g_all @ wk, atol=1e-4) and torch.allclose(gw, g_all.t() @ xin, atol=1e-4)
+    assert torch.allclose(gb, g_all.sum(0), atol=1e-4)
+
+
+def test_tp_helper_functions_cpu():
+    run_distributed("test_tp_pp_cpu", "body_tp_helpers", 2, init_kwargs=dict(tp_size=2))
