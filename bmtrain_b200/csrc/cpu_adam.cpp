@@ -149,50 +149,72 @@ __attribute__((target("avx512f,avx512bw,avx512vl"))) inline __m512 load_half16(c
     if (bf16) return _mm512_castsi512_ps(_mm512_slli_epi32(_mm512_cvtepu16_epi32(raw), 16));
     return _mm512_cvtph_ps(raw);
 }
-__attribute__((target("avx512f,avx512bw,avx512vl"))) inline void store_half16(uint16_t* p, __m512 x, bool bf16) {
-    if (!bf16) {
-        _mm256_storeu_si256((__m256i*)p, _mm512_cvtps_ph(x, _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC));
-        return;
-    }
+__attribute__((target("avx512f,avx512bw,avx512vl"))) inline __m256i to_half16(__m512 x, bool bf16) {
+    if (!bf16) return _mm512_cvtps_ph(x, _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC);
     const __m512i u = _mm512_castps_si512(x);
     const __m512i lsb = _mm512_and_si512(_mm512_srli_epi32(u, 16), _mm512_set1_epi32(1));
     const __m512i rounded = _mm512_add_epi32(u, _mm512_add_epi32(lsb, _mm512_set1_epi32(0x7fff)));
     const __mmask16 nan = _mm512_cmp_ps_mask(x, x, _CMP_UNORD_Q);
     const __m512i quiet = _mm512_or_si512(u, _mm512_set1_epi32(0x00400000));
     const __m512i sel = _mm512_mask_blend_epi32(nan, rounded, quiet);
-    _mm256_storeu_si256((__m256i*)p, _mm512_cvtepi32_epi16(_mm512_srli_epi32(sel, 16)));
+    return _mm512_cvtepi32_epi16(_mm512_srli_epi32(sel, 16));
+}
+__attribute__((target("avx512f,avx512bw,avx512vl"))) inline void store_half16(uint16_t* p, __m512 x, bool bf16) {
+    _mm256_storeu_si256((__m256i*)p, to_half16(x, bf16));
+}
+
+struct __attribute__((target("avx512f"))) AdamVec {
+    __m512 b1, ob1, b2, ob2, eps, lr, isc, lrwd, ibc1, ibc2;
+    __m512d s0, q0;
+};
+
+// 16 elements at `at`: updates m, v and the fp32 parameters in place and returns the new parameters.
+template <bool BF16>
+__attribute__((target("avx512f,avx512bw,avx512vl"))) inline __m512 adam16(int64_t at, float* p, const uint16_t* g, float* m, float* v,
+                                                                           AdamVec& k, bool stats) {
+    const __m512 gf = _mm512_mul_ps(load_half16(g + at, BF16), k.isc);
+    const __m512 mm = _mm512_fmadd_ps(k.b1, _mm512_loadu_ps(m + at), _mm512_mul_ps(k.ob1, gf));
+    const __m512 vv = _mm512_fmadd_ps(k.b2, _mm512_loadu_ps(v + at), _mm512_mul_ps(k.ob2, _mm512_mul_ps(gf, gf)));
+    const __m512 old = _mm512_loadu_ps(p + at);
+    const __m512 den = _mm512_add_ps(_mm512_sqrt_ps(_mm512_mul_ps(vv, k.ibc2)), k.eps);
+    const __m512 upd = _mm512_div_ps(_mm512_mul_ps(mm, k.ibc1), den);
+    __m512 np = _mm512_fnmadd_ps(k.lr, upd, old);
+    np = _mm512_fnmadd_ps(k.lrwd, old, np);
+    _mm512_storeu_ps(m + at, mm);
+    _mm512_storeu_ps(v + at, vv);
+    _mm512_storeu_ps(p + at, np);
+    if (stats) {
+        const __m512 d = _mm512_sub_ps(np, old);
+        const __m512d lo = _mm512_cvtps_pd(_mm512_castps512_ps256(d)), hi = _mm512_cvtps_pd(_mm256_castpd_ps(_mm512_extractf64x4_pd(_mm512_castps_pd(d), 1)));
+        k.s0 = _mm512_add_pd(k.s0, _mm512_add_pd(lo, hi));
+        k.q0 = _mm512_add_pd(k.q0, _mm512_fmadd_pd(lo, lo, _mm512_mul_pd(hi, hi)));
+    }
+    return np;
 }
 
 template <bool BF16>
 __attribute__((target("avx512f,avx512bw,avx512vl")))
 void adam_avx512(int64_t b, int64_t e, float* p, uint16_t* ph, const uint16_t* g, float* m, float* v, const AdamConst& c,
                  double* dsum, double* dsq) {
-    const __m512 b1 = _mm512_set1_ps(c.beta1), ob1 = _mm512_set1_ps(1.f - c.beta1);
-    const __m512 b2 = _mm512_set1_ps(c.beta2), ob2 = _mm512_set1_ps(1.f - c.beta2);
-    const __m512 eps = _mm512_set1_ps(c.eps), lr = _mm512_set1_ps(c.lr), isc = _mm512_set1_ps(c.inv_scale);
-    const __m512 lrwd = _mm512_set1_ps(c.lr * c.wd), ibc1 = _mm512_set1_ps(c.inv_bc1), ibc2 = _mm512_set1_ps(c.inv_bc2);
-    __m512d s0 = _mm512_setzero_pd(), q0 = _mm512_setzero_pd();
+    AdamVec k;
+    k.b1 = _mm512_set1_ps(c.beta1); k.ob1 = _mm512_set1_ps(1.f - c.beta1);
+    k.b2 = _mm512_set1_ps(c.beta2); k.ob2 = _mm512_set1_ps(1.f - c.beta2);
+    k.eps = _mm512_set1_ps(c.eps); k.lr = _mm512_set1_ps(c.lr); k.isc = _mm512_set1_ps(c.inv_scale);
+    k.lrwd = _mm512_set1_ps(c.lr * c.wd); k.ibc1 = _mm512_set1_ps(c.inv_bc1); k.ibc2 = _mm512_set1_ps(c.inv_bc2);
+    k.s0 = _mm512_setzero_pd(); k.q0 = _mm512_setzero_pd();
+    const bool stats = dsum != nullptr;
     int64_t i = b;
-    for (; i + 16 <= e; i += 16) {
-        const __m512 gf = _mm512_mul_ps(load_half16(g + i, BF16), isc);
-        const __m512 mm = _mm512_fmadd_ps(b1, _mm512_loadu_ps(m + i), _mm512_mul_ps(ob1, gf));
-        const __m512 vv = _mm512_fmadd_ps(b2, _mm512_loadu_ps(v + i), _mm512_mul_ps(ob2, _mm512_mul_ps(gf, gf)));
-        const __m512 old = _mm512_loadu_ps(p + i);
-        const __m512 den = _mm512_add_ps(_mm512_sqrt_ps(_mm512_mul_ps(vv, ibc2)), eps);
-        const __m512 upd = _mm512_div_ps(_mm512_mul_ps(mm, ibc1), den);
-        __m512 np = _mm512_fnmadd_ps(lr, upd, old);
-        np = _mm512_fnmadd_ps(lrwd, old, np);
-        _mm512_storeu_ps(m + i, mm);
-        _mm512_storeu_ps(v + i, vv);
-        _mm512_storeu_ps(p + i, np);
-        store_half16(ph + i, np, BF16);
-        if (dsum) {
-            const __m512 d = _mm512_sub_ps(np, old);
-            const __m512d lo = _mm512_cvtps_pd(_mm512_castps512_ps256(d)), hi = _mm512_cvtps_pd(_mm256_castpd_ps(_mm512_extractf64x4_pd(_mm512_castps_pd(d), 1)));
-            s0 = _mm512_add_pd(s0, _mm512_add_pd(lo, hi));
-            q0 = _mm512_add_pd(q0, _mm512_fmadd_pd(lo, lo, _mm512_mul_pd(hi, hi)));
-        }
+    // the half-precision output is write-only: whole cache lines of it go out with non-temporal stores, which saves the
+    // read-for-ownership of a line that would only be overwritten (the step is bound by host memory traffic)
+    while (i + 16 <= e && (((uintptr_t)(ph + i)) & 63)) { store_half16(ph + i, adam16<BF16>(i, p, g, m, v, k, stats), BF16); i += 16; }
+    for (; i + 32 <= e; i += 32) {
+        const __m256i h0 = to_half16(adam16<BF16>(i, p, g, m, v, k, stats), BF16);
+        const __m256i h1 = to_half16(adam16<BF16>(i + 16, p, g, m, v, k, stats), BF16);
+        _mm512_stream_si512((__m512i*)(ph + i), _mm512_inserti64x4(_mm512_castsi256_si512(h0), h1, 1));
     }
+    for (; i + 16 <= e; i += 16) store_half16(ph + i, adam16<BF16>(i, p, g, m, v, k, stats), BF16);
+    _mm_sfence();   // non-temporal stores are ordered before whatever signals that this range is done
+    const __m512d s0 = k.s0, q0 = k.q0;
     if (dsum) { *dsum += _mm512_reduce_add_pd(s0); *dsq += _mm512_reduce_add_pd(q0); }
     if (i < e) adam_scalar<BF16>(i, e, p, ph, g, m, v, c, dsum, dsq);
 }
