@@ -379,11 +379,15 @@ class Block(torch.nn.Module):
 
         mod = self._module
         name = getattr(mod, "_bmt_first_gemm", None)
-        # BMT_FUSED_GATHER: "0" never, "1" whenever possible, "auto" (default) only for the recomputation in backward.  The
-        # fused path needs more host work before the first kernel can start; that is hidden while the host runs ahead of
-        # the device (backward) and exposed at the cold start of a forward pass, where the plain all-gather is faster.
+        # BMT_FUSED_GATHER: "0" never, "1" whenever possible, "auto" (default): for the recomputation in backward in ZeRO
+        # groups of two.  Measured on B200s (benchmark/fused.py): with the device kept busy while the block is enqueued the
+        # fused path takes 0.57 ms against 0.64 ms for all-gather + block on 2 GPUs, but 0.78 / 0.83 ms against 0.63 / 0.69 ms
+        # on 4 / 8 GPUs (three cross-rank hand-shakes instead of one expose the skew between ranks), and at the cold start
+        # of a forward pass its extra host work makes it slower everywhere.
         policy = os.environ.get("BMT_FUSED_GATHER", "auto")
-        if name is None or policy == "0" or (policy == "auto" and not backward) or self._ref_block is not None:
+        if name is None or policy == "0" or self._ref_block is not None:
+            return False
+        if policy == "auto" and not (backward and all(b.comm.size <= 2 for b in self._buckets.values())):
             return False
         if any(b.full is not None for b in self._buckets.values()) or not mod._bmt_can_fuse_first_gemm(*args):
             return False

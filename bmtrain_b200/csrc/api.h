@@ -175,11 +175,28 @@ int bmt_zero_gather_expected(int64_t n, int64_t k, int world, const int64_t* fir
 // number of kernel launches issued by this library since load (for launch accounting)
 int64_t bmt_launch_count(void);
 void bmt_count_launch(int n);
-// status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out; reading clears it
 // SM copy of nbytes (multiple of 16) between device pointers, either of which may be a mapped peer buffer.
 int bmt_peer_copy(void* dst, const void* src, int64_t nbytes, int grid, void* stream);
 // Number of pusher CTAs that balances math and transfer of a fused all-gather -> GEMM / ZeRO gather -> GEMM kernel.
 int bmt_fused_comm_ctas(double flops, double push_bytes, double remote_bytes);
+
+// One chunk of an offloaded Adam step: wait for the gradient copy (grad_ready: cudaEvent_t or NULL), run the host Adam
+// on the pinned arrays, send the new half parameters to the device.
+typedef struct {
+    void* grad_ready;
+    void* p32; void* p16_host; const void* g16_host; void* m; void* v;
+    void* p_dev;
+    int64_t n;
+    float beta1, beta2, eps, lr, scale, wd, bc1, bc2;
+    int bf16;
+} BmtOffloadChunk;
+// Host Adam entry point of the CPU library (bmt_adam_cpu_fp16 / bmt_adam_cpu_bf16), passed in by address.
+typedef void (*BmtAdamCpuFn)(int64_t n, void* p32, void* p16, void* delta, const void* g16, void* m, void* v, float beta1,
+                             float beta2, float eps, float lr, float scale, float wd, float bc1, float bc2);
+// Runs the chunks in order on the calling thread; uploads go to `h2d_stream` with cudaMemcpyAsync.  Returns 0 or the
+// first CUDA error.
+int bmt_offload_adam_run(const BmtOffloadChunk* chunks, int n, BmtAdamCpuFn fn_fp16, BmtAdamCpuFn fn_bf16, void* h2d_stream);
+// status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out; reading clears it
 int bmt_gemm_status(void);
 // Timing counters of the fused compute+collective GEMM kernels since the last call, in nanoseconds: out[0] sum over
 // compute CTAs of producer time spent waiting for other ranks' data, out[1] longest pusher CTA, out[2] longest CTA,

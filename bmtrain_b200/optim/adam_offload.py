@@ -13,6 +13,8 @@ reference, so checkpoints resume bit-identically.
 """
 from __future__ import annotations
 
+import ctypes
+import math
 from collections import defaultdict
 from copy import deepcopy
 from itertools import chain
@@ -24,6 +26,16 @@ from ._distributed import state_dict_gather
 from .adam import _partition_bounds, _zero_grad
 
 _CHUNK = 1 << 23  # elements per pipeline stage (16 MiB of half data)
+
+
+class _OffloadChunk(ctypes.Structure):
+    """Mirror of ``BmtOffloadChunk`` (``csrc/api.h``)."""
+
+    _fields_ = [("grad_ready", ctypes.c_void_p), ("p32", ctypes.c_void_p), ("p16_host", ctypes.c_void_p),
+                ("g16_host", ctypes.c_void_p), ("m", ctypes.c_void_p), ("v", ctypes.c_void_p), ("p_dev", ctypes.c_void_p),
+                ("n", ctypes.c_int64), ("beta1", ctypes.c_float), ("beta2", ctypes.c_float), ("eps", ctypes.c_float),
+                ("lr", ctypes.c_float), ("scale", ctypes.c_float), ("wd", ctypes.c_float), ("bc1", ctypes.c_float),
+                ("bc2", ctypes.c_float), ("bf16", ctypes.c_int)]
 
 
 def _pinned(shape, dtype, pin):
@@ -313,6 +325,9 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
                     ev.record(d2h)
                     work[i] = (p, state, group, lo, hi, ev)
 
+        if on_gpu and not self.record_delta:
+            work = self._run_native(work, stepped, scale, h2d)
+
         sum_delta = sum_sq_delta = 0.0
         total_numel = 0
         for p, state, group, lo, hi, ev in work:
@@ -380,6 +395,50 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
             self.avg_delta = sum_delta / total_numel
             self.var_delta = sum_sq_delta / total_numel - self.avg_delta ** 2
         return loss
+
+    def _run_native(self, work, stepped, scale, h2d):
+        """Hand the half-precision device parameters' chunks to the native chunk loop (event wait -> host Adam -> upload,
+        ``csrc/runtime.cu``) in one call; returns the work items it does not cover (fp32 parameters, host tensors)."""
+        from ..ops import _native
+
+        cuda_lib, cpu_lib = _native.cuda_lib(), _native.cpu_lib()
+        if cpu_lib is None:
+            return work
+        rest, fast = [], []
+        for item in work:
+            p, state, group, lo, hi, ev = item
+            if p.is_cuda and p.dtype in (torch.float16, torch.bfloat16) and not group.get("maximize", False) and hi > lo:
+                fast.append(item)
+            else:
+                rest.append(item)
+        if not fast:
+            return work
+        arr = (_OffloadChunk * len(fast))()
+        es = 2
+        for c, (p, state, group, lo, hi, ev) in zip(arr, fast):
+            if id(p) not in stepped:
+                stepped.add(id(p))
+                state["step"] += 1
+            step = state["step"]
+            beta1, beta2 = group["betas"]
+            c.grad_ready = ev.cuda_event if ev is not None else None
+            c.p32 = state["_param_fp32"].data_ptr() + lo * 4
+            c.p16_host = state["_param_fp16"].data_ptr() + lo * es
+            c.g16_host = state["_grad_fp16"].data_ptr() + lo * es
+            c.m = state["exp_avg"].data_ptr() + lo * 4
+            c.v = state["exp_avg_sq"].data_ptr() + lo * 4
+            c.p_dev = p.data.data_ptr() + lo * es
+            c.n = hi - lo
+            c.beta1, c.beta2, c.eps = beta1, beta2, group["eps"]
+            c.lr = 0.0 if step < self._hold_steps else group["lr"]
+            c.scale, c.wd = scale, group["weight_decay"]
+            c.bc1, c.bc2 = 1.0 - math.pow(beta1, step), 1.0 - math.pow(beta2, step)
+            c.bf16 = 1 if p.dtype == torch.bfloat16 else 0
+        fn16 = ctypes.cast(cpu_lib.bmt_adam_cpu_fp16, ctypes.c_void_p)
+        fnbf = ctypes.cast(cpu_lib.bmt_adam_cpu_bf16, ctypes.c_void_p)
+        _native.check(cuda_lib.bmt_offload_adam_run(arr, ctypes.c_int(len(fast)), fn16, fnbf, ctypes.c_void_p(h2d.cuda_stream)),
+                      "offloaded Adam chunk loop")
+        return rest
 
     def get_avg_delta(self):
         return self.avg_delta if self.record_delta else 0
