@@ -305,3 +305,28 @@ def test_offload_adam_gpu_streamed_matches_host_math(dev, dtype, math):
         for key in ("exp_avg", "exp_avg_sq", "_param_fp32"):
             assert not sa["state"][i][key].is_cuda
             assert torch.allclose(sa["state"][i][key], sb["state"][i][key], atol=1e-5, rtol=1e-4), (i, key)
+
+
+def test_peer_copy_and_fused_helpers(dev):
+    """Small native helpers of the peer-memory runtime that need no second GPU: the SM copy kernel (here local to local),
+    the pusher-count heuristic and the fused kernels' timing counters."""
+    import ctypes
+
+    from bmtrain_b200.ops import _native
+    from bmtrain_b200.parallel import fused_ops
+
+    lib = _native.cuda_lib()
+    src = torch.randint(0, 255, (3 * 1024 * 1024 + 48,), dtype=torch.uint8, device=dev)
+    dst = torch.zeros_like(src)
+    for grid in (1, 37, 148):
+        dst.zero_()
+        _native.check(lib.bmt_peer_copy(_native.ptr(dst), _native.ptr(src), ctypes.c_int64(src.numel()), ctypes.c_int(grid),
+                                        _native.stream_handle()), "peer copy")
+        assert torch.equal(dst, src)
+    assert lib.bmt_peer_copy(_native.ptr(dst), _native.ptr(src), ctypes.c_int64(17), ctypes.c_int(4), _native.stream_handle()) != 0
+    # compute-bound problems get few pusher CTAs, transfer-bound ones many; always a multiple of 4 that leaves SMs for math
+    few = lib.bmt_fused_comm_ctas(ctypes.c_double(6.4e11), ctypes.c_double(4e7), ctypes.c_double(4e7))
+    many = lib.bmt_fused_comm_ctas(ctypes.c_double(4e10), ctypes.c_double(4e7), ctypes.c_double(4e7))
+    assert 8 <= few < many <= 116 and few % 4 == 0 and many % 4 == 0
+    stats = fused_ops.kernel_stats()
+    assert stats["kernels"] == 0 and stats["pusher_us_max"] == 0.0
