@@ -43,20 +43,78 @@ def parse():
 
 
 class ClockSampler:
-    """Samples SM clocks / throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clocks, power and throttle reasons of this rank's GPU while the timed region runs.
+
+    The figures are the ones `nvidia-smi --query-gpu=clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.*` prints,
+    read through NVML from a thread of this process every 100 ms: a looping nvidia-smi process needs a CPU core of its own
+    (more than 100 ms per sample here), which slows the host-side optimizer of the rank it shares cores with and, through
+    the max over ranks, the whole job.  Without the NVML binding the nvidia-smi loop is used at a slower rate.
+    """
 
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, index: int):
-        self.proc = None
+        self.proc = self.thread = None
+        self.sm, self.mx, self.power, self.reasons = [], [], [], set()
+        try:
+            import threading
+
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._nvml, self._handle = pynvml, handle
+            self._sample()  # fails here, not in the thread, when a query is unsupported
+            self._stop = threading.Event()
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+            self.sm, self.mx, self.power, self.reasons = [], [], [], set()
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "500"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
 
+    def _sample(self):
+        n, h = self._nvml, self._handle
+        self.sm.append(float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)))
+        self.mx.append(float(n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)))
+        self.power.append(n.nvmlDeviceGetPowerUsage(h) / 1000.0)
+        get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        mask = int(get(h))
+        for name, bit in self.BITS:
+            if mask & bit:
+                self.reasons.add(name)
+
+    def _loop(self):
+        while not self._stop.wait(0.1):
+            try:
+                self._sample()
+            except Exception:
+                return
+
+    def _summary(self, source):
+        sm = self.sm
+        busy = sorted(sm)[len(sm) // 2:] if sm else []  # the top half of the samples are the ones taken under load
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(self.mx) if self.mx else None,
+                "power_w_max": max(self.power) if self.power else None, "samples": len(sm), "reasons": sorted(self.reasons),
+                "source": source}
+
     def stop(self):
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            return self._summary("NVML, 100 ms")
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -65,22 +123,18 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons, power = [], [], set(), []
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 8:
                 continue
             try:
-                sm.append(float(f[0])); mx.append(float(f[1])); power.append(float(f[2]))
+                self.sm.append(float(f[0])); self.mx.append(float(f[1])); self.power.append(float(f[2]))
             except ValueError:
                 continue
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
                 if val.lower().startswith("active"):
-                    reasons.add(name)
-        # the top half of the samples are the ones taken under load
-        busy = sorted(sm)[len(sm) // 2:] if sm else []
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                    self.reasons.add(name)
+        return self._summary("nvidia-smi -lms 500")
 
 
 def setup_env(args):

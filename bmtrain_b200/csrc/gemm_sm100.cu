@@ -48,7 +48,8 @@ struct GemmParams {
     int bn;           // tile N
     int stages;
     uint32_t hdr_off;      // byte offset of the barrier header behind the tile stages (pusher CTAs need room for their ring)
-    uint32_t out_stage_off;  // GEMM -> reduce-scatter: byte offset of the epilogue's row staging area (128 rows x OUT_PITCH)
+    uint32_t out_stage_off;  // byte offset of the epilogue's row staging area (128 rows x OUT_PITCH) when rows go out as bulk copies
+    int staged;              // plain GEMM: the epilogue stages rows in shared memory and writes them with bulk copies
     int a_mn, b_mn;   // 1 = MN-major operand
     int m_blocks, n_blocks;
     int64_t batch_inner, batch_outer, b_inner_div;
@@ -302,6 +303,49 @@ template <typename TA> __device__ __forceinline__ void apply_extras(const GemmPa
 #pragma unroll
         for (int i = 0; i < 8; ++i)
             if (c + i < col_end) vv[i] += bmt::Cvt<TA>::to_f(rr[i]);
+    }
+}
+
+// The arithmetic of epilogue_chunk without the store, for rows whose column count is a multiple of 8: v = final values of
+// the columns [col0, min(col0 + 32, col_end)) of this thread's row (alpha, bias, activation, mask / residual, old C).
+template <typename TC>
+__device__ __forceinline__ void epilogue_math(const GemmParams& p, const TC* crow, int64_t row, int64_t col0, int64_t col_end,
+                                              const uint32_t (&r)[32], float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int64_t c = col0 + g * 8;
+        if (c >= col_end) break;
+        float* vv = v + g * 8;
+        if (p.bias) {
+            float b[8];
+            if (p.bias_dtype == BMT_DT_F16) load8((const __half*)p.bias + c, b);
+            else if (p.bias_dtype == BMT_DT_BF16) load8((const __nv_bfloat16*)p.bias + c, b);
+            else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) b[i] = ((const float*)p.bias)[c + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vv[i] += b[i];
+        }
+        if (p.act == 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vv[i] = fmaxf(vv[i], 0.f);
+        } else if (p.act == 2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vv[i] = gelu_f(vv[i]);
+        }
+        if (p.aux_mode || p.residual) {
+            if (p.bias_dtype == BMT_DT_F16) apply_extras<__half>(p, row, c, col_end, vv);
+            else apply_extras<__nv_bfloat16>(p, row, c, col_end, vv);
+        }
+        if (p.accumulate) {
+            float old[8];
+            load8(crow + c, old);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vv[i] += old[i];
+        }
     }
 }
 
@@ -877,8 +921,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * p.bn;
             const int64_t tile_end = (int64_t)(n_blk + 1) * p.bn;
             const int64_t col_end = tile_end < p.N ? tile_end : p.N;
-            if (FUSED == 1) {
-                // staged bulk-store epilogue: pack OUT_CHUNK columns of the row in shared memory, one bulk copy to the owner
+            if (FUSED == 1 || p.staged) {
+                // staged bulk-store epilogue: pack OUT_CHUNK columns of the row in shared memory, one bulk copy per row chunk
+                // (to the row's owner in the GEMM -> reduce-scatter kernel)
                 const uint32_t srow = smem_u32(smem) + p.out_stage_off + (uint32_t)((quarter * 32 + lane) * OUT_PITCH);
                 for (int c0 = 0; c0 < p.bn; c0 += OUT_CHUNK) {
                     const int64_t col0 = (int64_t)n_blk * p.bn + c0;
@@ -890,10 +935,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                         uint32_t r[32];
                         tmem_ld32(taddr + c0 + sub, r);
                         tmem_ld_wait();
+                        float vals[32];
+                        if (FUSED == 1) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(r[i]) * p.alpha;
+                        } else if (row_ok) {
+                            if (p.c_dtype == BMT_DT_F16) epilogue_math<__half>(p, (const __half*)cbase + coff, row, col0 + sub, col_end, r, vals);
+                            else epilogue_math<__nv_bfloat16>(p, (const __nv_bfloat16*)cbase + coff, row, col0 + sub, col_end, r, vals);
+                        }
                         uint32_t pk[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const float a = __uint_as_float(r[2 * i]) * p.alpha, b = __uint_as_float(r[2 * i + 1]) * p.alpha;
+                            const float a = vals[2 * i], b = vals[2 * i + 1];
                             if (p.c_dtype == BMT_DT_F16) { __half2 h = __floats2half2_rn(a, b); pk[i] = *reinterpret_cast<uint32_t*>(&h); }
                             else { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); pk[i] = *reinterpret_cast<uint32_t*>(&h); }
                         }
@@ -928,7 +981,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
         }
         if (remote_open) report_remote_done();
-        if (FUSED == 1) {
+        if (FUSED == 1 || p.staged) {
             // row copies read this CTA's shared memory and write the inboxes: complete them before the teardown barrier
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
             asm volatile("fence.proxy.async.global;" ::: "memory");
@@ -1134,7 +1187,17 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     p.bn = tc.bn;
     const int ncta = tc.cta2 ? 2 : 1;
     const uint32_t stage_bytes = BM * BK * 2 + (p.bn / ncta) * BK * 2;
-    const uint32_t out_stage_bytes = (fused && fused->mode == 1) ? BM * OUT_PITCH : 0;
+    // The staged bulk-store epilogue of the GEMM -> reduce-scatter kernel can also serve plain GEMMs with 16-bit output
+    // (BMT_GEMM_STAGED=1; =2: only for K <= 4096).  Off by default: measured on the transformer-block shapes it is slower
+    // than the direct stores (797 vs 734 us over the 15 GEMMs of a block) because it costs a pipeline stage and local
+    // stores do not need the 256-byte packets that peer stores do.
+    static int staged_env = -1;
+    if (staged_env < 0) { const char* e = getenv("BMT_GEMM_STAGED"); staged_env = e ? atoi(e) : 0; }
+    const bool c16 = c_dtype == BMT_DT_F16 || c_dtype == BMT_DT_BF16;
+    const bool can_stage = !fused && c16 && (ldc % 8 == 0) && (((uintptr_t)c & 15) == 0) && ((c_bs0 | c_bs1) % 8 == 0) && (n % 8 == 0) &&
+                           (!bias || ((uintptr_t)bias & 15) == 0);
+    p.staged = (can_stage && (staged_env == 1 || (staged_env == 2 && k <= 4096))) ? 1 : 0;
+    const uint32_t out_stage_bytes = ((fused && fused->mode == 1) || p.staged) ? BM * OUT_PITCH : 0;
     int stages = (int)((SMEM_BUDGET - 1024 - out_stage_bytes) / stage_bytes);
     p.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
     p.m_blocks = (int)((m + BM * ncta - 1) / (BM * ncta));
