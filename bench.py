@@ -265,7 +265,7 @@ def main():
         skipped = 0
         bmt.synchronize()
         torch.cuda.synchronize()
-        sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+        sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 and os.environ.get("BMT_BENCH_NO_CLOCKS") != "1" else None
         l0 = launch_count()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()

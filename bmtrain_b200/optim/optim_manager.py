@@ -44,6 +44,34 @@ def check_overflow(param_groups) -> None:
         raise OverflowError("Gradient overflow")
 
 
+_status_host = {}
+
+
+def check_peer_status() -> None:
+    """Raise when a peer-memory kernel of an earlier step gave up waiting for another rank (its bounded wait ran out).
+
+    The status words are copied to pinned host memory without synchronising; the copy started by the previous call is the
+    one that is looked at, so a failure surfaces one step late instead of costing a host sync per step."""
+    if config["device"] is None or config["device"].type != "cuda":
+        return
+    from ..parallel import symm
+
+    for key, rt in symm._runtimes.items():
+        if rt is None:
+            continue
+        slot = _status_host.get(key)
+        if slot is not None:
+            host, event = slot
+            if event.query() and int(host[0]) != 0:
+                _status_host.pop(key, None)
+                rt.check()
+        host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        host.copy_(rt.status, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        _status_host[key] = (host, event)
+
+
 def grad_rescale(param_groups, scale) -> None:
     for group in param_groups:
         for p in group["params"]:
@@ -92,6 +120,7 @@ class OptimManager:
 
     def step(self):
         drain_pending()
+        check_peer_status()
         if self.loss_scale_enabled:
             has_overflow = False
             for optimizer in self.optimizers:

@@ -117,7 +117,9 @@ def ag_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
         x_local = x_local.contiguous()  # the pushers copy flat 32 KiB pieces
     lib = _native.cuda_lib()
     es = x_local.element_size()
-    base = ("ag", m, K, x_local.dtype)
+    # everything that decides how the pushers cut the rows (pusher count, runs per block) has to be constant per key: the
+    # per-block counters on the peers grow by the same amount every time the key's buffers are used
+    base = ("ag", m, K, N, x_local.dtype, b_is_kn)
     key = base + (_next_parity(base),)
     gathered = rt.slot(key, W * m * K * es)
     counters = rt.slot(key + ("cnt",), max(256, W * (m // 128) * 4))

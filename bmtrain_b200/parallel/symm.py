@@ -225,3 +225,9 @@ def reset() -> None:
                 buf.close()
             rt.flags.close()
     _runtimes.clear()
+    try:
+        from ..optim import optim_manager
+
+        optim_manager._status_host.clear()
+    except Exception:
+        pass

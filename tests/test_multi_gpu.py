@@ -121,6 +121,24 @@ def body_tp_fused():
                 comm.all_reduce(full, "sum")
                 got_kn = fused_ops.gemm_rs(xs, wkn, None, comm, True)
                 assert ((got_kn.float() - full[rank * m:(rank + 1) * m]).abs().max() / full.abs().max()).item() < tol
+    # same activation shape feeding weights of different widths and layouts back to back (the projections of one
+    # transformer block): every combination keeps its own buffers and counters
+    torch.manual_seed(77 + rank)
+    x_local = torch.randn(256, 1024, device="cuda", dtype=torch.bfloat16)
+    x_all = torch.empty(W * 256, 1024, device="cuda", dtype=torch.bfloat16)
+    comm.all_gather_into(x_all, x_local)
+    torch.manual_seed(8)
+    ws = [(torch.randn(n, 1024, device="cuda") * 0.05).to(torch.bfloat16) for n in (512, 4096, 1536)]
+    wk = (torch.randn(1024, 2048, device="cuda") * 0.05).to(torch.bfloat16)
+    for rep in range(3):
+        for w in ws:
+            out = fused_ops.ag_gemm(x_local, w, None, comm, False, False)
+            ref = G.gemm_nt(x_all, w).float()
+            assert ((out.float() - ref).abs().max() / ref.abs().max()).item() < 2e-2
+        out, gathered = fused_ops.ag_gemm(x_local, wk, None, comm, True, True)
+        ref = G.gemm_nn(x_all, wk).float()
+        assert torch.equal(gathered, x_all)
+        assert ((out.float() - ref).abs().max() / ref.abs().max()).item() < 2e-2
     torch.cuda.synchronize()
     rt.check()
     from bmtrain_b200.ops import _native
