@@ -74,7 +74,7 @@ def build_cpu(force: bool = False) -> str:
     target = os.path.join(HERE, "_cpu.so")
     sources = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cpp")]
     if sources and (force or _stale(target, sources)):
-        _run([os.environ.get("CXX", "g++"), *CXX_FLAGS, "-I", CSRC, "-o", target, *sources])
+        _run([os.environ.get("CXX", "g++"), *CXX_FLAGS, "-I", CSRC, "-o", target, *sources, "-lrt"])
     return target
 
 

@@ -70,6 +70,8 @@ class Communicator:
         self.size = len(self.ranks)
         self.rank = self.ranks.index(my_global_rank)
         self._gloo = group is not None and dist.get_backend(group) == "gloo"
+        self._shm = None          # shared-memory transport of CPU ranks (created on first use when BMT_CPU_COMM=shm)
+        self._shm_tried = False
 
     # ------------------------------------------------------------------ helpers
     def global_rank(self, group_rank: int) -> int:
@@ -81,6 +83,28 @@ class Communicator:
     def _needs_upcast(self, t: torch.Tensor) -> bool:
         return self._gloo and t.dtype in (torch.float16, torch.bfloat16)
 
+    def _shm_for(self, t: torch.Tensor, op=None):
+        """The shared-memory transport when it is enabled and can carry ``t`` (see ``comm/shm.py``), else None.  The first
+        call creates it collectively, so every rank of the group has to reach its first CPU collective together (which
+        collectives are anyway)."""
+        if not self._gloo or t.is_cuda:
+            return None
+        if not self._shm_tried:
+            import os
+
+            self._shm_tried = True
+            from ..global_var import config
+
+            if os.environ.get("BMT_CPU_COMM", "gloo") == "shm" and config.get("local_size") == config.get("world_size"):
+                from .shm import ShmTransport
+
+                self._shm = ShmTransport(self.group, self.ranks, self.rank)
+        if self._shm is None:
+            return None
+        from .shm import ShmTransport
+
+        return self._shm if ShmTransport.supports(t, op) else None
+
     # -------------------------------------------------------------- collectives
     def all_gather_into(self, out: torch.Tensor, inp: torch.Tensor, async_op: bool = False):
         """``out`` (size * inp.numel()) <- concatenation of every rank's ``inp``."""
@@ -89,6 +113,10 @@ class Communicator:
             out.view(-1).copy_(inp.reshape(-1))
             return DONE
         inp = inp.contiguous()
+        shm = self._shm_for(inp)
+        if shm is not None and out.is_contiguous() and out.dtype == inp.dtype:
+            shm.all_gather(out, inp)
+            return DONE
         work = dist.all_gather_into_tensor(out.view(-1), inp.view(-1), group=self.group, async_op=async_op)
         return work if async_op else DONE
 
@@ -102,9 +130,14 @@ class Communicator:
         if self._gloo:
             # gloo has no reduce-scatter: all-reduce a (fp32 for half types) copy, keep own slice
             tmp = inp.reshape(-1).to(torch.float32 if self._needs_upcast(inp) else inp.dtype, copy=True)
-            dist.all_reduce(tmp, op=_REDUCE_OPS["sum" if avg else op], group=self.group)
             n = out.numel()
-            piece = tmp[self.rank * n:(self.rank + 1) * n]
+            shm = self._shm_for(tmp, "sum" if avg else op)
+            if shm is not None:
+                piece = torch.empty(n, dtype=tmp.dtype)
+                shm.reduce_scatter(piece, tmp, "sum" if avg else op)
+            else:
+                dist.all_reduce(tmp, op=_REDUCE_OPS["sum" if avg else op], group=self.group)
+                piece = tmp[self.rank * n:(self.rank + 1) * n]
             if avg:
                 piece = piece / self.size
             out.view(-1).copy_(piece)
@@ -121,12 +154,20 @@ class Communicator:
         if self._gloo:
             if self._needs_upcast(t) or not t.is_contiguous():
                 tmp = t.to(torch.float32).contiguous()
-                dist.all_reduce(tmp, op=_REDUCE_OPS["sum" if avg else op], group=self.group)
+                shm = self._shm_for(tmp, "sum" if avg else op)
+                if shm is not None:
+                    shm.all_reduce(tmp, "sum" if avg else op)
+                else:
+                    dist.all_reduce(tmp, op=_REDUCE_OPS["sum" if avg else op], group=self.group)
                 if avg:
                     tmp /= self.size
                 t.copy_(tmp)
             else:
-                dist.all_reduce(t, op=_REDUCE_OPS["sum" if avg else op], group=self.group)
+                shm = self._shm_for(t, "sum" if avg else op)
+                if shm is not None:
+                    shm.all_reduce(t, "sum" if avg else op)
+                else:
+                    dist.all_reduce(t, op=_REDUCE_OPS["sum" if avg else op], group=self.group)
                 if avg:
                     if t.is_floating_point():
                         t /= self.size
@@ -145,6 +186,10 @@ class Communicator:
             tmp = t.contiguous()
             dist.broadcast(tmp, src=self.ranks[root], group=self.group)
             t.copy_(tmp)
+            return DONE
+        shm = self._shm_for(t)
+        if shm is not None:
+            shm.broadcast(t, root)
             return DONE
         work = dist.broadcast(t, src=self.ranks[root], group=self.group, async_op=async_op)
         return work if async_op else DONE

@@ -245,6 +245,11 @@ def shutdown() -> None:
     from . import watchdog
 
     watchdog.stop()
+    for value in list(config.values()) if hasattr(config, "values") else []:
+        shm = getattr(value, "_shm", None)
+        if shm is not None:
+            shm.close()
+            value._shm = None
     if config.get("device") is not None and config["device"].type == "cuda":
         from .parallel import symm
 
