@@ -330,3 +330,34 @@ def test_peer_copy_and_fused_helpers(dev):
     assert 8 <= few < many <= 116 and few % 4 == 0 and many % 4 == 0
     stats = fused_ops.kernel_stats()
     assert stats["kernels"] == 0 and stats["pusher_us_max"] == 0.0
+
+
+def test_bounded_wait_reports_instead_of_hanging(dev):
+    """A kernel that waits for a flag nobody sets gives up after its time limit, records a status code and leaves the
+    context usable (the host-visible form of a peer that never arrives)."""
+    import ctypes
+    import time
+
+    from bmtrain_b200.ops import _native
+
+    lib = _native.cuda_lib()
+    world = 2
+    flags = torch.zeros(8 * world, dtype=torch.int32, device=dev)           # one flag row per slot, never written
+    table = torch.tensor([flags.data_ptr()] * world, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    t0 = time.perf_counter()
+    _native.check(lib.bmt_symm_signal_wait(ctypes.c_void_p(table.data_ptr()), ctypes.c_int(world), ctypes.c_int(0), ctypes.c_int(3),
+                                           ctypes.c_uint(1), ctypes.c_int(0), ctypes.c_int(1), _native.ptr(status),
+                                           ctypes.c_double(0.2), _native.stream_handle()), "signal/wait kernel")
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 0.15 < waited < 5.0, waited
+    assert int(status.item()) == (0x200 | 0)
+    # a wait whose flag is there returns at once and does not touch the status word
+    flags[3 * world:4 * world] = 1
+    status.zero_()
+    _native.check(lib.bmt_symm_signal_wait(ctypes.c_void_p(table.data_ptr()), ctypes.c_int(world), ctypes.c_int(0), ctypes.c_int(3),
+                                           ctypes.c_uint(1), ctypes.c_int(0), ctypes.c_int(1), _native.ptr(status),
+                                           ctypes.c_double(0.2), _native.stream_handle()), "signal/wait kernel")
+    assert int(status.item()) == 0
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0  # the context still works
