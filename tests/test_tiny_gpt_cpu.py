@@ -84,3 +84,25 @@ def test_tiny_gpt_zero3(world):
 
 def test_tiny_gpt_zero2_nocheckpoint():
     run_distributed("test_tiny_gpt_cpu", "body_train", 2, steps=3, zero_level=2, use_checkpoint=False)
+
+
+def test_example_script_runs_on_cpu(tmp_path):
+    """The example training loop end to end on one CPU process (tiny model): inspect tables, timing line, checkpoint."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ckpt = tmp_path / "model.pt"
+    env = dict(os.environ, BMT_DEVICE="cpu", BMT_QUIET="1", MASTER_PORT="29873")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE"):
+        env.pop(k, None)
+    out = subprocess.run([sys.executable, os.path.join(root, "examples", "train_gpt.py"), "--layers", "2", "--dim", "64", "--heads", "4",
+                          "--ffn", "128", "--vocab", "256", "--seq", "32", "--iters", "3", "--inspect-every", "2", "--save", str(ckpt)],
+                         capture_output=True, text=True, env=env, timeout=240)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "| Iter:      2 |" in out.stdout and "transformers.1.ff.w_out.weight" in out.stdout
+    import torch
+
+    state = torch.load(ckpt, map_location="cpu")
+    assert state["transformers.0.attn.project_qkv.weight"].shape == (192, 64)
