@@ -150,6 +150,12 @@ def test_tp_fused_kernels_2gpu():
     run_distributed("test_multi_gpu", "body_tp_fused", 2, device="cuda")
 
 
+def test_tp_fused_kernels_4gpu():
+    """Groups of four: rows of three other ranks per kernel (tile rotation, early "delivered", push order)."""
+    _need(4)
+    run_distributed("test_multi_gpu", "body_tp_fused", 4, device="cuda")
+
+
 def body_tp_model_gpu():
     """bf16 GPT with tp_size=2 on 2 GPUs (column/row parallel layers on the fused kernels, vocab-parallel embedding and
     loss) against the fp32 single-process oracle: loss and gradient statistics."""
