@@ -60,16 +60,20 @@ def check_peer_status() -> None:
         if rt is None:
             continue
         slot = _status_host.get(key)
-        if slot is not None:
-            host, event = slot
-            if event.query() and int(host[0]) != 0:
-                _status_host.pop(key, None)
+        if slot is None:
+            # one pinned word per runtime, allocated once (pinning memory is far too slow to do per step)
+            slot = _status_host[key] = [torch.zeros(1, dtype=torch.int32).pin_memory(), None]
+        host, event = slot
+        if event is not None:
+            if not event.query():
+                continue  # the previous copy has not landed yet: look again next step
+            if int(host[0]) != 0:
+                slot[1] = None
                 rt.check()
-        host = torch.zeros(1, dtype=torch.int32).pin_memory()
         host.copy_(rt.status, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
-        _status_host[key] = (host, event)
+        slot[1] = event
 
 
 def grad_rescale(param_groups, scale) -> None:
