@@ -136,6 +136,26 @@ def reset_shape_cache() -> None:
     _shape_cache.clear()
 
 
+def send_meta(x: torch.Tensor, next_rank: int, comm: Communicator) -> None:
+    """Send the header of ``x`` (number of dimensions, dtype index, shape) to group rank ``next_rank``
+    (reference: ``bmtrain/distributed/ops.py:21-30``)."""
+    meta = torch.zeros(_META_LEN, dtype=torch.int64)
+    meta[0] = x.dim()
+    meta[1] = _DTYPES.index(x.dtype)
+    for i, s in enumerate(x.shape):
+        meta[2 + i] = s
+    comm.send(meta.to(x.device), next_rank).wait()
+
+
+def recv_meta(prev_rank: int, comm: Communicator):
+    """Receive a header sent by :func:`send_meta`; returns ``(dtype, shape)`` (reference: ``bmtrain/distributed/ops.py:32-45``).
+    Reading the header is a host sync; the pipeline avoids it after the first transfer by caching shapes."""
+    meta = torch.zeros(_META_LEN, dtype=torch.int64, device=config["device"])
+    comm.recv(meta, prev_rank).wait()
+    m = meta.tolist()
+    return _DTYPES[m[1]], list(m[2:2 + m[0]])
+
+
 def send_activations(hidden_state: torch.Tensor, next_rank: int, comm: Communicator, tag: str = "act", static: bool = False):
     """Send a tensor to group rank ``next_rank``.
 
@@ -146,12 +166,7 @@ def send_activations(hidden_state: torch.Tensor, next_rank: int, comm: Communica
     key = (id(comm), next_rank, "s" + tag)
     desc = (tuple(hidden_state.shape), hidden_state.dtype)
     if not static or _shape_cache.get(key) != desc:
-        meta = torch.zeros(_META_LEN, dtype=torch.int64)
-        meta[0] = hidden_state.dim()
-        meta[1] = _DTYPES.index(hidden_state.dtype)
-        for i, s in enumerate(hidden_state.shape):
-            meta[2 + i] = s
-        comm.send(meta.to(hidden_state.device), next_rank).wait()
+        send_meta(hidden_state, next_rank, comm)
         if static:
             _shape_cache[key] = desc
     work = comm.send(hidden_state, next_rank)
@@ -164,10 +179,8 @@ def recv_activations(prev_rank: int, comm: Communicator, tag: str = "act", stati
     key = (id(comm), prev_rank, "r" + tag)
     desc = _shape_cache.get(key) if static else None
     if desc is None:
-        meta = torch.zeros(_META_LEN, dtype=torch.int64, device=dev)
-        comm.recv(meta, prev_rank).wait()
-        m = meta.tolist()
-        desc = (tuple(m[2:2 + m[0]]), _DTYPES[m[1]])
+        dtype, shape = recv_meta(prev_rank, comm)
+        desc = (tuple(shape), dtype)
         if static:
             _shape_cache[key] = desc
     out = torch.empty(desc[0], dtype=desc[1], device=dev)

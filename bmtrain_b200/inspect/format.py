@@ -15,6 +15,21 @@ def _cell(value: Any, width: int) -> str:
     return text.ljust(width)
 
 
+def item_formater(x: Any) -> str:
+    """Cell text of one value: floats with four decimals, everything else through ``str``."""
+    return f"{x:.4f}" if isinstance(x, float) else str(x)
+
+
+def align_str(s: str, align: int, left: bool) -> str:
+    """Pad ``s`` with blanks to ``align`` characters on the right (``left``) or on the left."""
+    return s.ljust(align) if left else s.rjust(align)
+
+
+def format_line(strs: List[str], length: List[int]) -> str:
+    """One table row: every string gets a leading blank, is cut to its column and padded to the column width."""
+    return "".join(_cell(v, w) for v, w in zip(strs, length))
+
+
 def format_summary(summary: List[Dict[str, Any]]) -> str:
     """Render a list of summary dicts (from ``inspect_model`` / ``InspectTensor.get_summary``)."""
     name_width = max([len("name")] + [len(item["name"]) for item in summary]) + 4

@@ -28,6 +28,20 @@ def _stats(name: str, p: torch.Tensor, g) -> Dict:
     return out
 
 
+def _gather_value(value: torch.Tensor, partition_size: int, origin_size) -> torch.Tensor:
+    """Full tensor of shape ``origin_size`` from every rank's flat shard ``value`` (shards shorter than
+    ``partition_size`` are zero padded first; reference: ``bmtrain/inspect/model.py:10-33``)."""
+    comm = config["comm"]
+    shard = torch.zeros(partition_size, dtype=value.dtype, device=value.device)
+    shard[:value.numel()] = value.reshape(-1)
+    full = torch.empty(partition_size * comm.size, dtype=value.dtype, device=value.device)
+    comm.all_gather_into(full, shard)
+    numel = 1
+    for s in tuple(origin_size):
+        numel *= s
+    return full[:numel].view(tuple(origin_size))
+
+
 def inspect_block(model: Block, param_name: str, prefix: str = "") -> List[Dict]:
     if not any(fnmatch.fnmatch(prefix + s.name, param_name) for s in model._slots):
         return []

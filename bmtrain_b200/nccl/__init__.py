@@ -31,6 +31,24 @@ def _t(x) -> torch.Tensor:
     raise TypeError(f"expected a tensor or typed storage, got {type(x)}")
 
 
+def dtype2nccl(dtype: torch.dtype) -> int:
+    """NCCL's ``ncclDataType_t`` number of a torch dtype (reference: ``bmtrain/nccl/__init__.py:29-47``).  The numbers are
+    the public ones of ``nccl.h``; nothing in this package needs them, the process groups take torch dtypes."""
+    table = {torch.int8: 0, torch.uint8: 1, torch.int32: 2, torch.int64: 4, torch.float16: 6, torch.float32: 7,
+             torch.float64: 8, torch.bfloat16: 9}
+    if dtype not in table:
+        raise TypeError(f"Unsupport dtype {dtype}")
+    return table[dtype]
+
+
+def op2nccl(op: str) -> int:
+    """NCCL's ``ncclRedOp_t`` number of a reduction name (reference: ``bmtrain/nccl/__init__.py:49-59``)."""
+    table = {"sum": 0, "prod": 1, "max": 2, "min": 3, "avg": 4}
+    if op not in table:
+        raise ValueError(f"Unsupport op {op}")
+    return table[op]
+
+
 def getUniqueId() -> bytes:
     """An opaque id for a new communicator (random token; the rendezvous is torch.distributed's)."""
     return os.urandom(16)

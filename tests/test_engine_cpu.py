@@ -564,3 +564,38 @@ def test_misc_utils(bmt_cpu, capsys):
     assert bmt.world_size() == 1 and bmt.rank() == 0 and bmt.CheckpointBlock is bmt.Block
     groups = dict(bmt.grouped_parameters(bmt.nn.Linear(4, 4, dtype=torch.float32)))
     assert None in groups and len(groups[None]) == 2
+
+
+def test_reference_named_internals(bmt_cpu):
+    """Module paths and helper names of the reference that user code may import: ZeroContext gathers a block by hand,
+    the hook functions bracket a module, formatting / header / enum helpers give the reference's values."""
+    bmt = bmt_cpu
+    from bmtrain_b200.benchmark import all_gather, reduce_scatter, send_recv, shape, utils  # noqa: F401
+    from bmtrain_b200.hook_func import OneStepNoGradFunc, PostHookFunc, PreHookFunc  # noqa: F401
+    from bmtrain_b200.inspect.format import align_str, format_line, item_formater
+    from bmtrain_b200.inspect.model import _gather_value
+    from bmtrain_b200.nccl import dtype2nccl, op2nccl
+    from bmtrain_b200.zero_context import ZeroContext
+
+    assert shape.SHAPES[0] == 1024 and shape.SHAPES[-1] == 2 ** 32
+    assert utils.format_size_(512) == "512B" and utils.format_size_(3 * 1024 * 1024) == "3.00MB" and len(utils.format_size(10 ** 10)) <= 6
+    assert align_str("ab", 4, True) == "ab  " and align_str("ab", 4, False) == "  ab"
+    assert format_line(["name", "toolongvalue"], [6, 5]) == " name  tool" and item_formater(0.5) == "0.5000" and item_formater(3) == "3"
+    assert dtype2nccl(torch.float16) == 6 and dtype2nccl(torch.bfloat16) == 9 and op2nccl("max") == 2
+    full = _gather_value(torch.arange(5.0), 6, (5,))
+    assert torch.equal(full, torch.arange(5.0))
+
+    lin = bmt.nn.Linear(6, 4)
+    bmt.init_parameters(lin)
+    blk = bmt.Block(lin)
+    x = torch.randn(3, 6)
+    want = blk(x)
+    with ZeroContext(blk):
+        assert blk._module.weight.shape == (4, 6)
+        got = blk._module(x)
+    assert torch.allclose(got, want)
+    # bracketing by hand with the identity functions gathers / releases around the inner module as well
+    (xin,) = PreHookFunc.apply(blk, x.clone().requires_grad_())
+    out = blk._module(xin)
+    (out,) = PostHookFunc.apply(blk, out)
+    assert torch.allclose(out, want)
