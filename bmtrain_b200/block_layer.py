@@ -43,6 +43,15 @@ _callback_queued = False
 _extra_drains: List = []  # other subsystems (pipeline sends) register completion hooks here
 
 
+# Bumped whenever parameter values change (optimizer step, checkpoint load): a gathered copy made before that -- e.g. a
+# prefetch for a block that was then never run -- must not be used afterwards.
+_param_epoch = [0]
+
+
+def params_changed() -> None:
+    _param_epoch[0] += 1
+
+
 def drain_pending() -> None:
     """Complete every outstanding gradient reduce-scatter (stream-level wait, no host block on NCCL)."""
     global _callback_queued
@@ -64,11 +73,6 @@ def _queue_backward_callback() -> None:
     except RuntimeError:
         # not inside a backward pass (e.g. torch.autograd.grad from a test): finish now
         drain_pending()
-
-
-def storage_type_cuda(storage_type):  # pragma: no cover - kept for API parity
-    """Legacy helper of the reference (typed storages): the type itself is returned."""
-    return storage_type
 
 
 def _get_param_kw(param: DistributedParameter) -> str:
@@ -355,6 +359,7 @@ class Block(torch.nn.Module):
     def _load_param(self, param: DistributedParameter, value: torch.Tensor) -> None:
         """Write the local part of ``value`` (full tensor of one inner parameter) into the partition."""
         b, s = self._slot_of[id(param)]
+        params_changed()
         if s.hi > s.lo:
             flat = value.reshape(-1)
             b.storage.data[s.lo - b.begin:s.hi - b.begin].copy_(flat[s.lo - s.offset:s.hi - s.offset])
@@ -363,9 +368,12 @@ class Block(torch.nn.Module):
     def _begin_gather(self) -> None:
         """Start the all-gather of every bucket (no-op when resident or already in flight)."""
         for b in self._buckets.values():
-            if b.full is not None:
+            if b.full is not None and getattr(b, "full_epoch", -1) == _param_epoch[0]:
                 continue
+            if b.full is not None and b.work is not None:
+                b.work.wait()  # a stale prefetch: let it finish before its buffer is dropped
             b.full = torch.empty(b.total, dtype=b.dtype, device=b.storage.device)
+            b.full_epoch = _param_epoch[0]
             b.work = b.comm.all_gather_into(b.full, b.storage.data, async_op=True)
 
     def _try_deferred_gather(self, args, backward: bool = False) -> bool:
@@ -439,6 +447,7 @@ class Block(torch.nn.Module):
             return state["ev_rest"]
 
         b.full = buf.tensor(b.dtype, b.total)
+        b.full_epoch = _param_epoch[0]
         b.full_sym = (rt, free_row, epoch)
         mod._bmt_deferred_gather = dict(rt=rt, buf=buf, bucket=b, slot=slot, epoch=epoch, key=key, free_row=free_row,
                                         ev_small=ev_small, push_rest=push_rest)
@@ -486,7 +495,10 @@ class Block(torch.nn.Module):
         return symm.peer_runtime(b.comm)
 
     def _grad_slot_key(self, b: _Bucket):
-        return ("grad", self._slot_parity, b.key, b.total)
+        # Blocks of a plain list alternate between two staging slots (a slot is free again once the reduce-scatter of the
+        # block after next has been waited for).  Inside a pipeline stage every block keeps its full gradients alive
+        # across all micro-batches, so each block needs a slot of its own.
+        return ("grad", self._slot_parity, b.key, b.total, id(self) if self._mode == "PIPE" else 0)
 
     def _prepare_grads(self) -> None:
         """Full-size zeroed gradient buffers; inner ``.grad`` fields become views into them."""
@@ -810,20 +822,22 @@ class _WeakOwner:
 
 
 def _block_wrapper(module, module_dict: dict, mode: str = "BLOCK") -> Block:
-    if not isinstance(module, Block):
-        if id(module) in module_dict:
-            new_module = Block(module, initialized=True, mode=mode, _share=module_dict[id(module)])
-        else:
-            new_module = Block(module, mode=mode)
-            module_dict[id(module)] = new_module
-    else:
+    """Entry of a block list as a :class:`Block`.  ``module_dict`` maps ``id(inner module)`` to the block that already
+    owns it: a raw module listed twice becomes a weight-tied block sharing the first one's storage, while the same
+    ``Block`` object (or two blocks around one module) in a list is an error."""
+    if isinstance(module, Block):
+        inner = module._module
         if mode == "PIPE" and module._mode != "PIPE":
-            raise AssertionError('You must be set mode="PIPE" in bmt.Block when use PipelineTransformerBlockList!')
-        if id(module._module) in module_dict:
-            raise AssertionError("Duplicate bmt.Block not supported in same block list!")
-        new_module = module
-        module_dict[id(module._module)] = new_module
-    return new_module
+            raise AssertionError('a Block inside a PipelineTransformerBlockList must be created with mode="PIPE"')
+        if id(inner) in module_dict:
+            raise AssertionError("the same bmt.Block appears twice in one block list")
+        module_dict[id(inner)] = module
+        return module
+    owner = module_dict.get(id(module))
+    if owner is not None:
+        return Block(module, initialized=True, mode=mode, _share=owner)
+    module_dict[id(module)] = block = Block(module, mode=mode)
+    return block
 
 
 class TransformerBlockList(torch.nn.Module):
@@ -831,29 +845,25 @@ class TransformerBlockList(torch.nn.Module):
 
     The first ``num_hidden`` outputs of each block replace the first
     ``num_hidden`` inputs of the next one; the remaining arguments are passed
-    to every block unchanged.  Calling the list (instead of looping over it)
-    lets it prefetch the next block's parameters during the current block and
-    overlap each block's gradient reduction with the backward pass of the
-    blocks before it.
+    to every block unchanged.  Neighbouring blocks are linked, so each block
+    starts the gather of the block that runs after it (the next one in
+    forward, the previous one in backward) before it computes, and a block's
+    gradient reduction runs under the backward pass of the blocks before it.
+    Contract: reference ``bmtrain/block_layer.py:651-726``.
     """
 
     _modules: Dict[str, Block]
 
     def __init__(self, modules: Iterable[Block], num_hidden: int = 1) -> None:
         super().__init__()
-        modules = list(modules)
-        pre_module = None
-        module_dict: dict = {}
-        for i, module in enumerate(modules):
-            module = _block_wrapper(module, module_dict)
-            module.set_pre_module(pre_module)
-            pre_module = module
-            module._is_first_layer = False
-            module._is_last_layer = False
-            module._slot_parity = i % 2  # neighbouring blocks alternate between two peer-visible gradient staging slots
-            self.add_module(str(i), module)
-        self._modules[str(0)]._is_first_layer = True
-        self._modules[str(len(modules) - 1)]._is_last_layer = True
+        owners: dict = {}
+        chain: List[Block] = [_block_wrapper(m, owners) for m in modules]
+        for i, block in enumerate(chain):
+            block.set_pre_module(chain[i - 1] if i else None)
+            block._is_first_layer = i == 0
+            block._is_last_layer = i == len(chain) - 1
+            block._slot_parity = i % 2  # neighbouring blocks alternate between two peer-visible gradient staging slots
+            self.add_module(str(i), block)
         self.num_hidden = num_hidden
 
     def __len__(self) -> int:
@@ -863,20 +873,24 @@ class TransformerBlockList(torch.nn.Module):
         return iter(self._modules.values())
 
     def __getitem__(self, index: Union[int, str]) -> Block:
+        if isinstance(index, int) and index < 0:
+            index += len(self)
         return self._modules[str(index)]
 
     def forward(self, *args, return_hidden_states: bool = False):
         self.return_hidden_states = return_hidden_states
-        hidden_states = []
-        outputs: Tuple = ()
-        for i in range(len(self)):
+        k = self.num_hidden
+        carried, shared = tuple(args[:k]), tuple(args[k:])
+        seen: List[List[torch.Tensor]] = [[] for _ in range(k)]  # inputs of every block, per carried position
+        produced: Tuple = ()
+        for block in self._modules.values():
             if return_hidden_states:
-                hidden_states.extend(args[: self.num_hidden])
-            outputs = self._modules[str(i)](*args)
-            if not isinstance(outputs, tuple):
-                outputs = (outputs,)
-            args = outputs + args[self.num_hidden:]
+                for trail, value in zip(seen, carried):
+                    trail.append(value)
+            produced = block(*carried, *shared)
+            if not isinstance(produced, tuple):
+                produced = (produced,)
+            carried = produced[:k]
         if return_hidden_states:
-            stacked = [torch.stack(hidden_states[i:: self.num_hidden], dim=0) for i in range(self.num_hidden)]
-            return outputs + tuple(stacked)
-        return tuple(outputs[: self.num_hidden]) if self.num_hidden > 1 else outputs[0]
+            return produced + tuple(torch.stack(trail, dim=0) for trail in seen)
+        return produced[0] if k == 1 else tuple(produced[:k])

@@ -3,8 +3,7 @@
 import torch
 
 from ..global_var import config
-from ..layer import DistributedModule
-from ..parameter import DistributedParameter
+from ._tp_linear import ShardedLinearBase
 from .parallel_linear_func import OpParallelLinear, ReduceType
 
 
@@ -26,7 +25,7 @@ class _AddReplicatedBias(torch.autograd.Function):
         return grad, gb
 
 
-class RowParallelLinear(DistributedModule):
+class RowParallelLinear(ShardedLinearBase):
     """``y = reduce(x_r W_r^T) + b`` with ``W_r`` = columns ``[r*in/tp, (r+1)*in/tp)`` of the full weight.
 
     By default the partial products are reduce-scattered over the token dim
@@ -37,36 +36,16 @@ class RowParallelLinear(DistributedModule):
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, dtype=None,
                  split_input=False, all_reduce_output=False, async_chunks=2):
-        super().__init__()
-        self.in_features = in_features
-        self.out_features = out_features
-        self.split_input = split_input
-        self.all_reduce_output = all_reduce_output
-        self.async_chunks = async_chunks
-        tp_size = config["tp_size"]
-        assert in_features % tp_size == 0
-        self.in_features_per_partition = in_features // tp_size
-        self.weight = DistributedParameter(
-            torch.empty(out_features, self.in_features_per_partition, dtype=dtype, device="meta"),
-            init_method=torch.nn.init.xavier_normal_, tp_split_dim=1, tp_mode=True)
-        if bias:
-            self.bias = DistributedParameter(torch.empty(out_features, dtype=dtype, device="meta"),
-                                             init_method=torch.nn.init.zeros_, tp_split_dim=-1, tp_mode=True)
-        else:
-            self.register_parameter("bias", None)
+        super().__init__(in_features, out_features, bias, dtype, split_dim=1)
+        self.in_features_per_partition = in_features // config["tp_size"]
+        self.split_input, self.all_reduce_output, self.async_chunks = split_input, all_reduce_output, async_chunks
 
     def forward(self, input):
-        gather_input = self.split_input
         reduce_type = ReduceType.ALL_REDUCE.value if self.all_reduce_output else ReduceType.REDUCE_SCATTER.value
-        out = OpParallelLinear.apply(input, self.weight, None, gather_input, False, self.split_input,
+        out = OpParallelLinear.apply(input, self.weight, None, self.split_input, False, self.split_input,
                                      reduce_type, self.async_chunks)
-        if self.bias is not None:
-            if config["tp_size"] > 1 and not self.all_reduce_output:
-                out = _AddReplicatedBias.apply(out, self.bias)
-            else:
-                out = out + self.bias
-        return out
-
-    def extra_repr(self) -> str:
-        return (f"in_features={self.in_features_per_partition}, out_features={self.out_features}, "
-                f"bias={self.bias is not None}")
+        if self.bias is None:
+            return out
+        if config["tp_size"] > 1 and not self.all_reduce_output:
+            return _AddReplicatedBias.apply(out, self.bias)
+        return out + self.bias

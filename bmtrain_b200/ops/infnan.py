@@ -95,6 +95,10 @@ def multi_scale(tensors: Sequence[torch.Tensor], coef: torch.Tensor) -> None:
     lib = _native.cuda_lib()
     by_dtype = {}
     for t in tensors:
+        if t.dtype not in _DT or not t.is_contiguous():
+            # the kernel walks flat memory of the three training dtypes; anything else is scaled by torch
+            t.mul_(torch.clamp(coef.float(), max=1.0).to(t.dtype))
+            continue
         by_dtype.setdefault(t.dtype, []).append(t)
     for dtype, group in by_dtype.items():
         for i in range(0, len(group), _MAX):

@@ -244,6 +244,9 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
     # ------------------------------------------------------------------- step
     @torch.no_grad()
     def step(self, closure=None, scale=1):
+        from ..block_layer import params_changed
+
+        params_changed()
         loss = None
         if closure is not None:
             with torch.enable_grad():

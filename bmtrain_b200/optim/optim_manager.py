@@ -14,15 +14,15 @@ from typing import Optional
 
 import torch
 
-from ..block_layer import drain_pending
+from ..block_layer import drain_pending, params_changed
 from ..global_var import config
 from ..lr_scheduler.warmup import WarmupLRScheduler
 from ..ops import infnan
 from ..utils import print_rank
 
 
-def check_overflow(param_groups) -> None:
-    """Raise ``OverflowError`` if any half-precision gradient (on any rank) holds inf or nan."""
+def found_overflow(param_groups) -> bool:
+    """True when any half-precision gradient of ``param_groups``, on any rank, holds inf or nan (one host read)."""
     dev = config["device"]
     flag = torch.zeros(1, dtype=torch.uint8, device=dev)
     grads = [p.grad for group in param_groups for p in group["params"]
@@ -40,7 +40,12 @@ def check_overflow(param_groups) -> None:
         f32 = flag.to(torch.int32)
         config["comm"].all_reduce(f32, "max")
         flag = f32
-    if int(flag.item()) > 0:
+    return int(flag.item()) > 0
+
+
+def check_overflow(param_groups) -> None:
+    """Reference-compatible form (``bmtrain/optim/optim_manager.py:9-21``): raises ``OverflowError`` on inf/nan."""
+    if found_overflow(param_groups):
         raise OverflowError("Gradient overflow")
 
 
@@ -83,27 +88,64 @@ def grad_rescale(param_groups, scale) -> None:
                 p.grad /= scale
 
 
+class LossScaler:
+    """Dynamic loss scale: ``scale`` shrinks by ``factor`` after a step with inf/nan gradients (never below ``floor``)
+    and grows by ``factor`` after ``interval`` clean steps in a row (never above ``ceiling``).  ``on_change(old, new)``
+    is called before every change so that state kept in scaled units can follow."""
+
+    def __init__(self, scale, factor, interval, floor, ceiling, on_change):
+        self.enabled = scale is not None
+        self.scale = scale if self.enabled else 1
+        self.factor = factor if factor > 1 else 1 / factor
+        self.interval, self.floor, self.ceiling = interval, floor, ceiling
+        self.clean_steps = 0
+        self._on_change = on_change
+
+    def set(self, value) -> None:
+        self._on_change(self.scale, value)
+        self.scale = value
+        self.clean_steps = 0
+
+    def overflowed(self) -> None:
+        if self.scale > self.floor:
+            self.set(self.scale / self.factor)
+
+    def stepped(self) -> None:
+        self.clean_steps += 1
+        if self.clean_steps >= self.interval and self.scale < self.ceiling:
+            self.set(self.scale * self.factor)
+
+
 class OptimManager:
     """Drives several optimizers (+ schedulers) under one dynamic loss scale."""
 
     def __init__(self, loss_scale: Optional[float] = None, loss_scale_factor: float = 2, loss_scale_steps: int = 1024,
                  min_loss_scale=1, max_loss_scale=float("inf"), grad_scale: Optional[int] = None):
-        if loss_scale is not None:
-            self.loss_scale = loss_scale
-            self.loss_scale_enabled = True
-        else:
-            self.loss_scale = 1
-            self.loss_scale_enabled = False
-        self.steps_since_last_scale = 0
-        self.loss_scale_factor = loss_scale_factor if loss_scale_factor > 1 else 1 / loss_scale_factor
-        self.loss_scale_steps = loss_scale_steps
-        self.min_loss_scale = min_loss_scale
-        self.max_loss_scale = max_loss_scale
-        if grad_scale is None:
-            grad_scale = config["zero_size"]
-        self.grad_scale = grad_scale
         self.optimizers = []
         self.lr_schedulers = []
+        self._scaler = LossScaler(loss_scale, loss_scale_factor, loss_scale_steps, min_loss_scale, max_loss_scale,
+                                  self._rescale_optimizer_state)
+        self.grad_scale = config["zero_size"] if grad_scale is None else grad_scale
+
+    # the scaler's fields under the names the reference exposes (read and written by user code and checkpoints)
+    loss_scale = property(lambda self: self._scaler.scale, lambda self, v: setattr(self._scaler, "scale", v))
+    loss_scale_enabled = property(lambda self: self._scaler.enabled, lambda self, v: setattr(self._scaler, "enabled", v))
+    steps_since_last_scale = property(lambda self: self._scaler.clean_steps,
+                                      lambda self, v: setattr(self._scaler, "clean_steps", v))
+    loss_scale_factor = property(lambda self: self._scaler.factor)
+    loss_scale_steps = property(lambda self: self._scaler.interval)
+    min_loss_scale = property(lambda self: self._scaler.floor)
+    max_loss_scale = property(lambda self: self._scaler.ceiling)
+
+    def _rescale_optimizer_state(self, old, new) -> None:
+        with torch.no_grad():
+            for optimizer in self.optimizers:
+                hook = getattr(optimizer, "_on_justify_scale", None)
+                if hook is not None:
+                    hook(old, new)
+
+    def _justify_scale(self, scale) -> None:
+        self._scaler.set(scale)
 
     def add_optimizer(self, optimizer: torch.optim.Optimizer, lr_scheduler: Optional[WarmupLRScheduler] = None):
         self.optimizers.append(optimizer)
@@ -114,8 +156,7 @@ class OptimManager:
 
     def backward(self, loss: torch.Tensor):
         """Backward of the scaled loss; returns once all gradient reductions are queued behind it."""
-        loss = self.scale_loss(loss)
-        loss.backward()
+        self.scale_loss(loss).backward()
         drain_pending()
 
     def zero_grad(self):
@@ -125,35 +166,26 @@ class OptimManager:
     def step(self):
         drain_pending()
         check_peer_status()
-        if self.loss_scale_enabled:
-            has_overflow = False
-            for optimizer in self.optimizers:
-                try:
-                    check_overflow(optimizer.param_groups)
-                except OverflowError:
-                    has_overflow = True
-                    break
-            if has_overflow:
-                print_rank("Gradient overflow, change scale from %lf to %lf"
-                           % (self.loss_scale, self.loss_scale / self.loss_scale_factor))
-                with torch.no_grad():
-                    if self.loss_scale > self.min_loss_scale:
-                        self._justify_scale(self.loss_scale / self.loss_scale_factor)
-                    self.zero_grad()
-                return
+        scaler = self._scaler
+        if scaler.enabled and any(found_overflow(opt.param_groups) for opt in self.optimizers):
+            shrunk = scaler.scale / scaler.factor if scaler.scale > scaler.floor else scaler.scale
+            print_rank("Gradient overflow, change scale from %lf to %lf" % (scaler.scale, shrunk))
+            scaler.overflowed()
+            with torch.no_grad():
+                self.zero_grad()
+            return  # nothing is stepped, schedulers do not advance
+        params_changed()
         for optimizer, lr_scheduler in zip(self.optimizers, self.lr_schedulers):
             if getattr(optimizer, "_bmtrain_optimizer", False):
-                optimizer.step(scale=self.loss_scale)
+                optimizer.step(scale=scaler.scale)
             else:
-                if self.loss_scale_enabled:
-                    grad_rescale(optimizer.param_groups, self.loss_scale)
+                if scaler.enabled:
+                    grad_rescale(optimizer.param_groups, scaler.scale)
                 optimizer.step()
             if lr_scheduler is not None:
                 lr_scheduler.step()
-        if self.loss_scale_enabled:
-            self.steps_since_last_scale += 1
-            if self.steps_since_last_scale >= self.loss_scale_steps and self.loss_scale < self.max_loss_scale:
-                self._justify_scale(self.loss_scale * self.loss_scale_factor)
+        if scaler.enabled:
+            scaler.stepped()
 
     def clip_grad_norm(self, param_groups, max_norm, norm_type=2, eps=1e-6):
         """Clip the global gradient norm (computed on the still loss-scaled gradients); returns the unscaled norm."""
@@ -185,14 +217,6 @@ class OptimManager:
             if hasattr(optimizer, "_invalidate_staged"):
                 optimizer._invalidate_staged()
         return total_norm / scale
-
-    @torch.no_grad()
-    def _justify_scale(self, scale):
-        for optimizer in self.optimizers:
-            if hasattr(optimizer, "_on_justify_scale"):
-                optimizer._on_justify_scale(self.loss_scale, scale)
-        self.loss_scale = scale
-        self.steps_since_last_scale = 0
 
     def state_dict(self, gather_opt: bool = False) -> dict:
         def opt_state(opt):

@@ -31,8 +31,6 @@ def _comm_ctas(flops: float, push_bytes: float, remote_bytes: float) -> int:
     lib = _native.cuda_lib()
     return int(lib.bmt_fused_comm_ctas(ctypes.c_double(flops), ctypes.c_double(push_bytes), ctypes.c_double(remote_bytes)))
 calls = {"gemm_rs": 0, "ag_gemm": 0, "zero_gather_gemm": 0}  # how often each fused kernel ran (tests and benchmarks read this)
-_ring: Dict[Tuple, int] = {}
-_counters: Dict[Tuple, torch.Tensor] = {}
 
 
 class _GemmDesc(ctypes.Structure):
@@ -60,13 +58,28 @@ def kernel_stats() -> dict:
             "rs_wait_us_max": out[5] / 1e3, "rs_total_us_max": out[6] / 1e3, "rs_wait_us_sum": out[7] / 1e3}
 
 
-def _next_parity(key: Tuple) -> int:
-    _ring[key] = (_ring.get(key, -1) + 1) % 2
-    return _ring[key]
+def _next_parity(rt, key: Tuple) -> int:
+    # ring positions and grid counters belong to the runtime: they start over together with its epochs when the
+    # process group is torn down and set up again, and two communicators never share them
+    ring = rt.cache.setdefault(("ring",), {})
+    ring[key] = (ring.get(key, -1) + 1) % 2
+    return ring[key]
 
 
-def _tma_ok(t: torch.Tensor) -> bool:
-    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+def _grid_counter(rt, key: Tuple, device) -> torch.Tensor:
+    table = rt.cache.setdefault(("grid_counters",), {})
+    if key not in table:
+        table[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return table[key]
+
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """``t`` in a layout the TMA descriptors accept (row-major, 16-byte aligned rows).  Whether the fused kernel is
+    used must not depend on a rank-local property such as a pointer or a stride -- a rank that fell back alone would
+    leave its peers waiting -- so a non-conforming operand is copied instead of being a reason to fall back."""
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous().clone() if t.is_contiguous() else t.contiguous()
 
 
 def gemm_rs(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], comm: Communicator, b_is_kn: bool) -> Optional[torch.Tensor]:
@@ -75,19 +88,19 @@ def gemm_rs(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
     M, K = x.shape
     N = weight.shape[1] if b_is_kn else weight.shape[0]
     W = comm.size
-    if rt is None or x.dtype not in _DT or M % W or N % 8 or K % 8 or not _tma_ok(x) or not _tma_ok(weight):
+    if rt is None or x.dtype not in _DT or M % W or N % 8 or K % 8:
         return None
+    x, weight = _tma_ready(x), _tma_ready(weight)
     lib = _native.cuda_lib()
     rows = M // W
     es = x.element_size()
     base = ("rs", M, N, K, x.dtype, b_is_kn)
-    key = base + (_next_parity(base),)
+    key = base + (_next_parity(rt, base),)
     inbox = rt.slot(key, W * rows * N * es)
     free_row, done_row = rt.row(key + ("free",)), rt.row(key + ("done",))
     epoch = rt.next_epoch(free_row)
     rt.epochs[done_row] = epoch
-    if key not in _counters:
-        _counters[key] = torch.zeros(2, dtype=torch.int32, device=x.device)
+    grid_counter = _grid_counter(rt, key, x.device)
     out = torch.empty(rows, N, dtype=x.dtype, device=x.device)
     d = _GemmDesc()
     d.m, d.n, d.k = M, N, K
@@ -97,7 +110,7 @@ def gemm_rs(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
     slots = (ctypes.c_void_p * W)(*[p + comm.rank * rows * N * es for p in inbox.ptrs])
     _native.check(lib.bmt_gemm_reduce_scatter(
         ctypes.byref(d), ctypes.c_int(W), ctypes.c_int(comm.rank), rt.flag_ptrs, ctypes.c_int(free_row), ctypes.c_int(done_row),
-        ctypes.c_uint(epoch), slots, ctypes.c_void_p(inbox.local_ptr), ctypes.c_int64(rows), _native.ptr(_counters[key]),
+        ctypes.c_uint(epoch), slots, ctypes.c_void_p(inbox.local_ptr), ctypes.c_int64(rows), _native.ptr(grid_counter),
         _native.ptr(out), _native.ptr(bias), _native.ptr(rt.status), ctypes.c_double(rt.timeout_s), _native.stream_handle()),
         "fused GEMM -> reduce-scatter kernel")
     calls["gemm_rs"] += 1
@@ -111,8 +124,9 @@ def ag_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     m, K = x_local.shape
     N = weight.shape[1] if b_is_kn else weight.shape[0]
     W = comm.size
-    if rt is None or x_local.dtype not in _DT or m % 128 or K % 8 or N % 8 or not _tma_ok(weight):
+    if rt is None or x_local.dtype not in _DT or m % 128 or K % 8 or N % 8:
         return None
+    weight = _tma_ready(weight)
     if not x_local.is_contiguous() or x_local.data_ptr() % 16:
         x_local = x_local.contiguous()  # the pushers copy flat 32 KiB pieces
     lib = _native.cuda_lib()
@@ -120,7 +134,7 @@ def ag_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     # everything that decides how the pushers cut the rows (pusher count, runs per block) has to be constant per key: the
     # per-block counters on the peers grow by the same amount every time the key's buffers are used
     base = ("ag", m, K, N, x_local.dtype, b_is_kn)
-    key = base + (_next_parity(base),)
+    key = base + (_next_parity(rt, base),)
     gathered = rt.slot(key, W * m * K * es)
     counters = rt.slot(key + ("cnt",), max(256, W * (m // 128) * 4))
     free_row = rt.row(key + ("free",))

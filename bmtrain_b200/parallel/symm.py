@@ -42,25 +42,43 @@ class SymmetricBuffer:
     def __init__(self, comm: Communicator, nbytes: int):
         lib = _native.cuda_lib()
         self.comm, self.nbytes = comm, int(nbytes)
-        local = ctypes.c_void_p()
-        _native.check(lib.bmt_symm_alloc(ctypes.c_int64(self.nbytes), ctypes.byref(local)), "symmetric allocation")
-        self.local_ptr = local.value
-        handle = (ctypes.c_ubyte * lib.bmt_ipc_handle_size())()
-        _native.check(lib.bmt_ipc_get_handle(ctypes.c_void_p(self.local_ptr), handle), "IPC handle export")
-        gathered: List = [None] * comm.size
-        dist.all_gather_object(gathered, bytes(handle), group=comm.group)
+        self.local_ptr = 0
         self.ptrs: List[int] = []
         self._opened: List[int] = []
+        # Every step that can fail on one rank alone (allocation, export, import) is followed by an agreement before the
+        # next collective, so that a failing rank never leaves the others blocked inside a collective it will not join.
+        local = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * lib.bmt_ipc_handle_size())()
+        ok = lib.bmt_symm_alloc(ctypes.c_int64(self.nbytes), ctypes.byref(local)) == 0
+        if ok:
+            self.local_ptr = local.value
+            ok = lib.bmt_ipc_get_handle(ctypes.c_void_p(self.local_ptr), handle) == 0
+        if not self._all_ok(ok):
+            self.close()
+            raise RuntimeError(f"symmetric allocation of {self.nbytes} bytes failed on a rank of communicator {comm.name}")
+        gathered: List = [None] * comm.size
+        dist.all_gather_object(gathered, bytes(handle), group=comm.group)
+        ok = True
         for j, raw in enumerate(gathered):
             if j == comm.rank:
                 self.ptrs.append(self.local_ptr)
                 continue
             buf = (ctypes.c_ubyte * len(raw)).from_buffer_copy(raw)
             out = ctypes.c_void_p()
-            _native.check(lib.bmt_ipc_open_handle(buf, ctypes.byref(out)), "IPC handle import")
+            if lib.bmt_ipc_open_handle(buf, ctypes.byref(out)) != 0:
+                ok = False
+                break
             self.ptrs.append(out.value)
             self._opened.append(out.value)
+        if not self._all_ok(ok):
+            self.close()
+            raise RuntimeError(f"mapping a peer's buffer failed on a rank of communicator {comm.name}")
         self._bytes = torch.as_tensor(_CudaArray(self.local_ptr, self.nbytes, self), device=config["device"])
+
+    def _all_ok(self, ok: bool) -> bool:
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=config["device"])
+        self.comm.all_reduce(flag, "min")
+        return int(flag.item()) == 1
 
     def tensor(self, dtype: torch.dtype, numel: int, byte_offset: int = 0) -> torch.Tensor:
         """A tensor that aliases the local buffer."""
@@ -202,12 +220,7 @@ def peer_runtime(comm: Communicator) -> Optional[PeerRuntime]:
     if ok:
         try:
             rt = PeerRuntime(comm)
-            good = 1
-        except Exception:  # IPC / peer mapping not available: every rank has to agree to fall back
-            good = 0
-        flag = torch.tensor([good], dtype=torch.int32, device=config["device"])
-        comm.all_reduce(flag, "min")
-        if int(flag.item()) == 0:
+        except RuntimeError:  # IPC / peer mapping not available; the buffer constructor made every rank raise together
             rt = None
     _runtimes[key] = rt
     return rt

@@ -3,7 +3,7 @@
 These are the tensor-parallel hot pairs of ``ColumnParallelLinear`` /
 ``RowParallelLinear`` (reference: chunked NCCL + cuBLAS overlap in
 ``bmtrain/nn/parallel_linear_func.py:26-105``).  On NVLink-connected B200s
-each pair is one kernel working on peer memory (``csrc/fused_tp.cu``); on other
+each pair is one kernel working on peer memory (``csrc/gemm_sm100.cu``, fused modes 1 and 2); on other
 setups (CPU ranks, or peer access unavailable) the collective and the GEMM run
 back to back.
 """

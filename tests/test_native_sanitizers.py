@@ -1,5 +1,5 @@
 """Host-side native code (thread pool + AVX Adam, shared-memory collectives) under AddressSanitizer + UBSan and under
-ThreadSanitizer.  The device code cannot be run under compute-sanitizer on this pool; the C++ runtime around it can be
+ThreadSanitizer.  The device code cannot be run under compute-sanitizer here; the C++ runtime around it can be
 checked on the CPU, which is what this does: ``tests/native/sanitize_driver.cpp`` is compiled together with the library
 sources and has to finish without a sanitizer report."""
 import os
