@@ -52,6 +52,14 @@ def params_changed() -> None:
     _param_epoch[0] += 1
 
 
+def update_ready(param, block: bool = True) -> bool:
+    """An optimizer that applies its step asynchronously marks the parameters it is still rewriting
+    (``_bmt_pending_update``).  ``block`` true: wait until the new values are in place (the current stream is made to wait
+    for their upload); false: only tell whether they are."""
+    hook = getattr(param, "_bmt_pending_update", None)
+    return True if hook is None else hook(block)
+
+
 def drain_pending() -> None:
     """Complete every outstanding gradient reduce-scatter (stream-level wait, no host block on NCCL)."""
     global _callback_queued
@@ -365,10 +373,16 @@ class Block(torch.nn.Module):
             b.storage.data[s.lo - b.begin:s.hi - b.begin].copy_(flat[s.lo - s.offset:s.hi - s.offset])
 
     # ------------------------------------------------------ gather / release
-    def _begin_gather(self) -> None:
-        """Start the all-gather of every bucket (no-op when resident or already in flight)."""
+    def _begin_gather(self, prefetch: bool = False) -> None:
+        """Start the all-gather of every bucket (no-op when resident or already in flight).  ``prefetch``: called on behalf
+        of a neighbouring block; a bucket whose optimizer update has not landed yet is then left for later instead of
+        making the caller wait."""
         for b in self._buckets.values():
             if b.full is not None and getattr(b, "full_epoch", -1) == _param_epoch[0]:
+                continue
+            # the optimizer may hold the flat partition or the parameters that are views of it
+            holders = [b.storage] + [s.param for s in b.slots]
+            if not all([update_ready(h, block=not prefetch) for h in holders]):
                 continue
             if b.full is not None and b.work is not None:
                 b.work.wait()  # a stale prefetch: let it finish before its buffer is dropped
@@ -455,6 +469,10 @@ class Block(torch.nn.Module):
 
     def _ensure_gathered(self, args=None, backward: bool = False) -> None:
         if args is not None:
+            for b in self._buckets.values():
+                if b.full is None:
+                    for h in [b.storage] + [s.param for s in b.slots]:
+                        update_ready(h)
             self._try_deferred_gather(args, backward)
         self._begin_gather()
         for b in self._buckets.values():
@@ -584,7 +602,7 @@ class Block(torch.nn.Module):
         self._ensure_gathered(args)
         nxt = self.next_module()
         if nxt is not None and nxt._mode != "PIPE":
-            nxt._begin_gather()
+            nxt._begin_gather(prefetch=True)
 
     def _exit_forward(self) -> None:
         if self._mode == "PIPE" and self._micro_idx != config["micros"] - 1:
@@ -601,7 +619,7 @@ class Block(torch.nn.Module):
         self._prepare_grads()
         pre = self.pre_module()
         if pre is not None and pre._mode != "PIPE" and pre._zero_level == 3:
-            pre._begin_gather()
+            pre._begin_gather(prefetch=True)
 
     def _exit_backward(self) -> None:
         if self._mode == "PIPE":

@@ -55,6 +55,21 @@ class _Chain:
 
 DONE = _Done()
 
+# Measurement aid: while set, all-gather and reduce-scatter only move this rank's own piece (no traffic between ranks).
+# A training step timed this way against the same step with real collectives gives the communication time that
+# computation does not hide.  Values are wrong in this mode; it is for timing only (see `local_collectives`).
+_LOCAL_ONLY = [False]
+
+
+class local_collectives:
+    """``with local_collectives(): ...`` -- run a region with rank-local stand-ins for all-gather / reduce-scatter."""
+
+    def __enter__(self):
+        self._old, _LOCAL_ONLY[0] = _LOCAL_ONLY[0], True
+
+    def __exit__(self, *exc):
+        _LOCAL_ONLY[0] = self._old
+
 
 class Communicator:
     """A group of ranks that communicate with each other.
@@ -112,6 +127,9 @@ class Communicator:
         if self.size == 1:
             out.view(-1).copy_(inp.reshape(-1))
             return DONE
+        if _LOCAL_ONLY[0]:
+            out.view(self.size, -1)[self.rank].copy_(inp.reshape(-1))
+            return DONE
         inp = inp.contiguous()
         shm = self._shm_for(inp)
         if shm is not None and out.is_contiguous() and out.dtype == inp.dtype:
@@ -126,6 +144,9 @@ class Communicator:
         avg = op == "avg"
         if self.size == 1:
             out.view(-1).copy_(inp.reshape(-1))
+            return DONE
+        if _LOCAL_ONLY[0]:
+            out.view(-1).copy_(inp.reshape(self.size, -1)[self.rank])
             return DONE
         if self._gloo:
             # gloo has no reduce-scatter: all-reduce a (fp32 for half types) copy, keep own slice

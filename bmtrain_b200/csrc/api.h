@@ -115,6 +115,8 @@ typedef struct {
     void* stats2;    // (2, T) fp32
     void* ff;        // (T, d_ff) post-activation
     void* pre;       // (T, d_ff) pre-activation, GELU only (NULL for ReLU)
+    // fused attention (csrc/attn_sm100.cu): non-NULL lse selects it; probs is then unused and may be NULL
+    void* lse;       // (batch, heads, seq) fp32
 } BmtGptBlock;
 
 typedef struct {
@@ -131,6 +133,9 @@ typedef struct {
     void* d_qkv;     // like qkv
     void* norm_partial;  // (2, nblk, d) fp32
     int nblk;
+    // fused attention backward scratch (used when the block carries lse): fp32, T*heads*d_head and batch*heads*seq
+    void* dq_acc;
+    void* delta;
 } BmtGptBlockGrad;
 
 int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream);
@@ -180,22 +185,60 @@ int bmt_peer_copy(void* dst, const void* src, int64_t nbytes, int grid, void* st
 // Number of pusher CTAs that balances math and transfer of a fused all-gather -> GEMM / ZeRO gather -> GEMM kernel.
 int bmt_fused_comm_ctas(double flops, double push_bytes, double remote_bytes);
 
-// One chunk of an offloaded Adam step: wait for the gradient copy (grad_ready: cudaEvent_t or NULL), run the host Adam
-// on the pinned arrays, send the new half parameters to the device.
+// ---- asynchronous offloaded Adam: a worker thread of this library runs batches of jobs in submission order ---------
+// One job = one contiguous range of one parameter shard.  The fp32 state is read from (p32, m, v) and written to
+// (p32_out, m_out, v_out); pass the same pointers for an in-place step, a second set of arrays for a step that can
+// still be discarded.  `upload` != 0: the new half parameters are copied to the device when the math is done.
 typedef struct {
-    void* grad_ready;
-    void* p32; void* p16_host; const void* g16_host; void* m; void* v;
-    void* p_dev;
+    void* grad_ready;                       // cudaEvent_t of the gradient's copy to the host, or NULL
+    const void* p32; const void* m; const void* v;
+    void* p32_out; void* m_out; void* v_out;
+    void* p16_host; const void* g16_host; void* p_dev;
     int64_t n;
     float beta1, beta2, eps, lr, scale, wd, bc1, bc2;
-    int bf16;
-} BmtOffloadChunk;
-// Host Adam entry point of the CPU library (bmt_adam_cpu_fp16 / bmt_adam_cpu_bf16), passed in by address.
-typedef void (*BmtAdamCpuFn)(int64_t n, void* p32, void* p16, void* delta, const void* g16, void* m, void* v, float beta1,
-                             float beta2, float eps, float lr, float scale, float wd, float bc1, float bc2);
-// Runs the chunks in order on the calling thread; uploads go to `h2d_stream` with cudaMemcpyAsync.  Returns 0 or the
-// first CUDA error.
-int bmt_offload_adam_run(const BmtOffloadChunk* chunks, int n, BmtAdamCpuFn fn_fp16, BmtAdamCpuFn fn_bf16, void* h2d_stream);
+    int bf16, upload;
+} BmtOffloadJob;
+typedef void (*BmtAdamCpuExFn)(int64_t n, const void* p32, const void* m, const void* v, void* p32_out, void* m_out, void* v_out,
+                               void* p16, const void* g16, float beta1, float beta2, float eps, float lr, float scale, float wd,
+                               float bc1, float bc2, int bf16);
+// Queue a batch (the jobs are copied); returns a ticket > 0, or a negative CUDA error.  Uploads go to `h2d_stream`.
+int64_t bmt_offload_submit(const BmtOffloadJob* jobs, int n, BmtAdamCpuExFn fn, void* h2d_stream);
+// Block until the batch has been processed (math done, uploads queued).  With `stream` != NULL that stream is then made
+// to wait for the batch's uploads.  Returns 0 or the CUDA error the batch ran into.
+int bmt_offload_wait(int64_t ticket, void* stream);
+// 1 when the batch has been processed, 0 while it is queued or running.
+int bmt_offload_poll(int64_t ticket);
+// Take a batch that has not been started out of the queue: 1 = removed (it will never run), 0 = running or finished.
+int bmt_offload_cancel(int64_t ticket);
+// Block until every batch submitted so far has been processed.
+int bmt_offload_drain(void);
+// Queue only the uploads of the jobs (no math): used to publish results that were computed ahead of time.
+int64_t bmt_offload_submit_uploads(const BmtOffloadJob* jobs, int n, void* h2d_stream);
+
+// Rotary position embedding on a packed (b, s, hk, g + 2, d) projection (csrc/elementwise.cu): split != 0 writes rotated q
+// (b, s, hk*g, d), rotated k and copied v (b, s, hk, d); split == 0 is the backward (q, k, v gradients -> packed gradient).
+int bmt_rope_qkv(int64_t batch, int64_t seq, int hk, int g, int d, void* packed, int64_t p_tok, int64_t p_batch, void* q, void* k,
+                 void* v, float theta, int64_t pos0, int split, int dtype, void* stream);
+
+// Fused attention forward (csrc/attn_sm100.cu): o = softmax(scale * q k^T + masks) v, lse = log-sum-exp per row.
+// q (b, sq, h, d), k / v (b, sk, hk, d), o (b, sq, h, d); *_strides = element strides {token, head, batch}, head dim
+// contiguous; d a multiple of 16 up to 128; strides multiples of 8; pointers 16-byte aligned.  lse (b, h, sq) fp32 or
+// NULL; mask (b, sq, sk) bytes (non-zero = attend) or NULL; kv_lens (b) int32 or NULL.
+int bmt_flash_attn_fwd(int64_t batch, int64_t sq, int64_t sk, int h, int hk, int d, const void* q, const int64_t* q_strides,
+                       const void* k, const int64_t* k_strides, const void* v, const int64_t* v_strides, void* o,
+                       const int64_t* o_strides, void* lse, float scale, int causal, const void* mask, const void* kv_lens,
+                       int dtype, void* stream);
+// Backward of bmt_flash_attn_fwd: o / lse from the forward, dout = gradient of o; dq, dk, dv receive the gradients (strided
+// like q, k, v).  Scratch from the caller: dq_acc = batch * sq * h * d floats, delta = batch * h * sq floats.
+int bmt_flash_attn_bwd(int64_t batch, int64_t sq, int64_t sk, int h, int hk, int d, const void* q, const int64_t* q_strides,
+                       const void* k, const int64_t* k_strides, const void* v, const int64_t* v_strides, const void* o,
+                       const int64_t* o_strides, const void* dout, const int64_t* do_strides, const void* lse, void* dq,
+                       const int64_t* dq_strides, void* dk, const int64_t* dk_strides, void* dv, const int64_t* dv_strides,
+                       void* dq_acc, void* delta, float scale, int causal, const void* mask, const void* kv_lens, int dtype,
+                       void* stream);
+// 0, or (wait code << 16 | CTA) of the first attention CTA whose bounded wait ran out; reading clears it
+int bmt_attn_status(void);
+
 // status word of the GEMM kernels: 0, or (role << 16 | cta) of the first CTA whose bounded wait ran out; reading clears it
 int bmt_gemm_status(void);
 // Timing counters of the fused compute+collective GEMM kernels since the last call, in nanoseconds: out[0] sum over

@@ -60,6 +60,15 @@ extern "C" int bmt_gpt_block_forward_steps(const BmtGptBlock* blk, int first_ste
         RUN(bmt_gemm_ex(&g, stream));
     }
     const int64_t tok = 3 * q.hd, head = 3 * q.dh;
+    // 3-5 as one fused attention kernel: q, k, v are strided views of the packed projection, nothing of size s x s is stored
+    if (k.lse) {
+        STEP(3) {
+            const int64_t in_str[3] = {tok, head, q.s * tok}, out_str[3] = {q.hd, q.dh, q.s * q.hd};
+            RUN(bmt_flash_attn_fwd(q.b, q.s, q.s, (int)q.h, (int)q.h, (int)q.dh, k.qkv, in_str, off(k.qkv, q.dh), in_str,
+                                   off(k.qkv, 2 * q.dh), in_str, k.ctx, out_str, k.lse, 1.f / sqrtf((float)q.dh), k.causal, k.mask,
+                                   nullptr, dt, stream));
+        }
+    } else {
     // 3. scores = q k^T / sqrt(d_head)   -> probs (b, h, s, ld)
     STEP(3) {
         BmtGemmDesc g = plain(q.s, q.s, q.dh, k.qkv, tok, 0, off(k.qkv, q.dh), tok, 0, k.probs, k.probs_ld, dt);
@@ -77,6 +86,7 @@ extern "C" int bmt_gpt_block_forward_steps(const BmtGptBlock* blk, int first_ste
         g.c_bs0 = q.dh; g.c_bs1 = q.s * q.hd;
         g.batch_inner = q.h; g.batch_outer = q.b;
         RUN(bmt_gemm_ex(&g, stream));
+    }
     }
     // 6. h1 = ctx W_o^T + b_o + x
     STEP(6) {
@@ -149,6 +159,14 @@ extern "C" int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockG
     RUN(bmt_colsum(q.T, q.d, w.d_h1, dt, w.d_out_b, stream));
     // ---- attention core
     const int64_t pl = k.probs_ld;
+    if (k.lse) {
+        // fused backward: dq, dk, dv go straight into the packed d_qkv buffer
+        const int64_t in_str[3] = {tok, head, q.s * tok}, out_str[3] = {q.hd, q.dh, q.s * q.hd};
+        RUN(bmt_flash_attn_bwd(q.b, q.s, q.s, (int)q.h, (int)q.h, (int)q.dh, k.qkv, in_str, off(k.qkv, q.dh), in_str,
+                               off(k.qkv, 2 * q.dh), in_str, k.ctx, out_str, w.d_ctx, out_str, k.lse, w.d_qkv, in_str,
+                               off(w.d_qkv, q.dh), in_str, off(w.d_qkv, 2 * q.dh), in_str, w.dq_acc, w.delta,
+                               1.f / sqrtf((float)q.dh), k.causal, k.mask, nullptr, dt, stream));
+    } else {
     {   // dP = d_ctx v^T
         BmtGemmDesc g = plain(q.s, q.s, q.dh, w.d_ctx, q.hd, 0, off(k.qkv, 2 * q.dh), tok, 0, w.d_probs, pl, dt);
         g.a_bs0 = q.dh; g.a_bs1 = q.s * q.hd; g.b_bs0 = head; g.b_bs1 = q.s * tok;
@@ -173,6 +191,7 @@ extern "C" int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockG
         g.a_bs0 = q.s * pl; g.a_bs1 = q.h * q.s * pl; g.b_bs0 = q.dh; g.b_bs1 = q.s * q.hd;
         g.c_bs0 = head; g.c_bs1 = q.s * tok; g.batch_inner = q.h; g.batch_outer = q.b;
         RUN(bmt_gemm_ex(&g, stream));
+    }
     }
     // ---- QKV projection
     {   // d_ln1 = d_qkv W_qkv   (reuses the d_ln2 buffer)

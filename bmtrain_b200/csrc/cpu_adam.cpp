@@ -168,10 +168,18 @@ struct __attribute__((target("avx512f"))) AdamVec {
     __m512d s0, q0;
 };
 
-// 16 elements at `at`: updates m, v and the fp32 parameters in place and returns the new parameters.
+// Where the new fp32 state goes: back over the old one (in place) or into a second set of arrays.  Writing a second
+// set with ordinary stores would read every destination line first; whole lines are written, so they go out with
+// non-temporal stores and the memory traffic stays what the in-place form has.
+struct StateOut {
+    float *p, *m, *v;
+    bool stream;   // destinations differ from the sources and are 64-byte aligned: non-temporal stores
+};
+
+// 16 elements at `at`: new m, v and fp32 parameters go to `o` (which may alias the inputs); returns the new parameters.
 template <bool BF16>
-__attribute__((target("avx512f,avx512bw,avx512vl"))) inline __m512 adam16(int64_t at, float* p, const uint16_t* g, float* m, float* v,
-                                                                           AdamVec& k, bool stats) {
+__attribute__((target("avx512f,avx512bw,avx512vl"))) inline __m512 adam16(int64_t at, const float* p, const uint16_t* g, const float* m,
+                                                                           const float* v, const StateOut& o, AdamVec& k, bool stats) {
     const __m512 gf = _mm512_mul_ps(load_half16(g + at, BF16), k.isc);
     const __m512 mm = _mm512_fmadd_ps(k.b1, _mm512_loadu_ps(m + at), _mm512_mul_ps(k.ob1, gf));
     const __m512 vv = _mm512_fmadd_ps(k.b2, _mm512_loadu_ps(v + at), _mm512_mul_ps(k.ob2, _mm512_mul_ps(gf, gf)));
@@ -180,9 +188,15 @@ __attribute__((target("avx512f,avx512bw,avx512vl"))) inline __m512 adam16(int64_
     const __m512 upd = _mm512_div_ps(_mm512_mul_ps(mm, k.ibc1), den);
     __m512 np = _mm512_fnmadd_ps(k.lr, upd, old);
     np = _mm512_fnmadd_ps(k.lrwd, old, np);
-    _mm512_storeu_ps(m + at, mm);
-    _mm512_storeu_ps(v + at, vv);
-    _mm512_storeu_ps(p + at, np);
+    if (o.stream) {
+        _mm512_stream_ps(o.m + at, mm);
+        _mm512_stream_ps(o.v + at, vv);
+        _mm512_stream_ps(o.p + at, np);
+    } else {
+        _mm512_storeu_ps(o.m + at, mm);
+        _mm512_storeu_ps(o.v + at, vv);
+        _mm512_storeu_ps(o.p + at, np);
+    }
     if (stats) {
         const __m512 d = _mm512_sub_ps(np, old);
         const __m512d lo = _mm512_cvtps_pd(_mm512_castps512_ps256(d)), hi = _mm512_cvtps_pd(_mm256_castpd_ps(_mm512_extractf64x4_pd(_mm512_castps_pd(d), 1)));
@@ -193,9 +207,23 @@ __attribute__((target("avx512f,avx512bw,avx512vl"))) inline __m512 adam16(int64_
 }
 
 template <bool BF16>
+void adam_scalar_out(int64_t b, int64_t e, const float* p, uint16_t* ph, const uint16_t* g, const float* m, const float* v,
+                     const StateOut& o, const AdamConst& c) {
+    for (int64_t i = b; i < e; ++i) {
+        const float gf = (BF16 ? bf16_to_float(g[i]) : half_to_float(g[i])) * c.inv_scale;
+        const float mm = c.beta1 * m[i] + (1.f - c.beta1) * gf;
+        const float vv = c.beta2 * v[i] + (1.f - c.beta2) * gf * gf;
+        const float old = p[i];
+        const float np = old - c.lr * (mm * c.inv_bc1) / (std::sqrt(vv * c.inv_bc2) + c.eps) - c.lr * c.wd * old;
+        o.m[i] = mm; o.v[i] = vv; o.p[i] = np;
+        ph[i] = BF16 ? float_to_bf16(np) : float_to_half(np);
+    }
+}
+
+template <bool BF16>
 __attribute__((target("avx512f,avx512bw,avx512vl")))
-void adam_avx512(int64_t b, int64_t e, float* p, uint16_t* ph, const uint16_t* g, float* m, float* v, const AdamConst& c,
-                 double* dsum, double* dsq) {
+void adam_avx512(int64_t b, int64_t e, const float* p, uint16_t* ph, const uint16_t* g, const float* m, const float* v,
+                 const StateOut& out, const AdamConst& c, double* dsum, double* dsq) {
     AdamVec k;
     k.b1 = _mm512_set1_ps(c.beta1); k.ob1 = _mm512_set1_ps(1.f - c.beta1);
     k.b2 = _mm512_set1_ps(c.beta2); k.ob2 = _mm512_set1_ps(1.f - c.beta2);
@@ -204,19 +232,25 @@ void adam_avx512(int64_t b, int64_t e, float* p, uint16_t* ph, const uint16_t* g
     k.s0 = _mm512_setzero_pd(); k.q0 = _mm512_setzero_pd();
     const bool stats = dsum != nullptr;
     int64_t i = b;
+    StateOut o = out;
+    // non-temporal stores need 64-byte aligned destinations: the three arrays have to be aligned alike at `b`
+    o.stream = out.stream && !((((uintptr_t)(out.p + b)) | ((uintptr_t)(out.m + b)) | ((uintptr_t)(out.v + b))) & 63);
     // the half-precision output is write-only: whole cache lines of it go out with non-temporal stores, which saves the
     // read-for-ownership of a line that would only be overwritten (the step is bound by host memory traffic)
-    while (i + 16 <= e && (((uintptr_t)(ph + i)) & 63)) { store_half16(ph + i, adam16<BF16>(i, p, g, m, v, k, stats), BF16); i += 16; }
+    while (i + 16 <= e && (((uintptr_t)(ph + i)) & 63)) { store_half16(ph + i, adam16<BF16>(i, p, g, m, v, o, k, stats), BF16); i += 16; }
     for (; i + 32 <= e; i += 32) {
-        const __m256i h0 = to_half16(adam16<BF16>(i, p, g, m, v, k, stats), BF16);
-        const __m256i h1 = to_half16(adam16<BF16>(i + 16, p, g, m, v, k, stats), BF16);
+        const __m256i h0 = to_half16(adam16<BF16>(i, p, g, m, v, o, k, stats), BF16);
+        const __m256i h1 = to_half16(adam16<BF16>(i + 16, p, g, m, v, o, k, stats), BF16);
         _mm512_stream_si512((__m512i*)(ph + i), _mm512_inserti64x4(_mm512_castsi256_si512(h0), h1, 1));
     }
-    for (; i + 16 <= e; i += 16) store_half16(ph + i, adam16<BF16>(i, p, g, m, v, k, stats), BF16);
+    for (; i + 16 <= e; i += 16) store_half16(ph + i, adam16<BF16>(i, p, g, m, v, o, k, stats), BF16);
     _mm_sfence();   // non-temporal stores are ordered before whatever signals that this range is done
     const __m512d s0 = k.s0, q0 = k.q0;
     if (dsum) { *dsum += _mm512_reduce_add_pd(s0); *dsq += _mm512_reduce_add_pd(q0); }
-    if (i < e) adam_scalar<BF16>(i, e, p, ph, g, m, v, c, dsum, dsq);
+    if (i < e) {
+        if (out.p == p) adam_scalar<BF16>(i, e, out.p, ph, g, out.m, out.v, c, dsum, dsq);
+        else adam_scalar_out<BF16>(i, e, p, ph, g, m, v, out, c);
+    }
 }
 
 // --------------------------------------------------------------------------------------------------- AVX2
@@ -263,6 +297,20 @@ int cpu_level() {
     return level;
 }
 
+// State read from (p, m, v), new state written to (po, mo, vo); the two sets are either identical or disjoint.
+template <bool BF16>
+void adam_cpu_out(int64_t n, const float* p, const float* m, const float* v, float* po, float* mo, float* vo, uint16_t* ph,
+                  const uint16_t* g, const AdamConst& c) {
+    const int level = cpu_level();
+    const StateOut out{po, mo, vo, po != p};
+    Pool::get().parallel_for(n, 1 << 16, [&](int64_t b, int64_t e, int) {
+        if (level == 2) adam_avx512<BF16>(b, e, p, ph, g, m, v, out, c, nullptr, nullptr);
+        else if (po == p && level == 1 && !BF16) adam_avx2_fp16(b, e, po, ph, g, mo, vo, c, nullptr, nullptr);
+        else if (po == p) adam_scalar<BF16>(b, e, po, ph, g, mo, vo, c, nullptr, nullptr);
+        else adam_scalar_out<BF16>(b, e, p, ph, g, m, v, out, c);
+    });
+}
+
 template <bool BF16>
 void adam_cpu(int64_t n, float* p, uint16_t* ph, float* delta, const uint16_t* g, float* m, float* v, float beta1, float beta2,
               float eps, float lr, float scale, float wd, float bc1, float bc2) {
@@ -270,10 +318,11 @@ void adam_cpu(int64_t n, float* p, uint16_t* ph, float* delta, const uint16_t* g
     Pool& pool = Pool::get();
     const int level = cpu_level();
     std::vector<double> sums(delta ? pool.size() * 16 : 0, 0.0);  // padded to keep workers on separate cache lines
+    const StateOut in_place{p, m, v, false};
     auto body = [&](int64_t b, int64_t e, int w) {
         double* ds = delta ? &sums[w * 16] : nullptr;
         double* dq = delta ? &sums[w * 16 + 1] : nullptr;
-        if (level == 2) adam_avx512<BF16>(b, e, p, ph, g, m, v, c, ds, dq);
+        if (level == 2) adam_avx512<BF16>(b, e, p, ph, g, m, v, in_place, c, ds, dq);
         else if (level == 1 && !BF16) adam_avx2_fp16(b, e, p, ph, g, m, v, c, ds, dq);
         else adam_scalar<BF16>(b, e, p, ph, g, m, v, c, ds, dq);
     };
@@ -318,6 +367,18 @@ void bmt_adam_cpu_bf16(int64_t n, void* p32, void* p16, void* delta, const void*
                        float eps, float lr, float scale, float wd, float bc1, float bc2) {
     adam_cpu<true>(n, (float*)p32, (uint16_t*)p16, (float*)delta, (const uint16_t*)g16, (float*)m, (float*)v, beta1, beta2, eps, lr,
                    scale, wd, bc1, bc2);
+}
+
+// Out-of-place capable form used by the offload worker: reads (p32, m, v), writes (p32_out, m_out, v_out) -- pass the
+// same three pointers for an in-place step -- and the half-precision copy `p16`.
+void bmt_adam_cpu_ex(int64_t n, const void* p32, const void* m, const void* v, void* p32_out, void* m_out, void* v_out, void* p16,
+                     const void* g16, float beta1, float beta2, float eps, float lr, float scale, float wd, float bc1, float bc2,
+                     int bf16) {
+    const AdamConst c{beta1, beta2, eps, lr, 1.f / scale, wd, 1.f / bc1, 1.f / bc2};
+    if (bf16) adam_cpu_out<true>(n, (const float*)p32, (const float*)m, (const float*)v, (float*)p32_out, (float*)m_out, (float*)v_out,
+                                 (uint16_t*)p16, (const uint16_t*)g16, c);
+    else adam_cpu_out<false>(n, (const float*)p32, (const float*)m, (const float*)v, (float*)p32_out, (float*)m_out, (float*)v_out,
+                             (uint16_t*)p16, (const uint16_t*)g16, c);
 }
 
 void bmt_fp16_from_fp32(int64_t n, const void* src, void* dst) { convert<false>(n, (const float*)src, (uint16_t*)dst); }

@@ -79,6 +79,50 @@ __global__ void __launch_bounds__(256) gelu_kernel(int64_t n8, const T* __restri
     }
 }
 
+// Rotary position embedding on a packed projection.  `packed` is (b, s, hk, g + 2, d): per kv head g query heads, one key
+// head, one value head ("half rotation" convention: element i pairs with i + d/2, angle = pos * theta^(-2i/d)).
+// SPLIT: packed -> q (b, s, hk*g, d) rotated, k (b, s, hk, d) rotated, v (b, s, hk, d) copied, all contiguous.
+// !SPLIT (backward): gradients of q, k, v -> gradient of packed (contiguous), q and k parts rotated back.
+// One thread moves 8 elements of the lower half of a head and their 8 partners of the upper half.
+template <typename T, bool SPLIT>
+__global__ void __launch_bounds__(256) rope_qkv_kernel(int64_t batch, int64_t seq, int hk, int g, int d, T* __restrict__ packed,
+                                                       int64_t p_tok, int64_t p_batch, T* __restrict__ q, T* __restrict__ k,
+                                                       T* __restrict__ v, float log2_theta, int64_t pos0) {
+    const int half = d / 2, vecs = half / 8, slots = hk * (g + 2);
+    const int64_t total = batch * seq * slots * vecs;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % vecs) * 8;
+        int64_t r = i / vecs;
+        const int slot = (int)(r % slots);
+        r /= slots;
+        const int64_t t = r % seq, bb = r / seq;
+        const int kvh = slot / (g + 2), j = slot % (g + 2);
+        T* pin = packed + bb * p_batch + t * p_tok + (int64_t)slot * d;
+        T* sep = j < g ? q + (((bb * seq + t) * hk + kvh) * g + j) * d : (j == g ? k : v) + ((bb * seq + t) * hk + kvh) * d;
+        const T* src = SPLIT ? pin : sep;
+        T* dst = SPLIT ? sep : pin;
+        bmt::Vec16<T> lo = bmt::ld16(src + c), hi = bmt::ld16(src + half + c), olo, ohi;
+        if (j <= g) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                // theta^(-2 (c + e) / d) = 2^(-(2 (c + e) / d) log2 theta)
+                const float inv_freq = exp2f(-(float)(2 * (c + e)) / (float)d * log2_theta);
+                float sn, cs;
+                sincosf((float)(pos0 + t) * inv_freq, &sn, &cs);
+                if (!SPLIT) sn = -sn;
+                const float a = bmt::Cvt<T>::to_f(lo.v[e]), b2 = bmt::Cvt<T>::to_f(hi.v[e]);
+                olo.v[e] = bmt::Cvt<T>::from_f(a * cs - b2 * sn);
+                ohi.v[e] = bmt::Cvt<T>::from_f(a * sn + b2 * cs);
+            }
+        } else {
+            olo = lo;
+            ohi = hi;
+        }
+        bmt::st16(dst + c, olo);
+        bmt::st16(dst + half + c, ohi);
+    }
+}
+
 unsigned grid1d(int64_t work) {
     int64_t b = bmt::ceil_div64(work, 256);
     if (b > 148 * 8) b = 148 * 8;
@@ -125,6 +169,27 @@ extern "C" int bmt_gelu_fwd(int64_t n, const void* x, int dtype, void* out, void
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == BMT_DT_F16) gelu_kernel<__half><<<grid1d(n / 8), 256, 0, s>>>(n / 8, (const __half*)x, (__half*)out);
     else gelu_kernel<__nv_bfloat16><<<grid1d(n / 8), 256, 0, s>>>(n / 8, (const __nv_bfloat16*)x, (__nv_bfloat16*)out);
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}
+
+// Rotary embedding of a packed (b, s, hk, g + 2, d) projection (token / batch strides p_tok / p_batch, the last three
+// dims contiguous).  split != 0: writes rotated q, k and the copied v (contiguous); split == 0: the backward, reads the
+// three gradients and writes the packed gradient (contiguous, p_tok / p_batch describe it).  d: multiple of 16.
+extern "C" int bmt_rope_qkv(int64_t batch, int64_t seq, int hk, int g, int d, void* packed, int64_t p_tok, int64_t p_batch, void* q,
+                            void* k, void* v, float theta, int64_t pos0, int split, int dtype, void* stream) {
+    if (batch <= 0 || seq <= 0) return 0;
+    if (d % 16 || dtype == BMT_DT_F32 || (p_tok & 7) || (p_batch & 7)) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t work = batch * seq * hk * (g + 2) * (d / 16);
+    const float l2t = log2f(theta);
+    if (dtype == BMT_DT_F16) {
+        if (split) rope_qkv_kernel<__half, true><<<grid1d(work), 256, 0, s>>>(batch, seq, hk, g, d, (__half*)packed, p_tok, p_batch, (__half*)q, (__half*)k, (__half*)v, l2t, pos0);
+        else rope_qkv_kernel<__half, false><<<grid1d(work), 256, 0, s>>>(batch, seq, hk, g, d, (__half*)packed, p_tok, p_batch, (__half*)q, (__half*)k, (__half*)v, l2t, pos0);
+    } else {
+        if (split) rope_qkv_kernel<__nv_bfloat16, true><<<grid1d(work), 256, 0, s>>>(batch, seq, hk, g, d, (__nv_bfloat16*)packed, p_tok, p_batch, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, l2t, pos0);
+        else rope_qkv_kernel<__nv_bfloat16, false><<<grid1d(work), 256, 0, s>>>(batch, seq, hk, g, d, (__nv_bfloat16*)packed, p_tok, p_batch, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, l2t, pos0);
+    }
     bmt_count_launch(1);
     return (int)cudaGetLastError();
 }

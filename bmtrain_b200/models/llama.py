@@ -43,11 +43,7 @@ class LlamaAttention(DistributedModule):
         else:
             b, s = qkv.shape[0], qkv.shape[1]
             qkv = qkv.view(b, s, self.hk, self.h // self.hk + 2, self.dh)
-        g = self.h // self.hk
-        q = qkv[:, :, :, :g].reshape(b, s, self.h, self.dh)
-        k = qkv[:, :, :, g]
-        v = qkv[:, :, :, g + 1]
-        q, k = _ew.rope(q, k, self.rope_theta)
+        q, k, v = _ew.rope_qkv(qkv, self.h // self.hk, self.rope_theta)
         out = _attn.attention(q, k, v, 1.0 / math.sqrt(self.dh), causal=True)
         if tp > 1:
             out = out.permute(1, 0, 2, 3).reshape(s, b, self.h * self.dh)

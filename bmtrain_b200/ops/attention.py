@@ -2,12 +2,17 @@
 
 The reference example materialises the scores with two ``bmm`` calls and a
 ``(b, S, S)`` boolean mask (``example/layers/attention.py:78-104``).  Here the
-two contractions run as batched tcgen05 GEMMs straight on the strided
-``(b, s, heads, dim)`` views (no permute/contiguous copies) and the masked
-softmax -- causal flag, per-sample key lengths and/or a dense boolean mask --
-is one fused in-place kernel; backward uses the same GEMM kernel in its NT /
-NN / TN forms plus one fused ``dS = P * (dP - rowsum(dP * P))`` kernel.
-Grouped-query attention is supported (``kv heads`` divides ``heads``).
+forward pass is one fused tcgen05 kernel (``csrc/attn_sm100.cu``): scores and
+probabilities stay in tensor memory / shared memory, only the output and one
+log-sum-exp per row reach HBM.  Causal flag, per-sample key lengths and a
+dense boolean mask are applied inside the kernel; grouped-query attention is
+supported (``kv heads`` divides ``heads``).  Head dims that the fused kernel
+does not take (not a multiple of 16, or above 128) use the two-GEMM form:
+batched tcgen05 GEMMs on the strided ``(b, s, heads, dim)`` views plus a fused
+masked-softmax kernel, with a backward built from the same pieces (NT / NN / TN
+GEMMs and one fused ``dS = P * (dP - rowsum(dP * P))`` kernel).  The fused
+backward recomputes the probabilities per 128 x 128 tile from q, k and the
+saved log-sum-exp and accumulates dK / dV in tensor memory.
 """
 from __future__ import annotations
 
@@ -43,8 +48,61 @@ def _reference_attention(q, k, v, scale, causal, mask, kv_lens):
     return torch.einsum("bhqk,bkhd->bqhd", p, v.float()).to(q.dtype)
 
 
+def _strides3(t):
+    """{token, head, batch} element strides of a (b, s, h, d) tensor as a ctypes array."""
+    return (ctypes.c_int64 * 3)(t.stride(1), t.stride(2), t.stride(0))
+
+
+def flash_usable(q, k, v) -> bool:
+    """Whether the fused kernel takes these operands (shape/stride rules of ``bmt_flash_attn_fwd``)."""
+    import os
+
+    d = q.shape[-1]
+    if os.environ.get("BMT_FLASH_ATTN", "1") == "0" or d % 16 or d > 128 or q.dtype not in _DT:
+        return False
+    for t in (q, k, v):
+        if t.stride(3) != 1 or t.data_ptr() % 16 or any(t.stride(i) % 8 for i in range(3)):
+            return False
+    return True
+
+
+def flash_forward(q, k, v, scale, causal, mask8, lens32):
+    """Fused forward: returns ``(o (b, sq, h, d), lse (b, h, sq) fp32)``."""
+    lib = _native.cuda_lib()
+    b, sq, h, d = q.shape
+    sk, hk = k.shape[1], k.shape[2]
+    o = torch.empty(b, sq, h, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(b, h, sq, dtype=torch.float32, device=q.device)
+    _native.check(lib.bmt_flash_attn_fwd(
+        ctypes.c_int64(b), ctypes.c_int64(sq), ctypes.c_int64(sk), ctypes.c_int(h), ctypes.c_int(hk), ctypes.c_int(d),
+        _native.ptr(q), _strides3(q), _native.ptr(k), _strides3(k), _native.ptr(v), _strides3(v), _native.ptr(o), _strides3(o),
+        _native.ptr(lse), ctypes.c_float(scale), ctypes.c_int(1 if causal else 0), _native.ptr(mask8), _native.ptr(lens32),
+        ctypes.c_int(_DT[q.dtype]), _native.stream_handle()), "fused attention forward")
+    return o, lse
+
+
+def flash_backward(q, k, v, o, lse, do, scale, causal, mask8, lens32):
+    """Fused backward: returns ``(dq, dk, dv)`` shaped like ``q, k, v`` (contiguous)."""
+    lib = _native.cuda_lib()
+    b, sq, h, d = q.shape
+    sk, hk = k.shape[1], k.shape[2]
+    dq = torch.empty(b, sq, h, d, dtype=q.dtype, device=q.device)
+    dk = torch.empty(b, sk, hk, d, dtype=q.dtype, device=q.device)
+    dv = torch.empty(b, sk, hk, d, dtype=q.dtype, device=q.device)
+    dq_acc = torch.empty(b * sq * h * d, dtype=torch.float32, device=q.device)
+    delta = torch.empty(b * h * sq, dtype=torch.float32, device=q.device)
+    _native.check(lib.bmt_flash_attn_bwd(
+        ctypes.c_int64(b), ctypes.c_int64(sq), ctypes.c_int64(sk), ctypes.c_int(h), ctypes.c_int(hk), ctypes.c_int(d),
+        _native.ptr(q), _strides3(q), _native.ptr(k), _strides3(k), _native.ptr(v), _strides3(v), _native.ptr(o), _strides3(o),
+        _native.ptr(do), _strides3(do), _native.ptr(lse), _native.ptr(dq), _strides3(dq), _native.ptr(dk), _strides3(dk),
+        _native.ptr(dv), _strides3(dv), _native.ptr(dq_acc), _native.ptr(delta), ctypes.c_float(scale),
+        ctypes.c_int(1 if causal else 0), _native.ptr(mask8), _native.ptr(lens32), ctypes.c_int(_DT[q.dtype]),
+        _native.stream_handle()), "fused attention backward")
+    return dq, dk, dv
+
+
 def _softmax_args(mask, kv_lens):
-    m = None if mask is None else mask.to(torch.uint8).contiguous()
+    m = None if mask is None else (mask.contiguous().view(torch.uint8) if mask.dtype == torch.bool else mask.to(torch.uint8).contiguous())
     l = None if kv_lens is None else kv_lens.to(torch.int32).contiguous()
     return m, l
 
@@ -57,25 +115,46 @@ class AttentionFunction(torch.autograd.Function):
         sk, hk = k.shape[1], k.shape[2]
         assert h % hk == 0 and q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1
         group = h // hk
-        # scores (b, h, sq, sk): batch inner = head (kv head = head // group), outer = sample
+        m8, l32 = _softmax_args(mask, kv_lens)
+        ctx.scale, ctx.group, ctx.causal = scale, group, causal
+        if flash_usable(q, k, v):
+            o, lse = flash_forward(q, k, v, scale, causal, m8, l32)
+            # nothing of size sq x sk is kept: backward rebuilds the probabilities tile by tile from q, k and lse
+            ctx.save_for_backward(q, k, v, o, lse, m8, l32)
+            ctx.fused = True
+            return o
         assert d % 8 == 0, "head dimension must be a multiple of 8"
-        skp = (sk + 7) // 8 * 8  # row pitch keeps every row 16-byte aligned for TMA
+        p = AttentionFunction._probabilities(lib, q, k, scale, causal, m8, l32, group)
+        o = torch.empty(b, sq, h, d, dtype=q.dtype, device=q.device)
+        _bgemm_heads(lib, "pv", sq, d, sk, p, v, o, b, h, group, 1.0)
+        ctx.save_for_backward(q, k, v, p)
+        ctx.fused = False
+        return o
+
+    @staticmethod
+    def _probabilities(lib, q, k, scale, causal, m8, l32, group):
+        """(b, h, sq, sk) masked softmax of the scaled scores (row pitch padded to 8 elements for TMA)."""
+        b, sq, h, d = q.shape
+        sk = k.shape[1]
+        skp = (sk + 7) // 8 * 8
         p = torch.empty(b, h, sq, skp, dtype=q.dtype, device=q.device)[..., :sk]
         _bgemm_heads(lib, "nt", sq, sk, d, q, k, p, b, h, group, scale)
-        m8, l32 = _softmax_args(mask, kv_lens)
         _native.check(lib.bmt_masked_softmax(
             ctypes.c_int64(b), ctypes.c_int64(h), ctypes.c_int64(sq), ctypes.c_int64(sk), ctypes.c_int64(p.stride(2)), _native.ptr(p),
             ctypes.c_int(_DT[q.dtype]), ctypes.c_int(1 if causal else 0), _native.ptr(m8), _native.ptr(l32),
             _native.stream_handle()), "masked softmax kernel")
-        o = torch.empty(b, sq, h, d, dtype=q.dtype, device=q.device)
-        _bgemm_heads(lib, "pv", sq, d, sk, p, v, o, b, h, group, 1.0)
-        ctx.save_for_backward(q, k, v, p)
-        ctx.scale, ctx.group = scale, group
-        return o
+        return p
 
     @staticmethod
     def backward(ctx, do):
         lib = _native.cuda_lib()
+        if ctx.fused:
+            q, k, v, o, lse, m8, l32 = ctx.saved_tensors
+            do = do.contiguous()
+            if do.data_ptr() % 16:
+                do = do.clone()
+            dq, dk, dv = flash_backward(q, k, v, o, lse, do, ctx.scale, ctx.causal, m8, l32)
+            return dq, dk, dv, None, None, None, None
         q, k, v, p = ctx.saved_tensors
         b, sq, h, d = q.shape
         sk, hk = k.shape[1], k.shape[2]

@@ -1,4 +1,9 @@
-"""Small fused elementwise operators: SwiGLU and rotary position embedding."""
+"""Small fused elementwise operators: SwiGLU and rotary position embedding.
+
+The rotary embedding works on the packed projection ``(b, s, kv heads, g + 2, d)`` the Llama-shaped attention produces:
+one kernel rotates the query and key heads and lays q, k, v out contiguously; its backward is one kernel as well
+(``csrc/elementwise.cu``).  The eager PyTorch form below is the CPU definition and the numerical reference.
+"""
 from __future__ import annotations
 
 import ctypes
@@ -78,3 +83,45 @@ class RopeFunction(torch.autograd.Function):
 def rope(q: torch.Tensor, k: torch.Tensor, theta: float = 10000.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Rotary embedding of ``q`` (b, s, h, d) and ``k`` (b, s, hk, d) by absolute position."""
     return RopeFunction.apply(q, k, theta)
+
+
+class RopeQKVFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, packed, g, theta):
+        b, s, hk, _, d = packed.shape
+        q = torch.empty(b, s, hk * g, d, dtype=packed.dtype, device=packed.device)
+        k = torch.empty(b, s, hk, d, dtype=packed.dtype, device=packed.device)
+        v = torch.empty(b, s, hk, d, dtype=packed.dtype, device=packed.device)
+        _native.check(_native.cuda_lib().bmt_rope_qkv(
+            ctypes.c_int64(b), ctypes.c_int64(s), ctypes.c_int(hk), ctypes.c_int(g), ctypes.c_int(d), _native.ptr(packed),
+            ctypes.c_int64(packed.stride(1)), ctypes.c_int64(packed.stride(0)), _native.ptr(q), _native.ptr(k), _native.ptr(v),
+            ctypes.c_float(theta), ctypes.c_int64(0), ctypes.c_int(1), ctypes.c_int(_DT[packed.dtype]), _native.stream_handle()),
+            "rotary embedding kernel")
+        ctx.g, ctx.theta, ctx.shape = g, theta, packed.shape
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, gq, gk, gv):
+        b, s, hk, _, d = ctx.shape
+        gq, gk, gv = gq.contiguous(), gk.contiguous(), gv.contiguous()
+        out = torch.empty(ctx.shape, dtype=gq.dtype, device=gq.device)
+        _native.check(_native.cuda_lib().bmt_rope_qkv(
+            ctypes.c_int64(b), ctypes.c_int64(s), ctypes.c_int(hk), ctypes.c_int(ctx.g), ctypes.c_int(d), _native.ptr(out),
+            ctypes.c_int64(out.stride(1)), ctypes.c_int64(out.stride(0)), _native.ptr(gq), _native.ptr(gk), _native.ptr(gv),
+            ctypes.c_float(ctx.theta), ctypes.c_int64(0), ctypes.c_int(0), ctypes.c_int(_DT[gq.dtype]), _native.stream_handle()),
+            "rotary embedding backward kernel")
+        return out, None, None
+
+
+def rope_qkv(packed: torch.Tensor, g: int, theta: float = 10000.0):
+    """``packed`` (b, s, kv heads, g + 2, d) -> rotated ``q`` (b, s, kv heads * g, d), rotated ``k`` and ``v``
+    (b, s, kv heads, d).  The token and batch dims of ``packed`` may be strided (a permuted view); the rest is contiguous."""
+    b, s, hk, _, d = packed.shape
+    ok = (packed.is_cuda and d % 16 == 0 and packed.dtype in (torch.float16, torch.bfloat16) and packed.stride(4) == 1
+          and packed.stride(3) == d and packed.stride(2) == (g + 2) * d and packed.stride(0) % 8 == 0 and packed.stride(1) % 8 == 0)
+    if not ok:
+        q = packed[:, :, :, :g].reshape(b, s, hk * g, d)
+        k, v = packed[:, :, :, g], packed[:, :, :, g + 1]
+        q, k = rope(q, k, theta)
+        return q, k, v
+    return RopeQKVFunction.apply(packed, g, theta)

@@ -27,6 +27,7 @@ class _Block(ctypes.Structure):
         ("x", _c_void_p), ("y", _c_void_p),
         ("ln1", _c_void_p), ("stats1", _c_void_p), ("qkv", _c_void_p), ("probs", _c_void_p), ("probs_ld", _i64),
         ("ctx", _c_void_p), ("h1", _c_void_p), ("ln2", _c_void_p), ("stats2", _c_void_p), ("ff", _c_void_p), ("pre", _c_void_p),
+        ("lse", _c_void_p),
     ]
 
 
@@ -39,11 +40,19 @@ class _Grad(ctypes.Structure):
         ("acc_w", _int),
         ("d_ff", _c_void_p), ("d_ln2", _c_void_p), ("d_h1", _c_void_p), ("d_ctx", _c_void_p), ("d_probs", _c_void_p),
         ("d_qkv", _c_void_p), ("norm_partial", _c_void_p), ("nblk", _int),
+        ("dq_acc", _c_void_p), ("delta", _c_void_p),
     ]
 
 
 _PARAM_NAMES = ("ln1_w", "ln1_b", "qkv_w", "qkv_b", "out_w", "out_b", "ln2_w", "ln2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b")
 _WEIGHTS = ("qkv_w", "out_w", "fc1_w", "fc2_w")
+
+
+def _as_bytes(mask: torch.Tensor) -> torch.Tensor:
+    """A boolean mask as bytes without a conversion pass (bool tensors are stored as one 0/1 byte per element)."""
+    if mask.dtype == torch.bool:
+        return mask.contiguous().view(torch.uint8)
+    return mask.to(torch.uint8).contiguous()
 
 
 def _fill(blk: _Block, x, y, mask, params, saved, n_heads, d_head, act, eps, causal):
@@ -57,9 +66,13 @@ def _fill(blk: _Block, x, y, mask, params, saved, n_heads, d_head, act, eps, cau
     for name, p in zip(_PARAM_NAMES, params):
         setattr(blk, name, p.data_ptr())
     blk.x, blk.y = x.data_ptr(), y.data_ptr()
-    for name in ("ln1", "stats1", "qkv", "probs", "ctx", "h1", "ln2", "stats2", "ff"):
+    for name in ("ln1", "stats1", "qkv", "ctx", "h1", "ln2", "stats2", "ff"):
         setattr(blk, name, saved[name].data_ptr())
-    blk.probs_ld = saved["probs"].stride(2)
+    if saved.get("lse") is not None:
+        # fused attention: scores and probabilities never reach memory, one log-sum-exp per row is kept instead
+        blk.lse, blk.probs, blk.probs_ld = saved["lse"].data_ptr(), None, 0
+    else:
+        blk.lse, blk.probs, blk.probs_ld = None, saved["probs"].data_ptr(), saved["probs"].stride(2)
     blk.pre = saved["pre"].data_ptr() if saved.get("pre") is not None else None
 
 
@@ -72,11 +85,15 @@ class GPTBlockFunction(torch.autograd.Function):
         T, hd, dff = b * s, n_heads * d_head, params[8].shape[0]
         dev, dt = x.device, x.dtype
         sp = (s + 7) // 8 * 8
-        mask8 = None if mask is None else mask.to(torch.uint8).contiguous()
+        mask8 = None if mask is None else _as_bytes(mask)
+        import os
+
+        fused_attn = d_head % 16 == 0 and d_head <= 128 and os.environ.get("BMT_FLASH_ATTN", "1") != "0"
         saved = {
             "ln1": torch.empty(T, d, dtype=dt, device=dev), "stats1": torch.empty(2, T, dtype=torch.float32, device=dev),
             "qkv": torch.empty(T, 3 * hd, dtype=dt, device=dev),
-            "probs": torch.empty(b, n_heads, s, sp, dtype=dt, device=dev),
+            "probs": None if fused_attn else torch.empty(b, n_heads, s, sp, dtype=dt, device=dev),
+            "lse": torch.empty(b, n_heads, s, dtype=torch.float32, device=dev) if fused_attn else None,
             "ctx": torch.empty(T, hd, dtype=dt, device=dev), "h1": torch.empty(T, d, dtype=dt, device=dev),
             "ln2": torch.empty(T, d, dtype=dt, device=dev), "stats2": torch.empty(2, T, dtype=torch.float32, device=dev),
             "ff": torch.empty(T, dff, dtype=dt, device=dev),
@@ -146,11 +163,14 @@ class GPTBlockFunction(torch.autograd.Function):
         work = {
             "d_ff": torch.empty(T, dff, dtype=dt, device=dev), "d_ln2": torch.empty(T, d, dtype=dt, device=dev),
             "d_h1": torch.empty(T, d, dtype=dt, device=dev), "d_ctx": torch.empty(T, hd, dtype=dt, device=dev),
-            "d_probs": torch.empty_like(saved["probs"]), "d_qkv": torch.empty(T, 3 * hd, dtype=dt, device=dev),
+            "d_probs": None if saved["probs"] is None else torch.empty_like(saved["probs"]),
+            "d_qkv": torch.empty(T, 3 * hd, dtype=dt, device=dev),
             "norm_partial": torch.empty(2, nblk, d, dtype=torch.float32, device=dev),
+            "dq_acc": torch.empty(T * hd, dtype=torch.float32, device=dev) if saved["probs"] is None else None,
+            "delta": torch.empty(b * n_heads * s, dtype=torch.float32, device=dev) if saved["probs"] is None else None,
         }
         for name, t in work.items():
-            setattr(g, name, t.data_ptr())
+            setattr(g, name, None if t is None else t.data_ptr())
         g.nblk = nblk
         _native.check(lib.bmt_gpt_block_backward(ctypes.byref(blk), ctypes.byref(g), _native.stream_handle()), "GPT block backward")
         ctx.saved = None

@@ -7,14 +7,25 @@ three-stage software pipeline over fixed-size chunks of every shard:
       -> AVX-512 Adam on a persistent host thread pool
         -> H2D copy of the updated half parameter (copy stream 2)
 
-so PCIe traffic in both directions overlaps the host math.  State-dict layout
-(``state``/``param_groups``/``is_whole``) and the ``gather`` option follow the
-reference, so checkpoints resume bit-identically.
+so PCIe traffic in both directions overlaps the host math.  The pipeline runs on
+a worker thread of the native library (``csrc/runtime.cu``): ``step`` queues the
+work in the order in which the next forward pass needs the parameters and
+returns; whoever gathers a parameter first waits for the batch that updates it
+(``_bmt_pending_update``), so the next step's forward pass runs under the tail of
+this step's optimizer.  When the loss scale of the coming step is known
+(``OptimManager.backward`` announces it), parameters whose gradients are
+complete are already stepped *during backward* into a second set of state
+arrays; ``step`` adopts those results if no overflow was found and nothing else
+changed, and drops them otherwise, so a skipped step leaves the state bit for
+bit as it was.  State-dict layout (``state``/``param_groups``/``is_whole``) and
+the ``gather`` option follow the reference, so checkpoints resume
+bit-identically.
 """
 from __future__ import annotations
 
 import ctypes
 import math
+import weakref
 from collections import defaultdict
 from copy import deepcopy
 from itertools import chain
@@ -26,16 +37,27 @@ from ._distributed import state_dict_gather
 from .adam import _partition_bounds, _zero_grad
 
 _CHUNK = 1 << 23  # elements per pipeline stage (16 MiB of half data)
+_live = weakref.WeakSet()  # optimizers that may have asynchronous batches queued
 
 
-class _OffloadChunk(ctypes.Structure):
-    """Mirror of ``BmtOffloadChunk`` (``csrc/api.h``)."""
+def finish_all_updates() -> None:
+    """Wait for every offloading optimizer's queued batches (``bmt.synchronize`` calls this)."""
+    for opt in list(_live):
+        opt.synchronize()
 
-    _fields_ = [("grad_ready", ctypes.c_void_p), ("p32", ctypes.c_void_p), ("p16_host", ctypes.c_void_p),
-                ("g16_host", ctypes.c_void_p), ("m", ctypes.c_void_p), ("v", ctypes.c_void_p), ("p_dev", ctypes.c_void_p),
+
+class _OffloadJob(ctypes.Structure):
+    """Mirror of ``BmtOffloadJob`` (``csrc/api.h``)."""
+
+    _fields_ = [("grad_ready", ctypes.c_void_p), ("p32", ctypes.c_void_p), ("m", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("p32_out", ctypes.c_void_p), ("m_out", ctypes.c_void_p), ("v_out", ctypes.c_void_p),
+                ("p16_host", ctypes.c_void_p), ("g16_host", ctypes.c_void_p), ("p_dev", ctypes.c_void_p),
                 ("n", ctypes.c_int64), ("beta1", ctypes.c_float), ("beta2", ctypes.c_float), ("eps", ctypes.c_float),
                 ("lr", ctypes.c_float), ("scale", ctypes.c_float), ("wd", ctypes.c_float), ("bc1", ctypes.c_float),
-                ("bc2", ctypes.c_float), ("bf16", ctypes.c_int)]
+                ("bc2", ctypes.c_float), ("bf16", ctypes.c_int), ("upload", ctypes.c_int)]
+
+
+_STATE_KEYS = ("_param_fp32", "exp_avg", "exp_avg_sq")
 
 
 def _pinned(shape, dtype, pin):
@@ -86,7 +108,18 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         self._tune_steps = 0
         self._last_timing = None
         self._d2h = self._h2d = None
+        self._ahead_owners = []  # parameters that own a second set of state arrays
         self._staged = {}  # param -> event of a gradient copy that was started during backward
+        # asynchronous pipeline: tickets of queued batches per parameter, results computed ahead of `step`, and what the
+        # coming step will be called with (announced by OptimManager.backward; None = unknown, nothing is computed ahead)
+        self._async = _os.environ.get("BMT_OFFLOAD_ASYNC", "1") != "0"
+        self._ahead_budget = int(float(_os.environ.get("BMT_OFFLOAD_AHEAD_GB", "4")) * (1 << 30))
+        self._tickets = {}   # param -> [ticket, ...]
+        self._keep = {}      # ticket -> objects whose raw handles the queued batch uses
+        self._ahead = {}     # param -> dict(ticket=, key=hyper-parameters the result was computed with)
+        self._announced_scale = None
+        self.stats = {"ahead_queued": 0, "ahead_adopted": 0, "ahead_requeued": 0, "ahead_dropped": 0}
+        _live.add(self)
         for group in self.param_groups:
             for p in group["params"]:
                 if (p.is_cuda and not self._use_gpu_math(p)   # chunks that may switch engines are staged at step time
@@ -182,7 +215,10 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         cur.wait_stream(math_s)   # later kernels see the updated parameters
 
     def _host_state_ready(self) -> None:
-        """Block until every write-back of the streamed step has reached host memory (before the host reads the state)."""
+        """Block until queued updates and every write-back of the streamed step have reached host memory (before the
+        host reads the state)."""
+        self._drop_ahead()
+        self.synchronize()
         if self._gpu_pipe is not None:
             self._gpu_pipe["down"].synchronize()
 
@@ -219,6 +255,7 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         ``None`` when an earlier staged copy became stale (gradient accumulation)."""
         if work is None:
             self._staged.pop(p, None)
+            self._drop_ahead(p)
             return
         state = self.state.get(p)
         if not state or p.dtype == torch.float32 or p.grad is None:
@@ -236,10 +273,171 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
             ev = torch.cuda.Event()
             ev.record(d2h)
         self._staged[p] = ev
+        self._step_ahead(p, state, ev)
 
     def _invalidate_staged(self) -> None:
-        """Gradients were modified after backward (clipping): copies made during backward are stale."""
+        """Gradients were modified after backward (clipping): copies made during backward, and anything computed from
+        them, are stale."""
+        self._drop_ahead()
         self._staged.clear()
+
+    # ------------------------------------------------------ asynchronous plumbing
+    def _lib(self):
+        from ..ops import _native
+
+        lib = _native.cuda_lib()
+        if not getattr(lib, "_bmt_offload_typed", False):
+            lib.bmt_offload_submit.restype = ctypes.c_int64
+            lib.bmt_offload_submit_uploads.restype = ctypes.c_int64
+            lib.bmt_offload_wait.argtypes = [ctypes.c_int64, ctypes.c_void_p]
+            lib.bmt_offload_poll.argtypes = [ctypes.c_int64]
+            lib.bmt_offload_cancel.argtypes = [ctypes.c_int64]
+            lib._bmt_offload_typed = True
+        return lib
+
+    def _pending_update(self, p, block: bool) -> bool:
+        """Hook installed on a parameter while batches that rewrite it are queued.  ``block`` false: only report whether
+        they are done.  Otherwise wait for them and make the current stream wait for their uploads; returns True."""
+        tickets = self._tickets.get(p)
+        if tickets:
+            lib = self._lib()
+            if not block and not all(lib.bmt_offload_poll(t) for t in tickets):
+                return False
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            for t in tickets:
+                rc = lib.bmt_offload_wait(t, stream)
+                self._keep.pop(t, None)
+                if rc != 0:
+                    raise RuntimeError(f"offloaded Adam batch failed (stage {rc >> 16}, CUDA error {rc & 0xffff})")
+            del self._tickets[p]
+        if getattr(p, "_bmt_pending_update", None) is not None:
+            p._bmt_pending_update = None
+        return True
+
+    def _track(self, p, ticket: int, keep=None) -> None:
+        """Remember a queued batch of ``p``.  ``keep``: objects the worker uses by raw handle (the events guarding the
+        gradient copies); they must outlive the batch, so they are held until it has been waited for."""
+        if ticket <= 0:
+            raise RuntimeError(f"could not queue an offloaded Adam batch (code {ticket})")
+        self._tickets.setdefault(p, []).append(ticket)
+        if keep:
+            self._keep[ticket] = keep
+        p._bmt_pending_update = lambda block=True, p=p: self._pending_update(p, block)
+
+    def synchronize(self) -> None:
+        """Block until every queued update has been applied and uploaded (host state and device parameters final)."""
+        for p in list(self._tickets):
+            self._pending_update(p, True)
+        if self._h2d is not None:
+            self._h2d.synchronize()
+
+    def _hyper(self, p, state, group, scale):
+        """Everything a result computed ahead of ``step`` depends on besides the gradient and the old state."""
+        step = state["step"] + 1
+        lr = 0.0 if step < self._hold_steps else group["lr"]
+        return (float(scale), step, float(lr), tuple(group["betas"]), float(group["eps"]), float(group["weight_decay"]),
+                bool(group.get("maximize", False)))
+
+    def _jobs_for(self, p, state, group, scale, step, pieces, out_state=None, upload=True):
+        """ctypes job array for the ranges ``pieces`` = [(lo, hi, event)] of one half-precision device parameter."""
+        arr = (_OffloadJob * len(pieces))()
+        beta1, beta2 = group["betas"]
+        out_state = out_state if out_state is not None else state
+        for c, (lo, hi, ev) in zip(arr, pieces):
+            c.grad_ready = ev.cuda_event if ev is not None else None
+            for dst, key in (("p32", "_param_fp32"), ("m", "exp_avg"), ("v", "exp_avg_sq")):
+                setattr(c, dst, state[key].data_ptr() + lo * 4)
+                setattr(c, dst + "_out", out_state[key].data_ptr() + lo * 4)
+            c.p16_host = state["_param_fp16"].data_ptr() + lo * 2
+            c.g16_host = state["_grad_fp16"].data_ptr() + lo * 2
+            c.p_dev = p.data.data_ptr() + lo * 2
+            c.n = hi - lo
+            c.beta1, c.beta2, c.eps = beta1, beta2, group["eps"]
+            c.lr = 0.0 if step < self._hold_steps else group["lr"]
+            c.scale, c.wd = scale, group["weight_decay"]
+            c.bc1, c.bc2 = 1.0 - math.pow(beta1, step), 1.0 - math.pow(beta2, step)
+            c.bf16 = 1 if p.dtype == torch.bfloat16 else 0
+            c.upload = 1 if upload else 0
+        return arr
+
+    def _cpu_fn(self):
+        from ..ops import _native
+
+        cpu_lib = _native.cpu_lib()
+        return None if cpu_lib is None else ctypes.cast(cpu_lib.bmt_adam_cpu_ex, ctypes.c_void_p)
+
+    # ------------------------------------------------ stepping ahead, during backward
+    def _expect_step(self, scale) -> None:
+        """The coming ``step`` will be called with this loss scale (``OptimManager.backward``)."""
+        self._announced_scale = scale
+
+    def _step_ahead(self, p, state, event) -> None:
+        """Queue the update of ``p`` now, into a second set of state arrays, from the gradient copy ``event`` guards."""
+        if (not self._async or self._announced_scale is None or self._math != "cpu" or self.record_delta
+                or p in self._ahead or p.dtype == torch.float32):
+            return
+        fn = self._cpu_fn()
+        if fn is None:
+            return
+        group = next(g for g in self.param_groups if any(q is p for q in g["params"]))
+        if group.get("maximize", False):
+            return
+        need = 3 * 4 * p.numel()
+        if "_ahead_state" not in state:
+            used = sum(3 * 4 * q.numel() for q in self._ahead_owners)
+            if used + need > self._ahead_budget:
+                return
+            state["_ahead_state"] = {k: torch.empty_like(state[k], pin_memory=False) for k in _STATE_KEYS}
+            self._ahead_owners.append(p)
+        key = self._hyper(p, state, group, self._announced_scale)
+        n = p.numel()
+        pieces = [(lo, min(n, lo + _CHUNK), event if lo == 0 else None) for lo in range(0, n, _CHUNK)]
+        jobs = self._jobs_for(p, state, group, key[0], key[1], pieces, out_state=state["_ahead_state"], upload=False)
+        _, h2d = self._streams()
+        ticket = self._lib().bmt_offload_submit(jobs, ctypes.c_int(len(pieces)), fn, ctypes.c_void_p(h2d.cuda_stream))
+        if ticket > 0:
+            self._ahead[p] = dict(ticket=ticket, key=key, event=event)
+            self.stats["ahead_queued"] += 1
+
+    def _drop_ahead(self, p=None) -> None:
+        """Forget results computed ahead (all, or those of ``p``); a batch that is running is waited for first."""
+        lib = None
+        for q in ([p] if p is not None else list(self._ahead)):
+            rec = self._ahead.pop(q, None)
+            if rec is None:
+                continue
+            lib = lib or self._lib()
+            self.stats["ahead_dropped"] += 1
+            if not lib.bmt_offload_cancel(rec["ticket"]):
+                lib.bmt_offload_wait(rec["ticket"], None)
+
+    def _adopt_ahead(self, p, state, group, scale) -> bool:
+        """Make the result computed ahead for ``p`` the current state if it was computed with exactly the arguments this
+        step has, and queue its upload.  False: there is none (or it was dropped) and ``p`` has to be stepped now."""
+        rec = self._ahead.pop(p, None)
+        if rec is None:
+            return False
+        lib = self._lib()
+        if lib.bmt_offload_cancel(rec["ticket"]):
+            self.stats["ahead_requeued"] += 1
+            return False          # it had not been started: it takes its turn in forward order instead
+        if rec["key"] != self._hyper(p, state, group, scale):
+            self.stats["ahead_dropped"] += 1
+            lib.bmt_offload_wait(rec["ticket"], None)
+            return False
+        rc = lib.bmt_offload_wait(rec["ticket"], None)
+        if rc != 0:
+            raise RuntimeError(f"offloaded Adam batch failed (stage {rc >> 16}, CUDA error {rc & 0xffff})")
+        other = state["_ahead_state"]
+        for k in _STATE_KEYS:
+            state[k], other[k] = other[k], state[k]
+        state["step"] += 1
+        self.stats["ahead_adopted"] += 1
+        n = p.numel()
+        jobs = self._jobs_for(p, state, group, scale, state["step"], [(0, n, None)])
+        _, h2d = self._streams()
+        self._track(p, lib.bmt_offload_submit_uploads(jobs, ctypes.c_int(1), ctypes.c_void_p(h2d.cuda_stream)))
+        return True
 
     # ------------------------------------------------------------------- step
     @torch.no_grad()
@@ -247,6 +445,8 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         from ..block_layer import params_changed
 
         params_changed()
+        self.synchronize()   # batches of the previous step (long finished in a training loop)
+        self._announced_scale = None
         loss = None
         if closure is not None:
             with torch.enable_grad():
@@ -268,6 +468,8 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
                 if len(state) == 0:
                     state = self._init_state(p)
                 n = p.numel()
+                if p in self._ahead and self._adopt_ahead(p, state, group, scale):
+                    continue
                 if self._use_gpu_math(p) and n > 0:
                     for lo in range(0, n, _CHUNK):
                         gpu_items.append((p, state, group, lo, min(n, lo + _CHUNK)))
@@ -330,6 +532,7 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
 
         if on_gpu and not self.record_delta:
             work = self._run_native(work, stepped, scale, h2d)
+        rest_uploads = any(p.is_cuda for p, *_ in work)
 
         sum_delta = sum_sq_delta = 0.0
         total_numel = 0
@@ -387,7 +590,11 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
                     p.data.view(-1)[lo:hi].copy_(out_half, non_blocking=True)
             else:
                 p.data.view(-1)[lo:hi].copy_(out_half)
-        if on_gpu:
+        self._drop_ahead()   # leftovers (parameters that had no gradient this time)
+        if on_gpu and not self._async:
+            self.synchronize()
+            torch.cuda.current_stream().wait_stream(h2d)
+        elif on_gpu and rest_uploads:
             torch.cuda.current_stream().wait_stream(h2d)
         pend = getattr(self, "_pending_timing", None)
         if pend is not None and pend[0] is not None:
@@ -400,47 +607,27 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         return loss
 
     def _run_native(self, work, stepped, scale, h2d):
-        """Hand the half-precision device parameters' chunks to the native chunk loop (event wait -> host Adam -> upload,
-        ``csrc/runtime.cu``) in one call; returns the work items it does not cover (fp32 parameters, host tensors)."""
-        from ..ops import _native
-
-        cuda_lib, cpu_lib = _native.cuda_lib(), _native.cpu_lib()
-        if cpu_lib is None:
+        """Queue the half-precision device parameters' chunks on the native worker (event wait -> host Adam -> upload,
+        ``csrc/runtime.cu``), one batch per parameter in the order given (= the order in which a forward pass uses
+        them); returns the work items it does not cover (fp32 parameters, host tensors)."""
+        fn = self._cpu_fn()
+        if fn is None:
             return work
-        rest, fast = [], []
+        rest, per_param = [], {}
         for item in work:
             p, state, group, lo, hi, ev = item
             if p.is_cuda and p.dtype in (torch.float16, torch.bfloat16) and not group.get("maximize", False) and hi > lo:
-                fast.append(item)
+                per_param.setdefault(p, (state, group, []))[2].append((lo, hi, ev))
             else:
                 rest.append(item)
-        if not fast:
-            return work
-        arr = (_OffloadChunk * len(fast))()
-        es = 2
-        for c, (p, state, group, lo, hi, ev) in zip(arr, fast):
+        lib = self._lib()
+        for p, (state, group, pieces) in per_param.items():
             if id(p) not in stepped:
                 stepped.add(id(p))
                 state["step"] += 1
-            step = state["step"]
-            beta1, beta2 = group["betas"]
-            c.grad_ready = ev.cuda_event if ev is not None else None
-            c.p32 = state["_param_fp32"].data_ptr() + lo * 4
-            c.p16_host = state["_param_fp16"].data_ptr() + lo * es
-            c.g16_host = state["_grad_fp16"].data_ptr() + lo * es
-            c.m = state["exp_avg"].data_ptr() + lo * 4
-            c.v = state["exp_avg_sq"].data_ptr() + lo * 4
-            c.p_dev = p.data.data_ptr() + lo * es
-            c.n = hi - lo
-            c.beta1, c.beta2, c.eps = beta1, beta2, group["eps"]
-            c.lr = 0.0 if step < self._hold_steps else group["lr"]
-            c.scale, c.wd = scale, group["weight_decay"]
-            c.bc1, c.bc2 = 1.0 - math.pow(beta1, step), 1.0 - math.pow(beta2, step)
-            c.bf16 = 1 if p.dtype == torch.bfloat16 else 0
-        fn16 = ctypes.cast(cpu_lib.bmt_adam_cpu_fp16, ctypes.c_void_p)
-        fnbf = ctypes.cast(cpu_lib.bmt_adam_cpu_bf16, ctypes.c_void_p)
-        _native.check(cuda_lib.bmt_offload_adam_run(arr, ctypes.c_int(len(fast)), fn16, fnbf, ctypes.c_void_p(h2d.cuda_stream)),
-                      "offloaded Adam chunk loop")
+            jobs = self._jobs_for(p, state, group, scale, state["step"], pieces)
+            self._track(p, lib.bmt_offload_submit(jobs, ctypes.c_int(len(pieces)), fn, ctypes.c_void_p(h2d.cuda_stream)),
+                        keep=[ev for _, _, ev in pieces if ev is not None])
         return rest
 
     def get_avg_delta(self):
@@ -527,6 +714,7 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         self.__setstate__({"state": state, "param_groups": param_groups})
 
     def zero_grad(self, set_to_none: bool = False):
+        self._drop_ahead()   # a skipped step: what was computed from these gradients is not wanted
         if self._staged:
             # a skipped step may leave copies in flight: let them finish before the gradients are overwritten
             for ev in self._staged.values():

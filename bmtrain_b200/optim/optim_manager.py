@@ -156,6 +156,10 @@ class OptimManager:
 
     def backward(self, loss: torch.Tensor):
         """Backward of the scaled loss; returns once all gradient reductions are queued behind it."""
+        for optimizer in self.optimizers:
+            announce = getattr(optimizer, "_expect_step", None)
+            if announce is not None:
+                announce(self.loss_scale)   # lets an offloading optimizer start on finished gradients during backward
         self.scale_loss(loss).backward()
         drain_pending()
 

@@ -211,6 +211,10 @@ def _same_node(comm: Communicator) -> bool:
 
 def peer_runtime(comm: Communicator) -> Optional[PeerRuntime]:
     """The runtime of ``comm``, created on first use (collective); None when peer memory cannot be used."""
+    from ..comm import _LOCAL_ONLY
+
+    if _LOCAL_ONLY[0]:
+        return None   # timing without inter-rank traffic: the peer-memory kernels are part of that traffic
     key = id(comm)
     if key in _runtimes:
         return _runtimes[key]

@@ -136,6 +136,9 @@ class OpAllGather(torch.autograd.Function):
         ctx.comm = value._zero_comm
         ctx.numel = value._original_shape.numel()
         ctx.bounds = (value._start_partition, value._end_partition)
+        hook = getattr(value, "_bmt_pending_update", None)
+        if hook is not None:
+            hook(True)   # an asynchronous optimizer step is still rewriting this shard
         full = gather_flat_shard(value.data, ctx.numel, ctx.comm)
         return full.view(value._original_shape)
 

@@ -9,6 +9,9 @@ def synchronize() -> None:
     """Block the host until every rank reached this point and all queued device work is done."""
     if not config["initialized"]:
         raise RuntimeError("call init_distributed() first")
+    from .optim.adam_offload import finish_all_updates
+
+    finish_all_updates()   # optimizer steps still being applied by the offload worker
     config["comm"].barrier()
     if config["device"].type == "cuda":
         torch.cuda.synchronize()

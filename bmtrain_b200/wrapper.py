@@ -50,7 +50,11 @@ def _shard_tensors(mod: torch.nn.Module) -> None:
 
 def _rebase(mod: torch.nn.Module) -> None:
     cls = mod.__class__
-    mod.__class__ = type("Distributed" + cls.__name__, (cls, DistributedModule), {})
+    if issubclass(DistributedModule, cls):
+        # a bare nn.Module used as a container: DistributedModule already is one
+        mod.__class__ = DistributedModule
+    else:
+        mod.__class__ = type("Distributed" + cls.__name__, (cls, DistributedModule), {})
 
 
 def _as_block_list(entries: torch.nn.ModuleList) -> TransformerBlockList:

@@ -216,6 +216,104 @@ def test_attention(dev, dtype, cfg):
     assert _rel(q.grad.cpu(), qr.grad) < tol and _rel(k.grad.cpu(), kr.grad) < tol and _rel(v.grad.cpu(), vr.grad) < tol
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [
+    # b, sq, sk, h, hk, d, causal, masking
+    (2, 128, 128, 4, 4, 64, True, None), (2, 512, 512, 8, 8, 80, True, None), (1, 300, 300, 8, 2, 128, True, None),
+    (2, 256, 384, 4, 2, 64, True, "lens"), (2, 200, 200, 4, 4, 96, False, "dense"), (3, 100, 260, 2, 1, 32, False, "lens"),
+    (1, 1024, 1024, 4, 4, 128, True, None), (1, 130, 130, 2, 2, 16, False, None)])
+def test_flash_attention_forward(dev, dtype, cfg):
+    """Fused tcgen05 attention forward against the fp32 definition: output and log-sum-exp, strided (packed QKV) inputs,
+    grouped-query heads, causal / key-length / dense masks, ragged tile edges and rows with no visible key."""
+    from bmtrain_b200.ops import attention as AT
+    from bmtrain_b200.ops import _native
+
+    b, sq, sk, h, hk, d, causal, masking = cfg
+    torch.manual_seed(13)
+    g = h // hk
+    # q, k, v as strided views of one packed projection, the way the models produce them
+    packed_q = torch.randn(b, sq, hk, g + 2, d, device=dev, dtype=dtype)
+    packed_kv = packed_q if sk == sq else torch.randn(b, sk, hk, g + 2, d, device=dev, dtype=dtype)
+    q = packed_q[:, :, :, :g].reshape(b, sq, h, d)
+    k, v = packed_kv[:, :, :, g], packed_kv[:, :, :, g + 1]
+    mask = lens = None
+    if masking == "lens":
+        lens = torch.tensor([max(1, sk - 37 * i) for i in range(b)], device=dev, dtype=torch.int32)
+        if b > 2:
+            lens[-1] = 0     # a sample without any visible key: zeros out, -inf log-sum-exp
+    if masking == "dense":
+        mask = torch.rand(b, sq, sk, device=dev) > 0.3
+        mask[:, 5] = False   # a fully masked row
+    assert AT.flash_usable(q, k, v)
+    m8, l32 = AT._softmax_args(mask, lens)
+    scale = 1.0 / math.sqrt(d)
+    out, lse = AT.flash_forward(q, k, v, scale, causal, m8, l32)
+    torch.cuda.synchronize()
+    assert _native.cuda_lib().bmt_attn_status() == 0
+    ref = AT._reference_attention(q.float().cpu(), k.float().cpu(), v.float().cpu(), scale, causal,
+                                  None if mask is None else mask.cpu(), None if lens is None else lens.cpu())
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    assert torch.isfinite(out).all()
+    assert _rel(out.float().cpu(), ref.float()) < tol
+    # log-sum-exp against the definition
+    kk = k.float().cpu().repeat_interleave(g, dim=2)
+    sc = torch.einsum("bqhd,bkhd->bhqk", q.float().cpu(), kk) * scale
+    keep = torch.ones(b, 1, sq, sk, dtype=torch.bool)
+    if causal:
+        keep = keep & torch.ones(sq, sk, dtype=torch.bool).tril(sk - sq)
+    if mask is not None:
+        keep = keep & mask.cpu().view(b, 1, sq, sk)
+    if lens is not None:
+        keep = keep & (torch.arange(sk)[None, None, None, :] < lens.cpu().view(b, 1, 1, 1))
+    want = torch.logsumexp(sc.masked_fill(~keep, float("-inf")), dim=-1)
+    got = lse.cpu()
+    finite = torch.isfinite(want)
+    assert torch.equal(torch.isfinite(got), finite)
+    assert (got[finite] - want[finite]).abs().max().item() < (5e-2 if dtype == torch.bfloat16 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [
+    (2, 128, 128, 4, 4, 64, True, None), (2, 512, 512, 8, 8, 80, True, None), (1, 300, 300, 8, 2, 128, True, None),
+    (2, 256, 384, 4, 2, 64, True, "lens"), (2, 200, 200, 4, 4, 96, False, "dense"), (3, 100, 260, 2, 1, 32, False, "lens"),
+    (1, 640, 640, 2, 2, 128, True, "dense")])
+def test_flash_attention_backward(dev, dtype, cfg):
+    """Fused attention backward (dq, dk, dv) through autograd against the fp32 definition."""
+    from bmtrain_b200.ops import attention as AT
+    from bmtrain_b200.ops import _native
+
+    b, sq, sk, h, hk, d, causal, masking = cfg
+    torch.manual_seed(14)
+    q = torch.randn(b, sq, h, d, device=dev, dtype=dtype, requires_grad=True)
+    k = torch.randn(b, sk, hk, d, device=dev, dtype=dtype, requires_grad=True)
+    v = torch.randn(b, sk, hk, d, device=dev, dtype=dtype, requires_grad=True)
+    mask = lens = None
+    if masking == "lens":
+        lens = torch.tensor([max(1, sk - 37 * i) for i in range(b)], device=dev, dtype=torch.int32)
+        if b > 2:
+            lens[-1] = 0
+    if masking == "dense":
+        mask = torch.rand(b, sq, sk, device=dev) > 0.3
+        if causal:
+            mask = mask & torch.ones(sq, sk, dtype=torch.bool, device=dev).tril(sk - sq)
+        mask[:, 5] = False
+    assert AT.flash_usable(q, k, v)
+    out = AT.attention(q, k, v, causal=causal, mask=mask, kv_lens=lens)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    assert _native.cuda_lib().bmt_attn_status() == 0
+    qr, kr, vr = (t.detach().float().cpu().requires_grad_() for t in (q, k, v))
+    ref = AT._reference_attention(qr, kr, vr, 1.0 / math.sqrt(d), causal, None if mask is None else mask.cpu(),
+                                  None if lens is None else lens.cpu())
+    ref.backward(g.float().cpu())
+    tol = 3e-2 if dtype == torch.bfloat16 else 6e-3
+    assert _rel(out.float().cpu(), ref) < tol
+    for name, got, want in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        assert torch.isfinite(got).all(), name
+        assert _rel(got.float().cpu(), want) < tol, name
+
+
 def test_swiglu_colsum(dev):
     from bmtrain_b200.ops import elementwise as EW, gemm as G
 
