@@ -1,4 +1,5 @@
-"""Headline benchmark: tokens/s of ZeRO-3 training on the reference's example GPT.
+"""Headline benchmark: tokens/s of ZeRO-3 training on the reference's example GPT (and, with ``--config llama13b``, of
+the Llama-13B-shaped ZeRO-3 x tensor-parallel-2 configuration).
 
 Config (the reference's example/train.py model): 8 pre-LN blocks, d_model 2560, 32 heads x 80, FFN 8192, vocab 10240,
 bias, learned positions (512), fp16 with OptimManager dynamic loss scaling (2**20), ZeRO-3 TransformerBlockList,
@@ -9,6 +10,12 @@ random-init weights.  Weak scaling: per-GPU work is fixed as N grows.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
         bench.py --gpus 8 --steps 10 --warmup 3
     python bench.py --impl reference ...      # the unmodified reference from baseline/_ref, same loop
+
+    torchrun ... bench.py --gpus 8 --config llama13b [--layers 40] [--micro-batch 2]   # second named configuration:
+        40 layers, d 5120, 40 heads x 128, SwiGLU 13824, RMSNorm, RoPE, vocab 32000, bf16, seq 4096, global batch 64
+        sequences per step (gradient accumulation over micro-batches), ZeRO-3 x tp 2, AdamOptimizer, vocabulary-parallel
+        fused cross-entropy; the reference arm builds the same decoder from the reference's own layers
+        (baseline/llama_reference.py)
 
 Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events around exactly K steps, inputs already on the
 device, max over ranks); `e2e` repeats the measurement with every step's inputs copied from pinned host memory and
@@ -36,6 +43,10 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="gpt-example", choices=["gpt-example", "llama13b"])
+    ap.add_argument("--layers", type=int, default=0, help="llama13b: number of layers (default 40; fewer = a reduced run, said so in the output)")
+    ap.add_argument("--micro-batch", type=int, default=2, help="llama13b: sequences per micro-batch and data-parallel rank")
+    ap.add_argument("--global-batch", type=int, default=64, help="llama13b: sequences per optimizer step over the whole job")
     ap.add_argument("--optimizer", default="offload", choices=["offload", "adam"],
                     help="offload = AdamOffloadOptimizer (the headline config); adam = AdamOptimizer with the state in HBM "
                          "(a secondary measurement: the step is then bound by the GPU, not by host memory)")
@@ -200,6 +211,126 @@ def build_reference(opt_kind="offload"):
     return bmt, model, om, loss_of, (lambda: 0)
 
 
+LLAMA = dict(vocab_size=32000, dim_model=5120, num_heads=40, dim_ff=13824)
+LLAMA_SEQ = 4096
+
+
+def run_llama(args, emit):
+    """``--config llama13b``: one optimizer step = global batch of sequences, accumulated over micro-batches."""
+    import torch
+
+    layers = args.layers or 40
+    tp = 2
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import bmtrain as bmt
+        from llama_reference import RefLlama
+
+        bmt.init_distributed(seed=0, tp_size=tp)
+        model = RefLlama(layers, dtype=torch.bfloat16, **LLAMA)
+        launch_count = lambda: 0
+        finish_updates = lambda: None
+    else:
+        import bmtrain_b200 as bmt
+
+        bmt.init_distributed(seed=0, tp_size=tp)
+        model = bmt.models.Llama(layers, dtype=torch.bfloat16, **LLAMA)
+        from bmtrain_b200.ops import _native
+        import ctypes
+
+        lib = _native.cuda_lib()
+        lib.bmt_launch_count.restype = ctypes.c_int64
+        launch_count = lib.bmt_launch_count
+        finish_updates = bmt.optim.adam_offload.finish_all_updates
+    bmt.init_parameters(model)
+    loss_func = bmt.loss.FusedCrossEntropy(ignore_index=-100, parallel=True)
+    optimizer = bmt.optim.AdamOptimizer(model.parameters(), lr=1e-4, weight_decay=1e-2)
+    om = bmt.optim.OptimManager(loss_scale=None)
+    om.add_optimizer(optimizer)
+    rank, world = bmt.rank(), bmt.world_size()
+    if world % tp:
+        raise SystemExit("llama13b needs an even number of GPUs (tp = 2)")
+    dp = world // tp
+    dp_rank = rank // tp
+    per_rank = args.global_batch // dp
+    mb = args.micro_batch
+    micro_steps = per_rank // mb
+    if micro_steps * mb * dp != args.global_batch:
+        raise SystemExit("global batch must be a multiple of dp x micro-batch")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator().manual_seed(2000 + dp_rank)   # the two ranks of a tensor-parallel pair see the same sequences
+    host = [torch.randint(0, LLAMA["vocab_size"], (mb, LLAMA_SEQ + 1), generator=gen).pin_memory() for _ in range(4)]
+    on_dev = [h.to(dev) for h in host]
+
+    def step(batches, e2e):
+        om.zero_grad()
+        total = None
+        for i in range(micro_steps):
+            ids = batches[i % len(batches)]
+            if e2e:
+                ids = ids.to(dev, non_blocking=True)
+            logits = model(ids[:, :-1].contiguous())                      # (s, b, vocab / tp)
+            target = ids[:, 1:].t().contiguous().view(-1)
+            loss = loss_func(logits.reshape(-1, logits.shape[-1]), target) / micro_steps
+            om.backward(loss)
+            total = loss.detach() if total is None else total + loss.detach()
+        om.step()
+        return float(total) if e2e else total
+
+    for _ in range(max(args.warmup, 1)):
+        step(on_dev, False)
+
+    def timed(e2e):
+        finish_updates()
+        bmt.synchronize()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+        l0 = launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        last = None
+        for _ in range(args.steps):
+            last = step(host if e2e else on_dev, e2e)
+        finish_updates()
+        end.record()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) * 1e3
+        bmt.synchronize()
+        t = torch.tensor([max(start.elapsed_time(end), wall) if e2e else start.elapsed_time(end), float(last)], device=dev)
+        t = bmt.distributed.all_reduce(t, "max")
+        return float(t[0]), float(t[1]), launch_count() - l0, sampler.stop() if sampler else None
+
+    ms, _, launches, clocks = timed(False)
+    ms_e2e, final_loss, _, _ = timed(True)
+    tokens = args.global_batch * LLAMA_SEQ * args.steps
+    value = tokens / (ms / 1e3)
+    n_params = layers * (4 * 5120 * 5120 + 3 * 5120 * 13824) + 2 * 32000 * 5120
+    if rank == 0:
+        emit({
+            "metric": "tokens/sec/box (device-timed, max over ranks)", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights", "impl": args.impl,
+            "config": {"model": f"Llama-13B-shaped decoder, {layers} layers" + ("" if layers == 40 else " (REDUCED from 40)")
+                                + ", d 5120, 40 heads x 128, SwiGLU 13824, RMSNorm, RoPE, vocab 32000",
+                       "global_batch": args.global_batch, "seq_len": LLAMA_SEQ, "micro_batch": mb, "micro_steps": micro_steps,
+                       "parallelism": f"zero3 x tp{tp} (dp {dp})", "optimizer": "AdamOptimizer (state in HBM), no loss scaling",
+                       "loss": "FusedCrossEntropy(parallel=True)", "activation_checkpointing": True,
+                       "l2": "inputs larger than L2: every step streams tens of GB of weights and activations"},
+            "clocks": clocks,
+            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": micro_steps * mb * (LLAMA_SEQ + 1) * 8,
+                    "d2h_bytes_per_step": 4, "timing": "max(CUDA events, wall clock), inputs from pinned host memory, loss read back"},
+            "gpu_launches": launches, "final_loss": round(final_loss, 4),
+            "model_tflops_per_gpu": 6.0 * n_params * tokens / (ms / 1e3) / world / 1e12,
+        })
+    try:
+        if torch.distributed.is_initialized():
+            torch.distributed.destroy_process_group()
+    except Exception:
+        pass
+
+
 def main():
     args = parse()
     setup_env(args)
@@ -220,6 +351,17 @@ def main():
 
     if not torch.cuda.is_available():
         emit({"impl": args.impl, "unavailable": "no CUDA device"})
+        return
+    if args.config == "llama13b":
+        try:
+            run_llama(args, emit)
+        except Exception as exc:
+            if args.impl != "reference":
+                raise
+            import traceback
+
+            traceback.print_exc()
+            emit({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"})
         return
     try:
         bmt, model, om, loss_of, launch_count = (build_reference if args.impl == "reference" else build_ours)(args.optimizer)

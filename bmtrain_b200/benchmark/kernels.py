@@ -3,6 +3,7 @@
     python -m bmtrain_b200.benchmark.kernels --op gemm --m 8192 --n 8192 --k 8192 --dtype bf16 --layout nt
     python -m bmtrain_b200.benchmark.kernels --op adam --n 268435456
     python -m bmtrain_b200.benchmark.kernels --op norm|ce|softmax ...
+    python -m bmtrain_b200.benchmark.kernels --op attention --batch 2 --seq 4096 --heads 20 --kv-heads 20 --head-dim 128
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, a >L2 buffer is rewritten between timed launches
 (``--flush``, default on) so every launch starts with a cold L2.  Peaks come from ``MEASURED_PEAKS.json`` at the
@@ -48,7 +49,14 @@ def time_it(fn, iters: int, flush: bool) -> float:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "adam", "norm", "ce", "softmax"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "adam", "norm", "ce", "softmax", "attention"])
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=20)
+    ap.add_argument("--kv-heads", type=int, default=0)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--no-causal", action="store_true")
+    ap.add_argument("--fwd-only", action="store_true", help="attention: time the fused forward kernel alone (for ncu captures)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -97,6 +105,43 @@ def main():
         nbytes = 2 * x.numel() * 2
         print(json.dumps({"op": "layernorm_fwd", "rows": args.m, "d": args.n, "ms": ms, "gbs": nbytes / ms / 1e6,
                           "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_source": src}))
+    elif args.op == "attention":
+        # fused tcgen05 attention against the two-GEMM + softmax form on the same strided (packed projection) operands;
+        # FLOPs: 4 s^2 d per head forward (halved under a causal mask), 2.5 x that backward
+        from bmtrain_b200.ops import attention as AT
+
+        b, s_, h, d = args.batch, args.seq, args.heads, args.head_dim
+        hk = args.kv_heads or h
+        g = h // hk
+        causal = not args.no_causal
+        packed = torch.randn(b, s_, hk, g + 2, d, device=dev, dtype=dt) * 0.5
+        q = packed[:, :, :, :g].reshape(b, s_, h, d).requires_grad_()
+        k = packed[:, :, :, g].clone().requires_grad_()
+        v = packed[:, :, :, g + 1].clone().requires_grad_()
+        flops_f = 4.0 * b * h * s_ * s_ * d * (0.5 if causal else 1.0)
+        go = torch.randn(b, s_, h, d, device=dev, dtype=dt)
+        res = {"op": "attention", "batch": b, "seq": s_, "heads": h, "kv_heads": hk, "head_dim": d, "causal": causal,
+               "dtype": args.dtype, "peak_source": src}
+        modes = (("fused", "1"),) if args.fwd_only else (("fused", "1"), ("two_gemm", "0"))
+        for name, flag in modes:
+            os.environ["BMT_FLASH_ATTN"] = flag
+            fwd = lambda: AT.attention(q, k, v, causal=causal)
+            with torch.no_grad():
+                ms_f = time_it(fwd, args.iters, flush)
+            res[name + "_fwd_ms"] = ms_f
+            res[name + "_fwd_tflops"] = flops_f / ms_f / 1e9
+            if args.fwd_only:
+                continue
+
+            def both():
+                q.grad = k.grad = v.grad = None
+                AT.attention(q, k, v, causal=causal).backward(go)
+
+            ms_fb = time_it(both, args.iters, flush)
+            res[name + "_fwd_bwd_ms"] = ms_fb
+            res[name + "_fwd_bwd_tflops"] = 3.5 * flops_f / ms_fb / 1e9
+        res["fused_fwd_frac_of_peak"] = res["fused_fwd_tflops"] / tflops
+        print(json.dumps(res))
     elif args.op == "ce":
         x = torch.randn(args.m, args.n, device=dev, dtype=dt)
         t = torch.randint(0, args.n, (args.m,), device=dev)

@@ -163,6 +163,15 @@ int bmt_gemm_reduce_scatter(const BmtGemmDesc* desc, int world, int rank, void* 
                             unsigned int epoch, void* const* inbox_slots, const void* inbox_local, int64_t rows_per_rank,
                             void* counter_u32, void* out, const void* bias, void* status_i32, double timeout_s, void* stream);
 int bmt_gemm_rs_grid(int64_t m, int64_t n, int64_t k, int b_major);
+// The same operator as three launches, for jobs in which other kernels that wait for other ranks (ZeRO gathers and
+// reductions) run next to the tensor-parallel ones: (1) the GEMM that delivers every row to its owner and publishes
+// "delivered", none of whose CTAs waits for another rank's result or for its own grid; (2) a one-CTA wait on
+// (done_row, epoch), e.g. bmt_symm_signal_wait; (3) the sum over the inbox slots (+ bias).
+int bmt_gemm_reduce_scatter_main(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, int done_row,
+                                 unsigned int epoch, void* const* inbox_slots, const void* inbox_local, int64_t rows_per_rank,
+                                 void* counter_u32, void* status_i32, double timeout_s, void* stream);
+int bmt_gemm_rs_reduce(const void* inbox_local, int64_t rows_per_rank, int64_t n, int world, int rank, void* const* flags,
+                       int free_row, unsigned int epoch, void* counter_u32, void* out, const void* bias, int dtype, void* stream);
 int bmt_all_gather_gemm(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, unsigned int epoch,
                         const void* src, int64_t ld_src, int64_t rows, void* const* gathered, void* const* counters,
                         int comm_ctas, int skip_local, void* status_i32, double timeout_s, void* stream);

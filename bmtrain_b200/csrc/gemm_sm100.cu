@@ -332,7 +332,7 @@ __device__ __forceinline__ void umma_commit_2cta(uint64_t* bar) {
 //         the row (own rank: local memory, other ranks: P2P stores).  When all CTAs of this rank are done, the last one
 //         publishes "rank r delivered" to every peer; each CTA then waits (bounded) for all ranks and sums the inbox
 //         slots of its share of the local rows (+ bias) into the output.
-// mode 2, all-gather -> GEMM: the last `ag_ctas` CTAs do no math; they push this rank's rows of A into the gathered
+// mode 2, all-gather -> GEMM: the first `ag_ctas` CTAs do no math; they push this rank's rows of A into the gathered
 //         buffer of every rank (own first) in pieces and bump a per-128-row-block counter on the destination.  The
 //         TMA producers of the compute CTAs visit local row blocks first and wait (bounded) on the counter of a block
 //         before loading it, so the transfer overlaps the math block by block.
@@ -352,6 +352,9 @@ struct FusedComm {
     int64_t rs_rows;          // rows per rank
     unsigned int* rs_counter; // local, monotonic: [0] epilogue warps that finished the tiles with rows of other ranks (early
                               // mode) or CTAs that finished all tiles; [1] early mode: CTAs that finished all tiles
+    int rs_split;             // the kernel ends after publishing "delivered": waiting for the other ranks and summing the inbox
+                              // are left to later launches (a one-CTA wait kernel and rs_reduce_kernel), so that no CTA of this
+                              // grid holds an SM while it waits for another rank or for the rest of its own grid
     int rs_early;             // tiles with other ranks' rows come first and "delivered" is published when they are done
     int rs_bpr;               // early mode: tile rows per rank
     int64_t rs_remote_tiles;  // early mode: number of tiles (in raster order) that hold rows of other ranks
@@ -499,9 +502,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int k_blocks = (int)((p.K + BK - 1) / BK);
     const int64_t tiles_per_batch = (int64_t)p.m_blocks * p.n_blocks;   // m_blocks counts (BM * NCTA)-row tiles
     const int64_t num_tiles = tiles_per_batch * p.batch_inner * p.batch_outer;
-    const int compute_ctas = (FUSED == 2 || FUSED == 3) ? (int)gridDim.x - f.ag_ctas : (int)gridDim.x;
-    const bool comm_cta = (FUSED == 2 || FUSED == 3) && (int)blockIdx.x >= compute_ctas;
-    const int64_t first_tile = comm_cta ? num_tiles : blockIdx.x / NCTA, tile_step = compute_ctas / NCTA;
+    // The pusher CTAs are the first CTAs of the grid: CTAs are handed to SMs in index order, so when another kernel keeps
+    // part of the GPU busy it is compute CTAs that wait for an SM, never the CTAs the other ranks depend on.
+    const int comm_first = (FUSED == 2 || FUSED == 3) ? f.ag_ctas : 0;
+    const int compute_ctas = (int)gridDim.x - comm_first;
+    const bool comm_cta = (int)blockIdx.x < comm_first;
+    const int64_t first_tile = comm_cta ? num_tiles : ((int)blockIdx.x - comm_first) / NCTA, tile_step = compute_ctas / NCTA;
     const int blocks_per_rank = FUSED == 2 ? (int)(f.ag_rows / (BM * NCTA)) : 0;   // in tile rows (256 rows for a CTA pair)
     const int row_blocks_per_rank = FUSED == 2 ? (int)(f.ag_rows / BM) : 1;          // in 128-row blocks (counter granularity)
     const uint32_t tmem_cols = 2 * p.bn <= 32 ? 32 : 2 * p.bn <= 64 ? 64 : 2 * p.bn <= 128 ? 128 : 2 * p.bn <= 256 ? 256 : 512;
@@ -534,7 +540,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         __shared__ PushMeta push_meta;
         PushPipe pipe;
         pipe.init(smem_u32(smem), smem_u32(&hdr->full[0]), &push_meta);
-        const int n_pushers = f.ag_ctas, me = (int)blockIdx.x - compute_ctas;
+        const int n_pushers = f.ag_ctas, me = (int)blockIdx.x;
         bool ok = true;
         unsigned int free_seen = 1u << f.rank;   // destinations whose "free for this epoch" flag has been observed
         auto dst_free = [&](int dst) -> bool {
@@ -893,19 +899,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     __threadfence_system();
                     for (int j = 0; j < f.world; ++j) st_release_sys_u32(f.flags[j] + f.done_row * f.world + f.rank, f.epoch);
                 }
-            } else {
+            } else if (!f.rs_split) {
                 // "delivered" went out when the other ranks' tiles were done; the tiles with own rows only have to be complete
                 // on this GPU: count the CTA and wait (bounded) for the rest of the grid, all of which is resident
                 __threadfence();
                 atomicAdd(f.rs_counter + 1, 1u);
                 ok = wait_counter(f.rs_counter + 1, f.epoch * gridDim.x, f.limit_ns);
             }
-            const uint64_t tw0 = global_ns();
-            for (int j = 0; j < f.world && ok; ++j) ok = wait_counter(f.flags[f.rank] + f.done_row * f.world + j, f.epoch, f.limit_ns);
-            atomicMax(&g_fused_stats[5], (unsigned long long)(global_ns() - tw0));
-            atomicAdd(&g_fused_stats[7], (unsigned long long)(global_ns() - tw0));
-            if (!ok) { atomicCAS(f.status, 0, 0x600 | f.rank); atomicCAS(&g_gemm_status, 0, (8 << 16) | (blockIdx.x & 0xffff)); }
-            rs_ok = ok ? 1 : 0;
+            if (!f.rs_split) {
+                const uint64_t tw0 = global_ns();
+                for (int j = 0; j < f.world && ok; ++j) ok = wait_counter(f.flags[f.rank] + f.done_row * f.world + j, f.epoch, f.limit_ns);
+                atomicMax(&g_fused_stats[5], (unsigned long long)(global_ns() - tw0));
+                atomicAdd(&g_fused_stats[7], (unsigned long long)(global_ns() - tw0));
+                if (!ok) { atomicCAS(f.status, 0, 0x600 | f.rank); atomicCAS(&g_gemm_status, 0, (8 << 16) | (blockIdx.x & 0xffff)); }
+            }
+            rs_ok = (ok && !f.rs_split) ? 1 : 0;
         }
         __syncthreads();
         if (rs_ok) {
@@ -914,6 +922,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             if (p.c_dtype == BMT_DT_F16) rs_reduce_all<__half>(f.rs_inbox_local, slot_elems, f.world, f.rs_bias, p.N, f.rs_out, nvec);
             else rs_reduce_all<__nv_bfloat16>(f.rs_inbox_local, slot_elems, f.world, f.rs_bias, p.N, f.rs_out, nvec);
             if (threadIdx.x == 0) atomicMax(&g_fused_stats[6], (unsigned long long)(global_ns() - t_kernel0));
+        }
+    }
+}
+
+// Second half of a split GEMM -> reduce-scatter: sums the inbox slots (+ bias) of this rank's rows once every rank's
+// "delivered" flag has been seen by the wait kernel launched before it.  The last CTA tells every rank that this
+// rank's inbox may be overwritten by the next use of the ring slot.
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS) rs_reduce_kernel(const void* inbox, int64_t slot_elems, int world, const void* bias, int64_t N,
+                                                                 void* out, int64_t nvec, FusedComm f, unsigned int next_epoch) {
+    rs_reduce_all<T>(inbox, slot_elems, world, bias, N, out, nvec);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(f.rs_counter + 1, 1u) + 1u;
+        if (done == f.epoch * gridDim.x) {
+            for (int j = 0; j < f.world; ++j) st_release_sys_u32(f.flags[j] + f.free_row * f.world + f.rank, next_epoch);
         }
     }
 }
@@ -1218,14 +1243,59 @@ extern "C" int bmt_gemm_batched(int64_t m, int64_t n, int64_t k, const void* a, 
 
 // GEMM -> reduce-scatter over the rows of C (see FusedComm mode 1).  `inbox_slots[j]`: where this rank's slot starts in rank
 // j's inbox; `grid_hint` receives the number of CTAs launched (the caller's counter advances by it per call).
+// Reduce phase of a split GEMM -> reduce-scatter (bmt_gemm_reduce_scatter_main): to be launched after a wait kernel has
+// seen every rank's "delivered" flag for `epoch`.  `counter_u32`: the same two counters the main kernel was given.
+extern "C" int bmt_gemm_rs_reduce(const void* inbox_local, int64_t rows_per_rank, int64_t n, int world, int rank, void* const* flags,
+                                  int free_row, unsigned int epoch, void* counter_u32, void* out, const void* bias, int dtype,
+                                  void* stream) {
+    if (world < 2 || world > 8 || n % 8 != 0) return -40;
+    FusedComm f;
+    memset(&f, 0, sizeof(f));
+    f.world = world; f.rank = rank; f.free_row = free_row; f.epoch = epoch; f.rs_counter = (unsigned int*)counter_u32;
+    for (int j = 0; j < world; ++j) f.flags[j] = (unsigned int*)flags[j];
+    const int64_t nvec = rows_per_rank * n / 8, slot_elems = rows_per_rank * n;
+    int64_t blocks = (nvec + NUM_THREADS * 4 - 1) / (NUM_THREADS * 4);
+    if (blocks > 148) blocks = 148;
+    if (blocks < 1) blocks = 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == BMT_DT_F16) rs_reduce_kernel<__half><<<(unsigned)blocks, NUM_THREADS, 0, st>>>(inbox_local, slot_elems, world, bias, n, out, nvec, f, epoch + 1);
+    else rs_reduce_kernel<__nv_bfloat16><<<(unsigned)blocks, NUM_THREADS, 0, st>>>(inbox_local, slot_elems, world, bias, n, out, nvec, f, epoch + 1);
+    bmt_count_launch(1);
+    return (int)cudaGetLastError();
+}
+
+static int gemm_reduce_scatter_impl(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, int done_row,
+                                    unsigned int epoch, void* const* inbox_slots, const void* inbox_local, int64_t rows_per_rank,
+                                    void* counter_u32, void* out, const void* bias, void* status_i32, double timeout_s,
+                                    void* stream, int split);
+
+// First half of a split GEMM -> reduce-scatter: the GEMM whose epilogue delivers every row to its owner's inbox and which
+// publishes "delivered" when done.  No CTA waits for another rank's result or for its own grid.  Follow it with a wait
+// on (done_row, epoch) and bmt_gemm_rs_reduce.
+extern "C" int bmt_gemm_reduce_scatter_main(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, int done_row,
+                                            unsigned int epoch, void* const* inbox_slots, const void* inbox_local,
+                                            int64_t rows_per_rank, void* counter_u32, void* status_i32, double timeout_s, void* stream) {
+    return gemm_reduce_scatter_impl(desc, world, rank, flags, free_row, done_row, epoch, inbox_slots, inbox_local, rows_per_rank,
+                                    counter_u32, nullptr, nullptr, status_i32, timeout_s, stream, 1);
+}
+
 extern "C" int bmt_gemm_reduce_scatter(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, int done_row,
                                        unsigned int epoch, void* const* inbox_slots, const void* inbox_local, int64_t rows_per_rank,
                                        void* counter_u32, void* out, const void* bias, void* status_i32, double timeout_s,
                                        void* stream) {
+    return gemm_reduce_scatter_impl(desc, world, rank, flags, free_row, done_row, epoch, inbox_slots, inbox_local, rows_per_rank,
+                                    counter_u32, out, bias, status_i32, timeout_s, stream, 0);
+}
+
+static int gemm_reduce_scatter_impl(const BmtGemmDesc* desc, int world, int rank, void* const* flags, int free_row, int done_row,
+                                    unsigned int epoch, void* const* inbox_slots, const void* inbox_local, int64_t rows_per_rank,
+                                    void* counter_u32, void* out, const void* bias, void* status_i32, double timeout_s,
+                                    void* stream, int split) {
     if (world < 2 || world > 8 || desc->m != rows_per_rank * world) return -40;
     if (desc->n % 8 != 0) return -41;
     FusedComm f;
     memset(&f, 0, sizeof(f));
+    f.rs_split = split;
     f.mode = 1; f.world = world; f.rank = rank; f.free_row = free_row; f.done_row = done_row; f.epoch = epoch;
     f.status = (int*)status_i32; f.limit_ns = (uint64_t)(timeout_s * 1e9);
     for (int j = 0; j < world; ++j) { f.flags[j] = (unsigned int*)flags[j]; f.rs_inbox[j] = inbox_slots[j]; }

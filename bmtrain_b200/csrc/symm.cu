@@ -85,19 +85,23 @@ struct RsArgs {
 template <typename T, int WMAX, int U>
 __global__ void __launch_bounds__(256, 2) fused_rs_kernel(RsArgs a) {
     __shared__ int ok_s;
-    // 1. tell every rank that this rank's buffer (written by earlier kernels of this stream) is complete
-    if (blockIdx.x == 0 && threadIdx.x < a.world) {
-        __threadfence_system();
-        st_release_sys(a.peer_flags[threadIdx.x] + a.slot * a.world + a.rank, a.epoch);
+    // epoch 0: the hand-shake (steps 1 and 2) was done by a one-CTA signal/wait kernel launched before this one, so that
+    // this grid never holds SMs while it waits for another rank
+    if (a.epoch != 0) {
+        // 1. tell every rank that this rank's buffer (written by earlier kernels of this stream) is complete
+        if (blockIdx.x == 0 && threadIdx.x < a.world) {
+            __threadfence_system();
+            st_release_sys(a.peer_flags[threadIdx.x] + a.slot * a.world + a.rank, a.epoch);
+        }
+        // 2. wait until every rank has said the same (bounded)
+        if (threadIdx.x == 0) {
+            const bool ok = wait_flags(a.peer_flags[a.rank] + a.slot * a.world, a.world, a.epoch, a.limit_ns);
+            if (!ok) atomicCAS(a.status, 0, 0x100 | a.rank);
+            ok_s = ok ? 1 : 0;
+        }
+        __syncthreads();
+        if (!ok_s) return;
     }
-    // 2. wait until every rank has said the same (bounded)
-    if (threadIdx.x == 0) {
-        const bool ok = wait_flags(a.peer_flags[a.rank] + a.slot * a.world, a.world, a.epoch, a.limit_ns);
-        if (!ok) atomicCAS(a.status, 0, 0x100 | a.rank);
-        ok_s = ok ? 1 : 0;
-    }
-    __syncthreads();
-    if (!ok_s) return;
     // 3. this rank's partition: sum over ranks in rank order (fp32), scale, accumulate, inf/nan, write
     const int64_t base = (int64_t)a.rank * a.part;
     const int64_t nvec = a.part / 8;

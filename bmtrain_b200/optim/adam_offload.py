@@ -272,6 +272,7 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
             state["_grad_fp16"].view(-1).copy_(p.grad.reshape(-1), non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(d2h)
+        p.grad.record_stream(d2h)   # the copy may outlive this call: the gradient's memory must not be reused before it ran
         self._staged[p] = ev
         self._step_ahead(p, state, ev)
 
@@ -525,6 +526,7 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
                         continue
                     key = "_grad_fp32" if p.dtype == torch.float32 else "_grad_fp16"
                     g = p.grad.reshape(-1)
+                    g.record_stream(d2h)   # step() returns before the copy has run
                     state[key].view(-1)[lo:hi].copy_(g[lo:hi], non_blocking=True)
                     ev = torch.cuda.Event()
                     ev.record(d2h)

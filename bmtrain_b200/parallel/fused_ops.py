@@ -108,6 +108,21 @@ def gemm_rs(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
     d.b, d.ldb, d.b_major = weight.data_ptr(), weight.stride(0), 1 if b_is_kn else 0
     d.ab_dtype, d.alpha = _DT[x.dtype], 1.0
     slots = (ctypes.c_void_p * W)(*[p + comm.rank * rows * N * es for p in inbox.ptrs])
+    if symm.no_spin():
+        # deliver / wait / sum as three launches (see symm.no_spin)
+        if epoch == 1:
+            rt.signal_wait(free_row, 1, signal=True, wait=False)
+        _native.check(lib.bmt_gemm_reduce_scatter_main(
+            ctypes.byref(d), ctypes.c_int(W), ctypes.c_int(comm.rank), rt.flag_ptrs, ctypes.c_int(free_row), ctypes.c_int(done_row),
+            ctypes.c_uint(epoch), slots, ctypes.c_void_p(inbox.local_ptr), ctypes.c_int64(rows), _native.ptr(grid_counter),
+            _native.ptr(rt.status), ctypes.c_double(rt.timeout_s), _native.stream_handle()), "GEMM -> reduce-scatter, deliver kernel")
+        rt.signal_wait(done_row, epoch, signal=False, wait=True)
+        _native.check(lib.bmt_gemm_rs_reduce(
+            ctypes.c_void_p(inbox.local_ptr), ctypes.c_int64(rows), ctypes.c_int64(N), ctypes.c_int(W), ctypes.c_int(comm.rank),
+            rt.flag_ptrs, ctypes.c_int(free_row), ctypes.c_uint(epoch), _native.ptr(grid_counter), _native.ptr(out), _native.ptr(bias),
+            ctypes.c_int(_DT[x.dtype]), _native.stream_handle()), "GEMM -> reduce-scatter, sum kernel")
+        calls["gemm_rs"] += 1
+        return out
     _native.check(lib.bmt_gemm_reduce_scatter(
         ctypes.byref(d), ctypes.c_int(W), ctypes.c_int(comm.rank), rt.flag_ptrs, ctypes.c_int(free_row), ctypes.c_int(done_row),
         ctypes.c_uint(epoch), slots, ctypes.c_void_p(inbox.local_ptr), ctypes.c_int64(rows), _native.ptr(grid_counter),

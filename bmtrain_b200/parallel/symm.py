@@ -198,11 +198,27 @@ class PeerRuntime:
         lib = _native.cuda_lib()
         epoch = self.next_epoch(row)
         dt = {torch.float16: 0, torch.bfloat16: 1}[out.dtype]
+        if no_spin():
+            # other kernels that wait for other ranks run next to this one (tensor-parallel kernels of the same step): the
+            # cross-rank hand-shake is done by one CTA, the reduction kernel itself then never waits
+            self.signal_wait(row, epoch, signal=True, wait=True)
+            epoch = 0
         _native.check(lib.bmt_fused_reduce_scatter(
             full.ptr_table(), self.flag_ptrs, ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank), ctypes.c_int(row),
             ctypes.c_uint(epoch), ctypes.c_int64(part), _native.ptr(out), ctypes.c_int(int(accumulate)), ctypes.c_float(scale),
             ctypes.c_int(dt), _native.ptr(self.overflow), _native.ptr(self.status), ctypes.c_double(self.timeout_s),
             _native.stream_handle()), "fused reduce-scatter kernel")
+
+
+def no_spin() -> bool:
+    """Whether kernels of more than one parallel dimension wait for other ranks during a step (tensor parallel x ZeRO).
+    Then no large grid may hold its SMs while it waits: a kernel of one dimension could keep the kernel another rank is
+    waiting for from being scheduled.  Waits are given to one-CTA kernels and the fused GEMM -> reduce-scatter runs as
+    separate deliver / wait / sum launches.  ``BMT_NO_SPIN=0/1`` overrides."""
+    env = os.environ.get("BMT_NO_SPIN")
+    if env is not None:
+        return env == "1"
+    return config.get("tp_size", 1) > 1 and config.get("tp_zero_size", 1) > 1
 
 
 def _same_node(comm: Communicator) -> bool:

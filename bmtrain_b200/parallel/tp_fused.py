@@ -20,16 +20,9 @@ from ..ops import gemm as _gemm
 def _fused_available(x: torch.Tensor, comm: Communicator) -> bool:
     if not x.is_cuda or comm.size == 1:
         return False
-    import os
-
-    from ..global_var import config
-
-    # The fused kernels are persistent grids whose CTAs wait for one another (pushers, end-of-kernel reduce), which is
-    # safe while the whole grid is resident.  With ZeRO groups larger than one, NCCL prefetch kernels of the data-parallel
-    # dimension run next to them and can take SMs away; that combination (tensor parallel x ZeRO > 1) has not been run on
-    # hardware yet, so it takes the collective + GEMM route unless asked for explicitly.
-    if config.get("tp_size", 1) > 1 and config.get("tp_zero_size", 1) > 1 and os.environ.get("BMT_TP_FUSED_WITH_ZERO", "0") != "1":
-        return False
+    # With ZeRO groups larger than one, kernels of the data-parallel dimension that wait for other ranks run next to the
+    # tensor-parallel ones.  The fused kernels then take their non-spinning form (``symm.no_spin``): pusher CTAs are the
+    # first of their grid, and the GEMM -> reduce-scatter leaves waiting and summing to separate small launches.
     from . import symm
 
     return symm.peer_runtime_ready(comm)

@@ -202,3 +202,134 @@ def body_tp_model_gpu():
 def test_tensor_parallel_model_2gpu():
     _need(2)
     run_distributed("test_multi_gpu", "body_tp_model_gpu", 2, device="cuda", init_kwargs=dict(tp_size=2))
+
+
+def _oracle_gpt(cfg, seed, std=0.03, activation="gelu"):
+    from oracle import OracleGPT
+
+    torch.manual_seed(seed)
+    ref = OracleGPT(cfg["num_layers"], cfg["vocab"], cfg["d"], cfg["dh"], cfg["h"], cfg["dff"], cfg["max_distance"], activation=activation)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.normal_(0, std)
+        for blk in ref.transformers:
+            blk.ln_attn.weight.add_(1.0)
+            blk.ln_ff.weight.add_(1.0)
+        ref.layernorm.weight.add_(1.0)
+    return ref
+
+
+def _compare_grads(bmt, model, ref, rel):
+    got = {r["name"]: r for r in bmt.inspect.inspect_model(model, "*")}
+    checked = 0
+    for name, p in ref.named_parameters():
+        if name not in got or tuple(got[name]["shape"]) != tuple(p.shape):
+            continue   # tensor-parallel shards report their own slice
+        ref_std = p.grad.std().item()
+        assert abs(got[name]["grad_std"] - ref_std) <= rel * ref_std + 1e-4, (name, got[name]["grad_std"], ref_std)
+        assert abs(got[name]["grad_mean"] - p.grad.mean().item()) <= rel * ref_std + 1e-4, name
+        checked += 1
+    assert checked > 0
+
+
+def body_tp_zero_gpu():
+    """bf16 GPT with tensor parallel 2 x ZeRO 2 on 4 GPUs, two accumulated backward passes.  The tensor-parallel pairs run on
+    the fused kernels in their non-spinning form next to the ZeRO gathers and the fused gradient reduce-scatter; loss and
+    gradients follow the fp32 single-process model."""
+    import bmtrain_b200 as bmt
+    from bmtrain_b200.parallel import fused_ops, symm
+
+    rank, world = bmt.rank(), bmt.world_size()
+    tp = bmt.config["tp_size"]
+    dp, dp_rank = world // tp, rank // tp
+    assert symm.no_spin()
+    cfg = dict(num_layers=3, vocab=2048, d=256, dh=64, h=4, dff=1024, max_distance=256)
+    ref = _oracle_gpt(cfg, 3)
+    model = bmt.models.GPT(cfg["num_layers"], cfg["vocab"], cfg["d"], cfg["dh"], cfg["h"], cfg["dff"], cfg["max_distance"],
+                           dtype=torch.bfloat16, activation="gelu")
+    model.load_state_dict(ref.state_dict())
+    all_ids = torch.randint(0, cfg["vocab"], (dp, 2, 2, 257), generator=torch.Generator().manual_seed(9))
+    pos = torch.arange(256)[None].expand(2, -1).contiguous()
+    mask = torch.ones(2, 256, dtype=torch.bool)
+    loss_fn = bmt.loss.FusedCrossEntropy(parallel=True)
+    losses = []
+    for it in range(2):
+        ids = all_ids[dp_rank, it]
+        logits = model(ids[:, :-1].cuda(), pos.cuda(), mask.cuda())      # (s, b, vocab / tp)
+        loss = loss_fn(logits.reshape(-1, logits.shape[-1]), ids[:, 1:].t().reshape(-1).cuda())
+        (loss * 256.0 / dp).backward()
+        losses.append(loss.item())
+    bmt.synchronize()
+    assert fused_ops.calls["ag_gemm"] > 0 and fused_ops.calls["gemm_rs"] > 0, fused_ops.calls
+    for d in range(dp):
+        for it in range(2):
+            ids = all_ids[d, it]
+            rl = torch.nn.functional.cross_entropy(ref(ids[:, :-1], pos, mask).view(-1, cfg["vocab"]), ids[:, 1:].reshape(-1))
+            (rl * 256.0 / dp).backward()
+            if d == dp_rank:
+                assert abs(losses[it] - rl.item()) < 3e-2, (it, losses[it], rl.item())
+    _compare_grads(bmt, model, ref, 0.08)
+    for rt in symm._runtimes.values():
+        if rt is not None:
+            rt.check()
+    from bmtrain_b200.ops import _native
+    assert _native.cuda_lib().bmt_gemm_status() == 0
+
+
+def test_tensor_parallel_with_zero_4gpu():
+    _need(4)
+    run_distributed("test_multi_gpu", "body_tp_zero_gpu", 4, device="cuda", init_kwargs=dict(tp_size=2))
+
+
+def test_tp_fused_kernels_nonspinning_2gpu(monkeypatch):
+    """The deliver / wait / sum form of GEMM -> reduce-scatter and the fused reduce-scatter with an external hand-shake."""
+    _need(2)
+    monkeypatch.setenv("BMT_NO_SPIN", "1")
+    run_distributed("test_multi_gpu", "body_tp_fused", 2, device="cuda")
+
+
+def body_pipe_zero_gpu():
+    """fp16 GPT, pipeline 2 x ZeRO 2 on 4 GPUs, 4 layers (two per stage), 4 micro-batches: every block of a stage keeps its
+    full gradients across the micro-batches in peer-visible staging memory, so each needs staging of its own."""
+    import bmtrain_b200 as bmt
+    from bmtrain_b200.parallel import symm
+
+    rank, world = bmt.rank(), bmt.world_size()
+    cfg = dict(num_layers=4, vocab=1024, d=256, dh=64, h=4, dff=512, max_distance=64)
+    ref = _oracle_gpt(cfg, 5, activation="relu")
+    model = bmt.models.GPT(cfg["num_layers"], cfg["vocab"], cfg["d"], cfg["dh"], cfg["h"], cfg["dff"], cfg["max_distance"],
+                           dtype=torch.float16, activation="relu")
+    assert isinstance(model.transformers, bmt.PipelineTransformerBlockList)
+    assert len(model.transformers.layer_ids) == 2
+    model.load_state_dict(ref.state_dict())
+    all_ids = torch.randint(0, cfg["vocab"], (world, 2, 65), generator=torch.Generator().manual_seed(60))
+    ids = all_ids[rank]
+    pos = torch.arange(64)[None].expand(2, -1).contiguous()
+    mask = torch.ones(2, 64, dtype=torch.bool)
+    loss_fn = bmt.loss.FusedCrossEntropy()
+    scale = 512.0
+    logits = model(ids[:, :-1].cuda(), pos.cuda(), mask.cuda())
+    loss = loss_fn(logits.view(-1, logits.shape[-1]), ids[:, 1:].reshape(-1).cuda())
+    (loss * scale / world).backward()
+    bmt.synchronize()
+    ref_loss = None
+    for d in range(world):
+        rl = torch.nn.functional.cross_entropy(ref(all_ids[d][:, :-1], pos, mask).view(-1, cfg["vocab"]), all_ids[d][:, 1:].reshape(-1))
+        (rl * scale / world).backward()
+        if d == rank:
+            ref_loss = rl.item()
+    assert abs(loss.item() - ref_loss) < 2e-2, (loss.item(), ref_loss)
+    got = {r["name"]: r for r in bmt.inspect.inspect_model(model, "*")}
+    for name, p in ref.named_parameters():
+        if name not in got:
+            continue
+        ref_std = p.grad.std().item()
+        assert abs(got[name]["grad_std"] - ref_std) <= 0.05 * ref_std + 1e-4, (name, got[name]["grad_std"], ref_std)
+    for rt in symm._runtimes.values():
+        if rt is not None:
+            rt.check()
+
+
+def test_pipeline_with_zero_4gpu():
+    _need(4)
+    run_distributed("test_multi_gpu", "body_pipe_zero_gpu", 4, device="cuda", init_kwargs=dict(pipe_size=2, num_micro_batches=4))
