@@ -281,29 +281,29 @@ def run_llama(args, emit):
     for _ in range(max(args.warmup, 1)):
         step(on_dev, False)
 
-    def timed(e2e):
-        finish_updates()
-        bmt.synchronize()
-        torch.cuda.synchronize()
-        sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-        l0 = launch_count()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        start.record()
-        last = None
-        for _ in range(args.steps):
-            last = step(host if e2e else on_dev, e2e)
-        finish_updates()
-        end.record()
-        torch.cuda.synchronize()
-        wall = (time.perf_counter() - t0) * 1e3
-        bmt.synchronize()
-        t = torch.tensor([max(start.elapsed_time(end), wall) if e2e else start.elapsed_time(end), float(last)], device=dev)
-        t = bmt.distributed.all_reduce(t, "max")
-        return float(t[0]), float(t[1]), launch_count() - l0, sampler.stop() if sampler else None
-
-    ms, _, launches, clocks = timed(False)
-    ms_e2e, final_loss, _, _ = timed(True)
+    # One timed pass (a step takes seconds): every micro-batch comes from pinned host memory and the loss is read back, so
+    # the pass is the end-to-end measurement; `value` is its CUDA-event time, `e2e` the larger of that and the wall clock.
+    finish_updates()
+    bmt.synchronize()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    l0 = launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    last = None
+    for _ in range(args.steps):
+        last = step(host, True)
+    finish_updates()
+    end.record()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) * 1e3
+    bmt.synchronize()
+    t = torch.tensor([start.elapsed_time(end), max(start.elapsed_time(end), wall), float(last)], device=dev)
+    t = bmt.distributed.all_reduce(t, "max")
+    ms, ms_e2e, final_loss = float(t[0]), float(t[1]), float(t[2])
+    launches = launch_count() - l0
+    clocks = sampler.stop() if sampler else None
     tokens = args.global_batch * LLAMA_SEQ * args.steps
     value = tokens / (ms / 1e3)
     n_params = layers * (4 * 5120 * 5120 + 3 * 5120 * 13824) + 2 * 32000 * 5120

@@ -195,6 +195,24 @@ def main() -> None:
     t_s = _timer(split_grad_rs, args.iters, args.warmup, flush)
     report("(2) grad reduce-scatter + accumulate + inf/nan", [W, part], t_f, t_s, 0.0, (W - 1) * part * 2)
     rt.check()
+    if symm.nvls_wanted():
+        # the same reduction summed inside the switch: every rank receives `part` elements instead of (W - 1) * part
+        mc = rt.slot(("bench_rs_mc",), W * part * 2, multicast=True)
+        if getattr(mc, "mc_ptr", 0):
+            mc.tensor(dt, W * part).copy_(plain_full)
+            acc2, row2 = acc.clone(), rt.row(("bench_rs_mc", "row"))
+            t_m = _timer(lambda: rt.reduce_scatter(mc, row2, part, acc2, accumulate=True, scale=1.0), args.iters, args.warmup, flush)
+            report("(2) the same through multimem.ld_reduce (NVLS)", [W, part], t_m, t_s, 0.0, part * 2,
+                   {"roofline_note": "link bytes = one partition: the switch sums, a rank receives the result only"})
+            ref = torch.empty(part, dtype=dt, device=dev)
+            comm.reduce_scatter_into(ref, plain_full, "sum")
+            chk = torch.zeros(part, dtype=dt, device=dev)
+            rt.reduce_scatter(mc, row2, part, chk, accumulate=False, scale=1.0)
+            torch.cuda.synchronize()
+            err = ((chk.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-6)).item()
+            if rank == 0:
+                print(json.dumps({"check": "multimem reduce-scatter vs NCCL", "max_rel_err": err}), flush=True)
+            rt.check()
 
     # ------------------------------- push all-gather kernel alone (moves the block's other parameters in path 1) vs NCCL
     gbuf = rt.slot(("bench_push",), W * part * 2)

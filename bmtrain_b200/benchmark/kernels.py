@@ -49,7 +49,8 @@ def time_it(fn, iters: int, flush: bool) -> float:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "adam", "norm", "ce", "softmax", "attention"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "adam", "norm", "norm_bwd", "rmsnorm", "ce", "ce_bwd", "softmax", "softmax_bwd", "embedding",
+                                                  "embedding_bwd", "infnan", "sqnorm", "colsum", "rope", "swiglu", "attention"])
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=20)
@@ -142,6 +143,76 @@ def main():
             res[name + "_fwd_bwd_tflops"] = 3.5 * flops_f / ms_fb / 1e9
         res["fused_fwd_frac_of_peak"] = res["fused_fwd_tflops"] / tflops
         print(json.dumps(res))
+    elif args.op in ("norm_bwd", "rmsnorm", "ce_bwd", "softmax", "softmax_bwd", "embedding", "embedding_bwd", "infnan", "sqnorm",
+                     "colsum", "rope", "swiglu"):
+        # memory-bound kernels: achieved = algorithmic bytes / time, against the measured copy bandwidth
+        import ctypes
+
+        from bmtrain_b200.ops import _native, elementwise as EW, embedding as EMB, infnan as IN
+
+        lib = _native.cuda_lib()
+        m, n = args.m, args.n
+        code = 0 if dt == torch.float16 else 1
+        if args.op == "rmsnorm":
+            x, w = torch.randn(m, n, device=dev, dtype=dt), torch.ones(n, device=dev, dtype=dt)
+            fn, nbytes = (lambda: N.rms_norm(x, w)), 2 * x.numel() * 2
+        elif args.op == "norm_bwd":
+            x = torch.randn(m, n, device=dev, dtype=dt, requires_grad=True)
+            w, b = torch.ones(n, device=dev, dtype=dt, requires_grad=True), torch.zeros(n, device=dev, dtype=dt, requires_grad=True)
+            y = N.layer_norm(x, w, b)
+            g = torch.randn_like(y)
+            fn, nbytes = (lambda: torch.autograd.grad(y, (x, w, b), g, retain_graph=True)), 3 * x.numel() * 2
+        elif args.op == "ce_bwd":
+            x = torch.randn(m, n, device=dev, dtype=dt)
+            t = torch.randint(0, n, (m,), device=dev)
+            mx, se, _ = CE.row_stats(x, t)
+            lse, gl = mx + se.log(), torch.ones(m, device=dev)
+            out = torch.empty_like(x)
+            fn, nbytes = (lambda: CE.ce_backward(x, t, lse, gl)), 2 * x.numel() * 2
+        elif args.op in ("softmax", "softmax_bwd"):
+            # (batch, heads, seq, seq) scores of the two-GEMM attention form
+            b_, h_, s_ = args.batch, args.heads, args.seq
+            p_ = torch.randn(b_, h_, s_, s_, device=dev, dtype=dt)
+            dp = torch.randn_like(p_)
+            if args.op == "softmax":
+                fn = lambda: lib.bmt_masked_softmax(ctypes.c_int64(b_), ctypes.c_int64(h_), ctypes.c_int64(s_), ctypes.c_int64(s_),
+                                                    ctypes.c_int64(s_), _native.ptr(p_), ctypes.c_int(code), ctypes.c_int(1), None, None,
+                                                    _native.stream_handle())
+                nbytes = 2 * p_.numel() * 2 * 0.5   # causal: about half of every row is read and written
+            else:
+                fn = lambda: lib.bmt_softmax_bwd(ctypes.c_int64(b_ * h_ * s_), ctypes.c_int64(s_), ctypes.c_int64(s_), _native.ptr(p_),
+                                                 _native.ptr(dp), ctypes.c_float(0.1), ctypes.c_int(code), _native.stream_handle())
+                nbytes = 3 * p_.numel() * 2
+        elif args.op in ("embedding", "embedding_bwd"):
+            w = torch.randn(n, args.k, device=dev, dtype=dt)          # (vocab, d)
+            ids = torch.randint(0, n, (m,), device=dev)
+            g = torch.randn(m, args.k, device=dev, dtype=dt)
+            if args.op == "embedding":
+                fn, nbytes = (lambda: EMB.embedding_forward(ids, w)), 2 * m * args.k * 2
+            else:
+                fn, nbytes = (lambda: EMB.embedding_backward(ids, g, n)), (m * args.k + n * args.k) * 2
+        elif args.op in ("infnan", "sqnorm"):
+            x = torch.randn(args.n, device=dev, dtype=dt)
+            flag, tot = torch.zeros(1, dtype=torch.uint8, device=dev), torch.zeros(1, device=dev)
+            fn = (lambda: IN.multi_has_inf_nan([x], flag)) if args.op == "infnan" else (lambda: IN.multi_sq_norm([x], tot))
+            nbytes = x.numel() * 2
+        elif args.op == "colsum":
+            x, out = torch.randn(m, n, device=dev, dtype=dt), torch.empty(n, device=dev, dtype=dt)
+            fn = lambda: lib.bmt_colsum(ctypes.c_int64(m), ctypes.c_int64(n), _native.ptr(x), ctypes.c_int(code), _native.ptr(out),
+                                        _native.stream_handle())
+            nbytes = x.numel() * 2
+        elif args.op == "rope":
+            hk = args.kv_heads or args.heads
+            g_ = args.heads // hk
+            packed = torch.randn(args.batch, args.seq, hk, g_ + 2, args.head_dim, device=dev, dtype=dt)
+            fn, nbytes = (lambda: EW.rope_qkv(packed, g_)), 2 * packed.numel() * 2
+        else:  # swiglu
+            x = torch.randn(m, 2 * n, device=dev, dtype=dt)
+            fn, nbytes = (lambda: EW.swiglu(x)), 3 * m * n * 2
+        with torch.no_grad() if args.op != "norm_bwd" else torch.enable_grad():
+            ms = time_it(fn, args.iters, flush)
+        print(json.dumps({"op": args.op, "m": m, "n": n, "dtype": args.dtype, "ms": ms, "gbs": nbytes / ms / 1e6,
+                          "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_source": src}))
     elif args.op == "ce":
         x = torch.randn(args.m, args.n, device=dev, dtype=dt)
         t = torch.randint(0, args.n, (args.m,), device=dev)

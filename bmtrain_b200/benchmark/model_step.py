@@ -33,6 +33,7 @@ def main() -> None:
     ap.add_argument("--kv-heads", type=int, default=0, help="llama: number of key/value heads (0 = same as --heads)")
     ap.add_argument("--ffn", type=int, default=8192)
     ap.add_argument("--vocab", type=int, default=10240)
+    ap.add_argument("--activation", default="relu", choices=["relu", "gelu"], help="gpt: feed-forward activation")
     ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--batch", type=int, default=2, help="sequences per data-parallel rank and step")
     ap.add_argument("--tp", type=int, default=1)
@@ -55,7 +56,7 @@ def main() -> None:
     rank, world = bmt.rank(), bmt.world_size()
     if args.model == "gpt":
         model = bmt.models.GPT(args.layers, args.vocab, args.dim, args.dim // args.heads, args.heads, args.ffn, args.seq,
-                               bias=True, dtype=dt, zero_level=args.zero)
+                               bias=True, dtype=dt, zero_level=args.zero, activation=args.activation)
     else:
         model = bmt.models.Llama(args.layers, args.vocab, args.dim, args.heads, args.ffn, num_kv_heads=args.kv_heads or None,
                                  dtype=dt, zero_level=args.zero)

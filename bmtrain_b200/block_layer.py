@@ -531,7 +531,7 @@ class Block(torch.nn.Module):
                 if rt is not None:
                     # staging buffer in peer-visible memory; peers must have finished reading its previous contents
                     key = self._grad_slot_key(b)
-                    buf = rt.slot(key, b.total * b.storage.element_size())
+                    buf = rt.slot(key, b.total * b.storage.element_size(), multicast=True)
                     done_row = rt.row(key + ("done",))
                     if rt.epochs.get(done_row, 0) > 0:
                         rt.signal_wait(done_row, rt.epochs[done_row], signal=False, wait=True)

@@ -72,14 +72,51 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
 
 def build_cpu(force: bool = False) -> str:
     target = os.path.join(HERE, "_cpu.so")
-    sources = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cpp")]
+    sources = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cpp") and f not in _OWN_LIBRARY]
     if sources and (force or _stale(target, sources)):
         _run([os.environ.get("CXX", "g++"), *CXX_FLAGS, "-I", CSRC, "-o", target, *sources, "-lrt"])
     return target
 
 
+_OWN_LIBRARY = {"nccl_comm.cpp"}  # sources that are linked into a library of their own
+
+
+def _nccl_paths():
+    """(include dir, library file) of the NCCL this process would load: the pip package next to torch when present (the
+    one torch itself links), else the system install."""
+    try:
+        import importlib.util
+
+        spec = importlib.util.find_spec("nvidia.nccl")
+        for root in (spec.submodule_search_locations if spec else []):
+            inc, lib = os.path.join(root, "include"), os.path.join(root, "lib", "libnccl.so.2")
+            if os.path.exists(os.path.join(inc, "nccl.h")) and os.path.exists(lib):
+                return inc, lib
+    except Exception:
+        pass
+    for inc, lib in (("/usr/include", "/usr/lib/x86_64-linux-gnu/libnccl.so.2"), ("/usr/local/cuda/include", "/usr/local/cuda/lib64/libnccl.so.2")):
+        if os.path.exists(os.path.join(inc, "nccl.h")) and os.path.exists(lib):
+            return inc, lib
+    return None, None
+
+
+def build_nccl(force: bool = False) -> str:
+    """``_nccl.so``: the C++ communicator wrapper (``csrc/nccl_comm.cpp``), linked against the NCCL shared library."""
+    target = os.path.join(HERE, "_nccl.so")
+    src = os.path.join(CSRC, "nccl_comm.cpp")
+    inc, lib = _nccl_paths()
+    if inc is None:
+        return ""   # no NCCL on this machine: the wrapper is optional (torch.distributed carries the collectives)
+    if force or _stale(target, [src]):
+        cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include") if os.path.sep in _nvcc() else "/usr/local/cuda/include"
+        _run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", inc, "-I", cuda_inc,
+              "-o", target, src, lib, "-Wl,-rpath," + os.path.dirname(lib)])
+    return target
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_cpu(force)
+    build_nccl(force)
     build_cuda(force, verbose)
 
 

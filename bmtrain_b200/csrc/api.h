@@ -152,6 +152,10 @@ int bmt_ipc_handle_size(void);
 int bmt_fused_reduce_scatter(const void* const* peers, void* const* peer_flags, int world, int rank, int slot,
                              unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
                              void* overflow_u8, void* status_i32, double timeout_s, void* stream);
+// Same reduction with one multimem.ld_reduce per 16 bytes through the NVSwitch multicast address of the full buffers.
+int bmt_fused_reduce_scatter_mc(const void* multicast, void* const* peer_flags, int world, int rank, int slot,
+                                unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
+                                void* overflow_u8, void* status_i32, double timeout_s, void* stream);
 int bmt_push_ranges(const void* const* src, const int64_t* dst_off, const int64_t* nbytes, int nranges, void* const* dst,
                     void* const* peer_flags, int world, int rank, int free_row, int done_row, unsigned int epoch,
                     void* counter_u32, void* status_i32, double timeout_s, int grid, void* stream);

@@ -20,14 +20,31 @@ __global__ void __launch_bounds__(256) ce_row_stats_kernel(int64_t m, int64_t n,
     float mx = -INFINITY, se = 0.f;
     const bool vec_ok = (n % V == 0) && (((uintptr_t)xr & 15) == 0);
     if (vec_ok) {
-        for (int64_t i = threadIdx.x; i < n / V; i += blockDim.x) {
-            bmt::Vec16<T> v = bmt::ld16(xr + i * V);
-            float f[V], lm = -INFINITY;
+        // U vectors per thread and trip: all loads are issued before the first use, the running maximum moves at most
+        // once per trip, and every element costs one FMA and one ex2 (base-2 exponent of x * log2e - max * log2e)
+        constexpr int U = 4;
+        constexpr float L2E = 1.4426950408889634f;
+        const int64_t nv = n / V;
+        for (int64_t i0 = threadIdx.x; i0 < nv; i0 += (int64_t)blockDim.x * U) {
+            bmt::Vec16<T> v[U];
 #pragma unroll
-            for (int k = 0; k < V; ++k) { f[k] = bmt::Cvt<T>::to_f(v.v[k]); lm = fmaxf(lm, f[k]); }
-            if (lm > mx) { se *= __expf(mx - lm); mx = lm; }
+            for (int u = 0; u < U; ++u)
+                if (i0 + (int64_t)u * blockDim.x < nv) v[u] = bmt::ld16(xr + (i0 + (int64_t)u * blockDim.x) * V);
+            float lm = -INFINITY;
 #pragma unroll
-            for (int k = 0; k < V; ++k) se += __expf(f[k] - mx);
+            for (int u = 0; u < U; ++u)
+                if (i0 + (int64_t)u * blockDim.x < nv) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) lm = fmaxf(lm, bmt::Cvt<T>::to_f(v[u].v[k]));
+                }
+            if (lm > mx) { se *= exp2f((mx - lm) * L2E); mx = lm; }
+            const float off = -mx * L2E;
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (i0 + (int64_t)u * blockDim.x < nv) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) se += exp2f(fmaf(bmt::Cvt<T>::to_f(v[u].v[k]), L2E, off));
+                }
         }
     } else {
         for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -63,15 +80,28 @@ __global__ void __launch_bounds__(256) ce_backward_kernel(int64_t m, int64_t n, 
     constexpr int V = bmt::Vec16<T>::N;
     const bool vec_ok = (n % V == 0) && (((uintptr_t)xr & 15) == 0) && (((uintptr_t)orow & 15) == 0);
     if (vec_ok) {
-        for (int64_t i = threadIdx.x; i < n / V; i += blockDim.x) {
-            bmt::Vec16<T> v = bmt::ld16(xr + i * V), o;
+        constexpr int U = 4;
+        constexpr float L2E = 1.4426950408889634f;
+        const int64_t nv = n / V;
+        const float off = -l * L2E;
+        for (int64_t i0 = threadIdx.x; i0 < nv; i0 += (int64_t)blockDim.x * U) {
+            bmt::Vec16<T> v[U];
 #pragma unroll
-            for (int k = 0; k < V; ++k) {
-                float p = __expf(bmt::Cvt<T>::to_f(v.v[k]) - l);
-                if (i * V + k == t) p -= 1.f;
-                o.v[k] = bmt::Cvt<T>::from_f(p * g);
+            for (int u = 0; u < U; ++u)
+                if (i0 + (int64_t)u * blockDim.x < nv) v[u] = bmt::ld16(xr + (i0 + (int64_t)u * blockDim.x) * V);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t i = i0 + (int64_t)u * blockDim.x;
+                if (i >= nv) continue;
+                bmt::Vec16<T> o;
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    float p = exp2f(fmaf(bmt::Cvt<T>::to_f(v[u].v[k]), L2E, off));
+                    if (i * V + k == t) p -= 1.f;
+                    o.v[k] = bmt::Cvt<T>::from_f(p * g);
+                }
+                bmt::st16(orow + i * V, o);
             }
-            bmt::st16(orow + i * V, o);
         }
     } else {
         for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {

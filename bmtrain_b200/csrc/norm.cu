@@ -7,6 +7,8 @@
 // its rows and keeps per-thread partial dgamma / dbeta in registers, written once to a
 // (nblk x d) fp32 scratch that a second kernel folds over nblk.
 // (The reference calls F.layer_norm: example/layers/layernorm.py:29.)
+#include <stdlib.h>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -142,8 +144,126 @@ __global__ void __launch_bounds__(1024) norm_fold_kernel(int d, int nblk, const 
     }
 }
 
+// Forward with the row held in registers: WPR warps share a row (8 / WPR rows per CTA at a time), every lane keeps VPL
+// 16-byte vectors, all of whose loads are issued before the first use; statistics are exact two-pass sums over the
+// registers, reduced with shuffles (and one shared-memory exchange when WPR > 1).  A persistent grid strides over the
+// rows.
+template <typename T, int VPL, int WPR>
+__global__ void __launch_bounds__(NT, 2) norm_fwd_reg_kernel(int64_t rows, int d, const T* __restrict__ x, const T* __restrict__ w,
+                                                          const T* __restrict__ b, float eps, int rms, T* __restrict__ y,
+                                                          float* __restrict__ stats) {
+    constexpr int RPC = 8 / WPR;                       // rows a CTA works on at a time
+    __shared__ float ex[2][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = warp % WPR, slot = warp / WPR;     // position inside the row's warp team, row slot inside the CTA
+    const int64_t groups = (rows + RPC - 1) / RPC;
+    for (int64_t gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+        const int64_t r = gi * RPC + slot;
+        const bool live = r < rows;
+        float f[VPL][8];
+        float s = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int c = ((v * WPR + sub) * 32 + lane) * 8;
+            if (live && c < d) {
+                const bmt::Vec16<T> t = bmt::ld16(x + r * d + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { f[v][k] = bmt::Cvt<T>::to_f(t.v[k]); s += f[v][k]; }
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[v][k] = 0.f;
+            }
+        }
+        float mean = 0.f;
+        if (!rms) {
+            s = bmt::warp_sum(s);
+            if (WPR > 1) {
+                if (lane == 0) ex[0][warp] = s;
+                __syncthreads();
+                s = 0.f;
+#pragma unroll
+                for (int i = 0; i < WPR; ++i) s += ex[0][slot * WPR + i];
+            }
+            mean = s / d;
+        }
+        float q = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int c = ((v * WPR + sub) * 32 + lane) * 8;
+            if (c < d) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { const float t = f[v][k] - mean; q += t * t; }
+            }
+        }
+        q = bmt::warp_sum(q);
+        if (WPR > 1) {
+            if (lane == 0) ex[1][warp] = q;
+            __syncthreads();
+            q = 0.f;
+#pragma unroll
+            for (int i = 0; i < WPR; ++i) q += ex[1][slot * WPR + i];
+        }
+        const float rstd = rsqrtf(q / d + eps);
+        if (live && sub == 0 && lane == 0) { stats[r] = mean; stats[rows + r] = rstd; }
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int c = ((v * WPR + sub) * 32 + lane) * 8;
+            if (live && c < d) {
+                // weight and bias stay hot in L1 (a few KB re-read by every row); keeping them in registers instead would
+                // halve the number of resident warps and with it the bytes in flight
+                const bmt::Vec16<T> wv = bmt::ld16(w + c);
+                bmt::Vec16<T> bv, o;
+                if (b) bv = bmt::ld16(b + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    float t = (f[v][k] - mean) * rstd * bmt::Cvt<T>::to_f(wv.v[k]);
+                    if (b) t += bmt::Cvt<T>::to_f(bv.v[k]);
+                    o.v[k] = bmt::Cvt<T>::from_f(t);
+                }
+                bmt::st16(y + r * d + c, o);
+            }
+        }
+        if (WPR > 1) __syncthreads();   // the exchange slots are reused by the next group
+    }
+}
+
+template <typename T, int VPL, int WPR>
+void launch_fwd_reg(int64_t rows, int d, const void* x, const void* w, const void* b, float eps, int rms, void* y, void* stats,
+                    cudaStream_t s) {
+    const int64_t groups = (rows + (8 / WPR) - 1) / (8 / WPR);
+    const int64_t grid = groups < 148 * 2 ? groups : 148 * 2;
+    norm_fwd_reg_kernel<T, VPL, WPR><<<(unsigned)grid, NT, 0, s>>>(rows, d, (const T*)x, (const T*)w, (const T*)b, eps, rms, (T*)y,
+                                                                    (float*)stats);
+}
+
+template <typename T, int WPR>
+bool fwd_reg_vpl(int vpl, int64_t rows, int d, const void* x, const void* w, const void* b, float eps, int rms, void* y, void* stats,
+                 cudaStream_t s) {
+    if (vpl <= 2) launch_fwd_reg<T, 2, WPR>(rows, d, x, w, b, eps, rms, y, stats, s);
+    else if (vpl <= 4) launch_fwd_reg<T, 4, WPR>(rows, d, x, w, b, eps, rms, y, stats, s);
+    else if (vpl <= 6) launch_fwd_reg<T, 6, WPR>(rows, d, x, w, b, eps, rms, y, stats, s);
+    else if (vpl <= 8) launch_fwd_reg<T, 8, WPR>(rows, d, x, w, b, eps, rms, y, stats, s);
+    else return false;
+    return true;
+}
+
 template <typename T>
 int fwd(int64_t rows, int64_t d, const void* x, const void* w, const void* b, float eps, int rms, void* y, void* stats, cudaStream_t s) {
+    // smallest warp team that keeps at most 8 vectors (64 values) per lane
+    static const bool use_reg = [] { const char* e = getenv("BMT_NORM_STAGED"); return !(e && atoi(e) == 1); }();
+    if (use_reg && d <= 16384) {
+        const int wpr = d <= 2048 ? 1 : d <= 4096 ? 2 : d <= 8192 ? 4 : 8;
+        const int vpl = (int)((d + 256 * wpr - 1) / (256 * wpr));
+        bool done = false;
+        if (wpr == 1) done = fwd_reg_vpl<T, 1>(vpl, rows, (int)d, x, w, b, eps, rms, y, stats, s);
+        else if (wpr == 2) done = fwd_reg_vpl<T, 2>(vpl, rows, (int)d, x, w, b, eps, rms, y, stats, s);
+        else if (wpr == 4) done = fwd_reg_vpl<T, 4>(vpl, rows, (int)d, x, w, b, eps, rms, y, stats, s);
+        else done = fwd_reg_vpl<T, 8>(vpl, rows, (int)d, x, w, b, eps, rms, y, stats, s);
+        if (done) {
+            bmt_count_launch(1);
+            return (int)cudaGetLastError();
+        }
+    }
     norm_fwd_kernel<T><<<(unsigned)rows, NT, d * sizeof(float), s>>>(rows, (int)d, (const T*)x, (const T*)w, (const T*)b, eps, rms, (T*)y, (float*)stats);
     bmt_count_launch(1);
     return (int)cudaGetLastError();
@@ -163,7 +283,7 @@ int bwd(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, c
 extern "C" int bmt_norm_fwd(int64_t rows, int64_t d, const void* x, const void* w, const void* b, float eps, int rms, int dtype,
                             void* y, void* stats, void* stream) {
     if (rows <= 0) return 0;
-    if (d % 8 != 0 || d > 12032 || dtype == BMT_DT_F32) return -3;  // row staged in <= 47 KB of shared memory
+    if (d % 8 != 0 || d > 16384 || dtype == BMT_DT_F32) return -3;
     cudaStream_t s = (cudaStream_t)stream;
     return dtype == BMT_DT_F16 ? fwd<__half>(rows, d, x, w, b, eps, rms, y, stats, s)
                                : fwd<__nv_bfloat16>(rows, d, x, w, b, eps, rms, y, stats, s);

@@ -152,6 +152,71 @@ __global__ void __launch_bounds__(256, 2) fused_rs_kernel(RsArgs a) {
     if (__syncthreads_or(bad) && threadIdx.x == 0 && a.overflow) *a.overflow = 1;
 }
 
+// ---- in-switch reduction (NVLS): one multimem.ld_reduce per 16 bytes reads the same offset of every rank's buffer through
+// the NVSwitch multicast address and returns the sum (added up in fp32 inside the switch), so a rank pulls 1 / W of the
+// bytes the plain peer loads above move.
+template <typename T> __device__ __forceinline__ void mc_ld_reduce(const void* mc, uint32_t (&r)[4]);
+template <> __device__ __forceinline__ void mc_ld_reduce<__nv_bfloat16>(const void* mc, uint32_t (&r)[4]) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "l"(mc) : "memory");
+}
+template <> __device__ __forceinline__ void mc_ld_reduce<__half>(const void* mc, uint32_t (&r)[4]) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "l"(mc) : "memory");
+}
+
+// Same contract as fused_rs_kernel; `mc` is the multicast address of the full gradient buffer (all ranks bound).
+template <typename T, int U>
+__global__ void __launch_bounds__(256, 2) fused_rs_mc_kernel(RsArgs a, const T* __restrict__ mc) {
+    __shared__ int ok_s;
+    if (a.epoch != 0) {
+        if (blockIdx.x == 0 && threadIdx.x < a.world) {
+            __threadfence_system();
+            st_release_sys(a.peer_flags[threadIdx.x] + a.slot * a.world + a.rank, a.epoch);
+        }
+        if (threadIdx.x == 0) {
+            const bool ok = wait_flags(a.peer_flags[a.rank] + a.slot * a.world, a.world, a.epoch, a.limit_ns);
+            if (!ok) atomicCAS(a.status, 0, 0x100 | a.rank);
+            ok_s = ok ? 1 : 0;
+        }
+        __syncthreads();
+        if (!ok_s) return;
+    }
+    const int64_t base = (int64_t)a.rank * a.part;
+    const int64_t nvec = a.part / 8;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    T* __restrict__ out = (T*)a.out;
+    bool bad = false;
+    for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+        uint32_t v[U][4];
+        bmt::Vec16<T> old[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i < nvec) {
+                mc_ld_reduce<T>(mc + base + i * 8, v[u]);
+                if (a.accumulate) old[u] = bmt::ld16(out + i * 8);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i >= nvec) continue;
+            bmt::Vec16<T> sum = *reinterpret_cast<bmt::Vec16<T>*>(v[u]), o;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float f = bmt::Cvt<T>::to_f(sum.v[k]) * a.scale;
+                if (a.accumulate) f += bmt::Cvt<T>::to_f(old[u].v[k]);
+                bad |= !(fabsf(f) <= 3.402823466e38f);
+                o.v[k] = bmt::Cvt<T>::from_f(f);
+                bad |= !(fabsf(bmt::Cvt<T>::to_f(o.v[k])) <= 3.402823466e38f);
+            }
+            bmt::st16(out + i * 8, o);
+        }
+    }
+    if (__syncthreads_or(bad) && threadIdx.x == 0 && a.overflow) *a.overflow = 1;
+}
+
 template <typename T>
 static void launch_fused_rs(const RsArgs& a, unsigned blocks, cudaStream_t s) {
     if (a.world <= 2) fused_rs_kernel<T, 2, 4><<<blocks, 256, 0, s>>>(a);
@@ -280,14 +345,34 @@ extern "C" int bmt_peer_copy(void* dst, const void* src, int64_t nbytes, int gri
 // Fused reduce-scatter: out[0..part) (+)= scale * sum_j peer_j[rank*part + i], with inf/nan detection.
 // peers / peer_flags: host arrays of `world` device pointers.  part must be a multiple of 8 elements and every
 // buffer 16-byte aligned.  dtype: 0 fp16, 1 bf16, 2 fp32.
+static int fused_reduce_scatter_impl(const void* const* peers, const void* multicast, void* const* peer_flags, int world, int rank,
+                                     int slot, unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
+                                     void* overflow_u8, void* status_i32, double timeout_s, void* stream);
+
 extern "C" int bmt_fused_reduce_scatter(const void* const* peers, void* const* peer_flags, int world, int rank, int slot,
                                         unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
                                         void* overflow_u8, void* status_i32, double timeout_s, void* stream) {
+    return fused_reduce_scatter_impl(peers, nullptr, peer_flags, world, rank, slot, epoch, part, out, accumulate, scale, dtype,
+                                     overflow_u8, status_i32, timeout_s, stream);
+}
+
+// The same reduction through the NVSwitch multicast address `multicast` of the full buffers (multimem.ld_reduce).
+extern "C" int bmt_fused_reduce_scatter_mc(const void* multicast, void* const* peer_flags, int world, int rank, int slot,
+                                           unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
+                                           void* overflow_u8, void* status_i32, double timeout_s, void* stream) {
+    if (!multicast) return -33;
+    return fused_reduce_scatter_impl(nullptr, multicast, peer_flags, world, rank, slot, epoch, part, out, accumulate, scale, dtype,
+                                     overflow_u8, status_i32, timeout_s, stream);
+}
+
+static int fused_reduce_scatter_impl(const void* const* peers, const void* multicast, void* const* peer_flags, int world, int rank,
+                                     int slot, unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
+                                     void* overflow_u8, void* status_i32, double timeout_s, void* stream) {
     if (world < 1 || world > 8) return -30;
     if (part % 8 != 0) return -31;
     RsArgs a;
     memset(&a, 0, sizeof(a));
-    for (int j = 0; j < world; ++j) { a.peer[j] = peers[j]; a.peer_flags[j] = (unsigned int*)peer_flags[j]; }
+    for (int j = 0; j < world; ++j) { a.peer[j] = peers ? peers[j] : nullptr; a.peer_flags[j] = (unsigned int*)peer_flags[j]; }
     a.world = world; a.rank = rank; a.slot = slot; a.epoch = epoch; a.part = part; a.out = out; a.accumulate = accumulate;
     a.scale = scale; a.overflow = (unsigned char*)overflow_u8; a.status = (int*)status_i32;
     a.limit_ns = (uint64_t)(timeout_s * 1e9);
@@ -295,6 +380,13 @@ extern "C" int bmt_fused_reduce_scatter(const void* const* peers, void* const* p
     if (blocks > 148 * 4) blocks = 148 * 4;
     if (blocks < 1) blocks = 1;
     cudaStream_t s = (cudaStream_t)stream;
+    if (multicast) {
+        if (dtype == BMT_DT_F16) fused_rs_mc_kernel<__half, 4><<<(unsigned)blocks, 256, 0, s>>>(a, (const __half*)multicast);
+        else if (dtype == BMT_DT_BF16) fused_rs_mc_kernel<__nv_bfloat16, 4><<<(unsigned)blocks, 256, 0, s>>>(a, (const __nv_bfloat16*)multicast);
+        else return -32;
+        bmt_count_launch(1);
+        return (int)cudaGetLastError();
+    }
     if (dtype == BMT_DT_F16) launch_fused_rs<__half>(a, (unsigned)blocks, s);
     else if (dtype == BMT_DT_BF16) launch_fused_rs<__nv_bfloat16>(a, (unsigned)blocks, s);
     else return -32;

@@ -3,7 +3,9 @@
 The reference exposes NCCL on torch storages (``bmtrain/nccl/__init__.py:7-336``):
 ``allReduce(src, dst, op, comm)``, ``allGather``, ``reduceScatter``,
 ``broadcast``, ``reduce``, ``send``, ``recv``, ``groupStart/groupEnd`` and the
-communicator helpers.  Here the same functions accept tensors (or anything
+communicator helpers.  ``bmtrain_b200.nccl.native.NativeCommunicator`` is the
+library's own C++ NCCL binding (non-blocking communicators with error polling
+and abort); every function below takes one of those as well.  Here the same functions accept tensors (or anything
 with ``.view(-1)``; a typed storage is wrapped) and run on a
 :class:`~bmtrain_b200.comm.Communicator`, i.e. on NCCL over NVLink when the
 ranks own GPUs and on gloo otherwise.

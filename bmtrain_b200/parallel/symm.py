@@ -99,6 +99,41 @@ class SymmetricBuffer:
             self.local_ptr = 0
 
 
+class MulticastBuffer:
+    """Symmetric buffer backed by CUDA virtual-memory allocations that are also bound to an NVSwitch multicast object:
+    ``ptrs[j]`` is rank j's copy as seen from this process, ``mc_ptr`` the multicast address (a ``multimem`` load from it
+    returns the sum over all copies, a ``multimem`` store writes all of them).  Allocation, handle exchange and multicast
+    binding are done by ``torch.distributed._symmetric_memory`` over the communicator's process group; the kernels that
+    use the addresses are this library's.  Same interface as :class:`SymmetricBuffer`."""
+
+    def __init__(self, comm: Communicator, nbytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.comm, self.nbytes = comm, int(nbytes)
+        self._bytes = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=config["device"])
+        self._handle = symm_mem.rendezvous(self._bytes, comm.group)
+        self.ptrs: List[int] = [int(p) for p in self._handle.buffer_ptrs]
+        self.local_ptr = self.ptrs[comm.rank]
+        self.mc_ptr = int(self._handle.multicast_ptr) if self._handle.has_multicast_support(config["device"].type, config["device"].index) else 0
+
+    def tensor(self, dtype: torch.dtype, numel: int, byte_offset: int = 0) -> torch.Tensor:
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        return self._bytes[byte_offset:byte_offset + nbytes].view(dtype)
+
+    def ptr_table(self, byte_offset: int = 0):
+        return (ctypes.c_void_p * self.comm.size)(*[p + byte_offset for p in self.ptrs])
+
+    def close(self) -> None:
+        self._handle = None
+        self._bytes = None
+        self.local_ptr = 0
+
+
+def nvls_wanted() -> bool:
+    """``BMT_NVLS=1``: gradient staging buffers are multicast-bound and the fused reduce-scatter sums inside the switch."""
+    return os.environ.get("BMT_NVLS", "0") == "1"
+
+
 class StreamWork:
     """Handle whose ``wait()`` makes the current stream wait for an event (same contract as a c10d work object)."""
 
@@ -125,6 +160,7 @@ class PeerRuntime:
         self.slots: Dict[Tuple, SymmetricBuffer] = {}
         self._counters: Dict[Tuple, torch.Tensor] = {}
         self.cache: Dict[Tuple, object] = {}
+        self._multicast_ok = nvls_wanted()
         self.timeout_s = float(os.environ.get("BMT_PEER_TIMEOUT", "10"))
         self.stream = torch.cuda.Stream(priority=-1)
 
@@ -140,15 +176,29 @@ class PeerRuntime:
         self.epochs[row] = self.epochs.get(row, 0) + 1
         return self.epochs[row]
 
-    def slot(self, key: Tuple, nbytes: int) -> SymmetricBuffer:
-        """Symmetric staging buffer for ``key`` (allocated collectively on first use, regrown when too small)."""
+    def slot(self, key: Tuple, nbytes: int, multicast: bool = False) -> SymmetricBuffer:
+        """Symmetric staging buffer for ``key`` (allocated collectively on first use, regrown when too small).
+        ``multicast``: bind it to an NVSwitch multicast object when the platform offers one (see MulticastBuffer)."""
         buf = self.slots.get(key)
         if buf is None or buf.nbytes < nbytes:
             if buf is not None:
                 torch.cuda.synchronize()
                 self.comm.barrier()
                 buf.close()
-            buf = SymmetricBuffer(self.comm, nbytes)
+            buf = None
+            if multicast and self._multicast_ok:
+                try:
+                    buf = MulticastBuffer(self.comm, nbytes)
+                    good = 1 if buf.mc_ptr else 0
+                except Exception:
+                    good = 0
+                flag = torch.tensor([good], dtype=torch.int32, device=config["device"])
+                self.comm.all_reduce(flag, "min")
+                if int(flag.item()) == 0:   # some rank cannot: everybody uses plain peer memory for this and later slots
+                    self._multicast_ok = False
+                    buf = None
+            if buf is None:
+                buf = SymmetricBuffer(self.comm, nbytes)
             self.slots[key] = buf
         return buf
 
@@ -203,6 +253,13 @@ class PeerRuntime:
             # cross-rank hand-shake is done by one CTA, the reduction kernel itself then never waits
             self.signal_wait(row, epoch, signal=True, wait=True)
             epoch = 0
+        if getattr(full, "mc_ptr", 0):
+            _native.check(lib.bmt_fused_reduce_scatter_mc(
+                ctypes.c_void_p(full.mc_ptr), self.flag_ptrs, ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank), ctypes.c_int(row),
+                ctypes.c_uint(epoch), ctypes.c_int64(part), _native.ptr(out), ctypes.c_int(int(accumulate)), ctypes.c_float(scale),
+                ctypes.c_int(dt), _native.ptr(self.overflow), _native.ptr(self.status), ctypes.c_double(self.timeout_s),
+                _native.stream_handle()), "fused reduce-scatter kernel (multimem)")
+            return
         _native.check(lib.bmt_fused_reduce_scatter(
             full.ptr_table(), self.flag_ptrs, ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank), ctypes.c_int(row),
             ctypes.c_uint(epoch), ctypes.c_int64(part), _native.ptr(out), ctypes.c_int(int(accumulate)), ctypes.c_float(scale),
