@@ -65,6 +65,7 @@ def main():
     ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--compare-library", action="store_true", help="gemm: also time torch.matmul (cuBLAS) on the same operands")
     args = ap.parse_args()
     dt = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     hbm, tflops, src = peaks()
@@ -85,8 +86,14 @@ def main():
             fn = lambda: G.gemm_tn(a, b)
         ms = time_it(fn, args.iters, flush)
         ach = 2.0 * m * n * k / ms / 1e9
-        print(json.dumps({"op": f"gemm_{args.layout}", "m": m, "n": n, "k": k, "dtype": args.dtype, "ms": ms,
-                          "tflops": ach, "frac_of_peak": ach / tflops, "peak_source": src}))
+        out = {"op": f"gemm_{args.layout}", "m": m, "n": n, "k": k, "dtype": args.dtype, "ms": ms,
+               "tflops": ach, "frac_of_peak": ach / tflops, "peak_source": src}
+        if args.compare_library:
+            # the library GEMM (cuBLAS through torch.matmul) on the same operands: a yardstick, never on a product path
+            lib_fn = {"nt": lambda: torch.matmul(a, b.t()), "nn": lambda: torch.matmul(a, b), "tn": lambda: torch.matmul(a.t(), b)}[args.layout]
+            lib_ms = time_it(lib_fn, args.iters, flush)
+            out.update({"library_ms": lib_ms, "vs_library": lib_ms / ms})
+        print(json.dumps(out))
     elif args.op == "adam":
         n = args.n
         p32 = torch.randn(n, device=dev)

@@ -2,12 +2,14 @@
 //
 // Forward, one CTA per (128 query rows, head, sample):
 //   warp 0      TMA producer: Q once, then the K and V tiles of 128 keys through two-stage rings
-//   warp 1      MMA issuer (one thread): S_j = Q K_j^T into tensor memory (two S buffers), O_j = P_j V_j (two O buffers);
-//               S_{j+1} is issued before O_j so that the tensor core works while the softmax warps are busy with S_j
-//   warps 2..5  softmax: one thread per query row reads its row of S_j from tensor memory (tcgen05.ld), applies the masks,
-//               keeps the running maximum and sum, writes P_j = exp2(..) as fp16/bf16 into shared memory in the
-//               128-byte-swizzled K-major layout the MMA reads, and folds the finished O_{j-1} into its fp32 accumulator
-//               row (rescaled when the maximum moved).  The epilogue normalises and stores the row and its log-sum-exp.
+//   warp 1      MMA issuer (one thread): S_j = Q K_j^T into tensor memory (two S buffers), O += P_j V_j into one fp32
+//               accumulator in tensor memory; S_{j+1} is issued before P_j V_j so that the tensor core works while the
+//               softmax warps are busy with S_j
+//   warps 2..5  softmax: one thread per query row reads its whole row of S_j from tensor memory in one round trip
+//               (tcgen05.ld), applies the masks, keeps the sum and a reference maximum, writes P_j = exp2(..) as
+//               fp16/bf16 into shared memory in the 128-byte-swizzled K-major layout the MMA reads.  The reference
+//               maximum follows the true one lazily; only when it moves is the accumulator rescaled (tcgen05.ld / st).
+//               The epilogue normalises and stores the row and its log-sum-exp.
 // Masks: causal (key j visible to query i iff j <= i + sk - sq), per-sample key counts, dense boolean (b, sq, sk).
 // Grouped-query attention: kv head = head / (h / hk).  Head dims up to 128 (multiples of 16); tiles are padded with
 // zeros by TMA.  Every mbarrier wait is bounded; on expiry a status word is set and the CTA winds down.
@@ -49,7 +51,7 @@ struct AttnParams {
 
 struct AttnShared {
     uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2];
-    uint64_t s_full[2], s_free[2], p_ready, p_free, o_full[2], o_free[2];
+    uint64_t s_full[2], s_free[2], p_ready, p_free, o_full;
     uint32_t tmem_base;
     int failed;
 };
@@ -131,10 +133,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         mbar_init(&sh->q_full, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh->k_full[i], 1); mbar_init(&sh->v_full[i], 1); mbar_init(&sh->k_empty[i], 1); mbar_init(&sh->v_empty[i], 1);
-            mbar_init(&sh->s_full[i], 1); mbar_init(&sh->s_free[i], 4); mbar_init(&sh->o_full[i], 1); mbar_init(&sh->o_free[i], 4);
+            mbar_init(&sh->s_full[i], 1); mbar_init(&sh->s_free[i], 4);
         }
         mbar_init(&sh->p_ready, 4);
         mbar_init(&sh->p_free, 1);
+        mbar_init(&sh->o_full, 1);
         sh->failed = 0;
         fence_barrier_init();
     }
@@ -143,7 +146,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
-    const uint32_t tmem_o = tmem + 256;             // S buffers: columns [0,128) and [128,256); O buffers behind them
+    const uint32_t tmem_o = tmem + 256;             // S buffers: columns [0,128) and [128,256); the O accumulator behind them
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------------ TMA producer
@@ -178,21 +181,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
                 const int st = i & 1;
                 const uint32_t ph = (uint32_t)((i >> 1) & 1);
                 if (!mbar_wait(&sh->v_full[st], ph)) { fail(sh, 4); return false; }
+                // P_i is in shared memory and, if the row maxima moved, the accumulator has been rescaled by its owners
                 if (!mbar_wait(&sh->p_ready, (uint32_t)(i & 1))) { fail(sh, 5); return false; }
-                if (!mbar_wait(&sh->o_free[st], ph ^ 1)) { fail(sh, 6); return false; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_o + st * HD;
+                const uint32_t d_tmem = tmem_o;
 #pragma unroll
                 for (int ks = 0; ks < TILE / 16; ++ks) {
                     // A = P (128 x 128 keys, K-major): chunk ks / 4, 32 bytes per step inside the swizzle row
                     // B = V (128 keys x HD, head dim contiguous = MN-major): 16 key rows per step, chunks of 64 columns apart by CHUNK
                     const uint64_t ad = pack_desc(desc_lo(sP + (ks >> 2) * CHUNK + (ks & 3) * 32, 0), hi);
                     const uint64_t bd = pack_desc(desc_lo(sV + st * TB + ks * 2048, CHUNK), hi);
-                    umma_f16(d_tmem, ad, bd, p.idesc_pv, ks != 0 ? 1u : 0u);
+                    umma_f16(d_tmem, ad, bd, p.idesc_pv, (i | ks) != 0 ? 1u : 0u);   // O accumulates over all key tiles
                 }
                 umma_commit(&sh->v_empty[st]);
                 umma_commit(&sh->p_free);
-                umma_commit(&sh->o_full[st]);
+                umma_commit(&sh->o_full);
                 return true;
             };
             for (int j = 0; j < J && ok; ++j) {
@@ -222,10 +225,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const uint8_t* mrow = (p.mask && row_ok) ? p.mask + ((int64_t)b * p.sq + qi) * p.sk : nullptr;
         const int64_t causal_last = p.causal ? qi + p.causal_off : p.sk;   // last visible key of this row under the causal rule
-        float o_acc[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        // m_ref: the maximum the exponents are taken against.  It follows the running maximum lazily: only when that
+        // has grown by more than 8 (in base-2 exponent units) is the accumulator in tensor memory rescaled -- probabilities
+        // stay below 2^8, sums are fp32 -- so that after the first few tiles a tile costs one round trip to tensor memory.
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < J && ok; ++j) {
             const int sb = j & 1;
@@ -234,117 +237,114 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             const int64_t kv0 = (int64_t)j * TILE;
             const bool need_mask = (kv0 + TILE > kv_end) || (p.causal && kv0 + TILE - 1 > q0 + p.causal_off) || mrow != nullptr;
             const uint32_t s_addr = tmem + lane_addr + sb * TILE;
+            uint32_t r[TILE / 32][32];
+#pragma unroll
+            for (int c4 = 0; c4 < TILE / 32; ++c4) tmem_ld32(s_addr + c4 * 32, r[c4]);
+            tmem_ld_wait();
+            // the scores are in registers: the S buffer may take the tile after next
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->s_free[sb]);
             uint32_t vis[TILE / 32];
+#pragma unroll
+            for (int c4 = 0; c4 < TILE / 32; ++c4) vis[c4] = 0xffffffffu;
             if (need_mask) {
                 const int64_t limit = kv_end < causal_last + 1 ? kv_end : causal_last + 1;
 #pragma unroll
                 for (int c4 = 0; c4 < TILE / 32; ++c4) vis[c4] = visible_bits(kv0 + c4 * 32, limit, mrow);
             }
-            // pass 1: row maximum of the visible scores
             float mt = -INFINITY;
 #pragma unroll
-            for (int c4 = 0; c4 < TILE / 32; ++c4) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + c4 * 32, r);
-                tmem_ld_wait();
-                if (need_mask) {
+            for (int c4 = 0; c4 < TILE / 32; ++c4)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if ((vis[c4] >> i) & 1u) mt = fmaxf(mt, __uint_as_float(r[i]));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mt = fmaxf(mt, __uint_as_float(r[i]));
-                }
+                for (int i = 0; i < 32; ++i)
+                    if ((vis[c4] >> i) & 1u) mt = fmaxf(mt, __uint_as_float(r[c4][i]));
+            // move the reference maximum?  (first visible score of the row, or growth beyond the threshold)
+            float alpha = 1.f;
+            bool move = false;
+            if (mt != -INFINITY) {
+                if (m_ref == -INFINITY) { m_ref = mt; }               // nothing accumulated yet: O and l are zero
+                else if ((mt - m_ref) * p.sl2 > 8.f) { alpha = ex2((m_ref - mt) * p.sl2); m_ref = mt; move = true; }
             }
-            const float m_new = fmaxf(m_run, mt);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = ex2((m_run - m_use) * p.sl2);        // 0 while nothing was visible so far
-            const float neg_m = -m_use * p.sl2;
-            // the previous P tile must have been consumed by its MMAs before it is overwritten
+            // the previous tile's MMAs have read P (and, when rescaling, must have finished adding into O)
             if (!warp_wait(&sh->p_free, (uint32_t)((j & 1) ^ 1), lane)) { if (lane == 0) fail(sh, 10); ok = false; break; }
-            // pass 2: probabilities -> shared memory (swizzled K-major), row sum
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                // rescale this warp's 32 rows of the accumulator (lanes whose maximum did not move multiply by one)
+                tc_fence_after();
+                l_run *= alpha;
+#pragma unroll
+                for (int c4 = 0; c4 < HD / 32; ++c4) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + lane_addr + c4 * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tmem_o + lane_addr + c4 * 32, o);
+                }
+                tmem_st_wait();
+            } else {
+                l_run *= alpha;
+            }
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref * p.sl2;
             float rowsum = 0.f;
 #pragma unroll
             for (int c4 = 0; c4 < TILE / 32; ++c4) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + c4 * 32, r);
-                tmem_ld_wait();
-                float pv[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float e = ex2(fmaf(__uint_as_float(r[i]), p.sl2, neg_m));
-                    if (need_mask && !((vis[c4] >> i) & 1u)) e = 0.f;
-                    pv[i] = e;
-                    rowsum += e;
-                }
                 const uint32_t base = sP + (uint32_t)(c4 >> 1) * CHUNK + (uint32_t)row * 128;
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
+                    float pv[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float e = ex2(fmaf(__uint_as_float(r[c4][8 * t + i]), p.sl2, neg_m));
+                        if (!((vis[c4] >> (8 * t + i)) & 1u)) e = 0.f;
+                        pv[i] = e;
+                        rowsum += e;
+                    }
                     const uint32_t piece = (uint32_t)(((c4 & 1) * 4 + t) ^ (row & 7));
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (piece << 4)),
-                                 "r"(pack2<T>(pv[8 * t], pv[8 * t + 1])), "r"(pack2<T>(pv[8 * t + 2], pv[8 * t + 3])),
-                                 "r"(pack2<T>(pv[8 * t + 4], pv[8 * t + 5])), "r"(pack2<T>(pv[8 * t + 6], pv[8 * t + 7])) : "memory");
+                                 "r"(pack2<T>(pv[0], pv[1])), "r"(pack2<T>(pv[2], pv[3])),
+                                 "r"(pack2<T>(pv[4], pv[5])), "r"(pack2<T>(pv[6], pv[7])) : "memory");
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores before the MMA's async-proxy reads
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&sh->p_ready); mbar_arrive(&sh->s_free[sb]); }
-            l_run = l_run * alpha + rowsum;
-            m_run = m_new;
-            // fold the previous tile's product into the accumulator row; both move to the new maximum
-            if (j >= 1) {
-                const int ob = (j - 1) & 1;
-                if (!warp_wait(&sh->o_full[ob], (uint32_t)(((j - 1) >> 1) & 1), lane)) { if (lane == 0) fail(sh, 11); ok = false; break; }
-                tc_fence_after();
-                const uint32_t o_addr = tmem_o + lane_addr + ob * HD;
-#pragma unroll
-                for (int c4 = 0; c4 < HD / 32; ++c4) {
-                    uint32_t r[32];
-                    tmem_ld32(o_addr + c4 * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o_acc[c4 * 32 + i] = (o_acc[c4 * 32 + i] + __uint_as_float(r[i])) * alpha;
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->o_free[ob]);
-            }
+            if (lane == 0) mbar_arrive(&sh->p_ready);
+            l_run += rowsum;
         }
         if (ok && J > 0) {
-            const int ob = (J - 1) & 1;
-            if (!warp_wait(&sh->o_full[ob], (uint32_t)(((J - 1) >> 1) & 1), lane)) { if (lane == 0) fail(sh, 12); ok = false; }
-            else {
-                tc_fence_after();
-                const uint32_t o_addr = tmem_o + lane_addr + ob * HD;
-#pragma unroll
-                for (int c4 = 0; c4 < HD / 32; ++c4) {
-                    uint32_t r[32];
-                    tmem_ld32(o_addr + c4 * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o_acc[c4 * 32 + i] += __uint_as_float(r[i]);
-                }
-                tc_fence_before();
-            }
+            if (!warp_wait(&sh->o_full, (uint32_t)((J - 1) & 1), lane)) { if (lane == 0) fail(sh, 12); ok = false; }
         }
-        if (ok && row_ok) {
+        if (ok) {
+            // normalise and store the row (the tensor-memory loads are warp-wide; only the stores depend on the row)
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             T* orow = (T*)p.o + (int64_t)b * p.o_batch + qi * p.o_tok + (int64_t)head * p.o_head;
+            tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
-                if (c * 8 < p.d) {
-                    float v8[8];
+            for (int c4 = 0; c4 < HD / 32; ++c4) {
+                uint32_t o[32];
+                if (J > 0) {
+                    tmem_ld32(tmem_o + lane_addr + c4 * 32, o);
+                    tmem_ld_wait();
+                } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v8[i] = o_acc[c * 8 + i] * inv;
-                    bmt::Vec16<T> o;
+                    for (int i = 0; i < 32; ++i) o[i] = 0u;
+                }
+                if (row_ok) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) o.v[i] = bmt::Cvt<T>::from_f(v8[i]);
-                    bmt::st16(orow + c * 8, o);
+                    for (int t = 0; t < 4; ++t) {
+                        if (c4 * 32 + t * 8 < p.d) {
+                            bmt::Vec16<T> ov;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) ov.v[i] = bmt::Cvt<T>::from_f(__uint_as_float(o[t * 8 + i]) * inv);
+                            bmt::st16(orow + c4 * 32 + t * 8, ov);
+                        }
+                    }
                 }
             }
-            if (p.lse)
-                p.lse[((int64_t)b * p.h + head) * p.sq + qi] = l_run > 0.f ? (m_run * p.sl2 + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+            tc_fence_before();
+            if (row_ok && p.lse)
+                p.lse[((int64_t)b * p.h + head) * p.sq + qi] = l_run > 0.f ? (m_ref * p.sl2 + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
         }
     }
 
@@ -536,31 +536,40 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             const bool need_mask = (kv0 + TILE > kv_valid) || (p.causal && kv0 + TILE - 1 > q0 + p.causal_off) || mrow != nullptr;
             if (!warp_wait(&sh->sdp_full, ph, lane)) { if (lane == 0) fail_bwd(sh, 6); ok = false; break; }
             tc_fence_after();
+            // A tensor-memory load costs a round trip of a few hundred nanoseconds however wide it is, so the loads of 64
+            // columns of S and of dP are issued together and waited for once (two round trips per tile).
 #pragma unroll
-            for (int c4 = 0; c4 < TILE / 32; ++c4) {
-                uint32_t rs[32], rd[32];
-                tmem_ld32(tmem + lane_addr + c4 * 32, rs);
-                tmem_ld32(tmem + lane_addr + C_DP + c4 * 32, rd);
-                tmem_ld_wait();
-                float pv[32], ds[32];
-                uint32_t bits = alive ? 0xffffffffu : 0u;
-                if (need_mask && alive) bits = visible_bits(kv0 + c4 * 32, kv_valid < causal_last + 1 ? kv_valid : causal_last + 1, mrow);
+            for (int half = 0; half < 2; ++half) {
+                uint32_t rs[2][32], rd[2][32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float e = ((bits >> i) & 1u) ? ex2(fmaf(__uint_as_float(rs[i]), p.sl2, nlse)) : 0.f;
-                    pv[i] = e;
-                    ds[i] = e * (__uint_as_float(rd[i]) - delta_r) * p.scale;
+                for (int u = 0; u < 2; ++u) {
+                    tmem_ld32(tmem + lane_addr + (half * 2 + u) * 32, rs[u]);
+                    tmem_ld32(tmem + lane_addr + C_DP + (half * 2 + u) * 32, rd[u]);
                 }
-                const uint32_t off = (uint32_t)(c4 >> 1) * CHUNK + (uint32_t)row * 128;
+                tmem_ld_wait();
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const uint32_t piece = (uint32_t)(((c4 & 1) * 4 + t) ^ (row & 7)) << 4;
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off + piece),
-                                 "r"(pack2<T>(pv[8 * t], pv[8 * t + 1])), "r"(pack2<T>(pv[8 * t + 2], pv[8 * t + 3])),
-                                 "r"(pack2<T>(pv[8 * t + 4], pv[8 * t + 5])), "r"(pack2<T>(pv[8 * t + 6], pv[8 * t + 7])) : "memory");
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sdS + off + piece),
-                                 "r"(pack2<T>(ds[8 * t], ds[8 * t + 1])), "r"(pack2<T>(ds[8 * t + 2], ds[8 * t + 3])),
-                                 "r"(pack2<T>(ds[8 * t + 4], ds[8 * t + 5])), "r"(pack2<T>(ds[8 * t + 6], ds[8 * t + 7])) : "memory");
+                for (int u = 0; u < 2; ++u) {
+                    const int c4 = half * 2 + u;
+                    uint32_t bits = alive ? 0xffffffffu : 0u;
+                    if (need_mask && alive) bits = visible_bits(kv0 + c4 * 32, kv_valid < causal_last + 1 ? kv_valid : causal_last + 1, mrow);
+                    const uint32_t off = (uint32_t)half * CHUNK + (uint32_t)row * 128;
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        float pv[8], ds[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float e = ((bits >> (8 * t + i)) & 1u) ? ex2(fmaf(__uint_as_float(rs[u][8 * t + i]), p.sl2, nlse)) : 0.f;
+                            pv[i] = e;
+                            ds[i] = e * (__uint_as_float(rd[u][8 * t + i]) - delta_r) * p.scale;
+                        }
+                        const uint32_t piece = (uint32_t)((u * 4 + t) ^ (row & 7)) << 4;
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off + piece),
+                                     "r"(pack2<T>(pv[0], pv[1])), "r"(pack2<T>(pv[2], pv[3])),
+                                     "r"(pack2<T>(pv[4], pv[5])), "r"(pack2<T>(pv[6], pv[7])) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sdS + off + piece),
+                                     "r"(pack2<T>(ds[0], ds[1])), "r"(pack2<T>(ds[2], ds[3])),
+                                     "r"(pack2<T>(ds[4], ds[5])), "r"(pack2<T>(ds[6], ds[7])) : "memory");
+                    }
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -570,22 +579,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             if (!warp_wait(&sh->dq_full, ph, lane)) { if (lane == 0) fail_bwd(sh, 7); ok = false; break; }
             tc_fence_after();
             float* dq_row = p.dq_acc + (((int64_t)b * p.sq + qi) * p.h + head) * p.d;
+            {
+                uint32_t r[HD / 32][32];
 #pragma unroll
-            for (int c4 = 0; c4 < HD / 32; ++c4) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_addr + C_DQ + c4 * 32, r);
+                for (int c4 = 0; c4 < HD / 32; ++c4) tmem_ld32(tmem + lane_addr + C_DQ + c4 * 32, r[c4]);
                 tmem_ld_wait();
+                // the values are in registers: the tensor memory may be overwritten by the next tile's MMAs while the
+                // reductions below are still being issued
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->tmem_free);
                 if (row_ok) {
 #pragma unroll
-                    for (int t = 0; t < 8; ++t)
-                        if (c4 * 32 + t * 4 < p.d)
-                            red_add_v4(dq_row + c4 * 32 + t * 4, __uint_as_float(r[4 * t]), __uint_as_float(r[4 * t + 1]),
-                                       __uint_as_float(r[4 * t + 2]), __uint_as_float(r[4 * t + 3]));
+                    for (int c4 = 0; c4 < HD / 32; ++c4)
+#pragma unroll
+                        for (int t = 0; t < 8; ++t)
+                            if (c4 * 32 + t * 4 < p.d)
+                                red_add_v4(dq_row + c4 * 32 + t * 4, __uint_as_float(r[c4][4 * t]), __uint_as_float(r[c4][4 * t + 1]),
+                                           __uint_as_float(r[c4][4 * t + 2]), __uint_as_float(r[c4][4 * t + 3]));
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->tmem_free);
         }
         // dK, dV rows of this CTA's keys (zeros when no query sees them).  The tensor-memory loads are warp-wide, so every
         // lane takes part in them; only the stores depend on the row.

@@ -222,8 +222,41 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
         if self._gpu_pipe is not None:
             self._gpu_pipe["down"].synchronize()
 
+    # ------------------------------------------------------------ host memory
+    def host_bytes(self) -> int:
+        """Host memory this rank's optimizer needs: fp32 master, two moments, and the half-precision staging copies of
+        gradient and parameter (16 bytes per half-precision parameter element, 16 per fp32 one)."""
+        total = 0
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p.requires_grad:
+                    total += p.numel() * (12 + (4 if p.dtype == torch.float32 else 4))
+        return total
+
+    def _check_host_memory(self) -> None:
+        """Before the first allocation: refuse with a clear message when the host cannot hold the state of all ranks of
+        this machine (page-locking more memory than there is takes the machine down long before an allocation fails)."""
+        from ..global_var import config
+
+        if getattr(self, "_host_checked", False):
+            return
+        self._host_checked = True
+        try:
+            with open("/proc/meminfo") as f:
+                info = dict(line.split(":", 1) for line in f)
+            avail = int(info["MemAvailable"].split()[0]) * 1024
+        except (OSError, KeyError, ValueError):
+            return
+        need = self.host_bytes() * max(1, int(config.get("local_size", 1) or 1))
+        if need > 0.9 * avail:
+            raise MemoryError(
+                f"AdamOffloadOptimizer needs about {need / 2 ** 30:.0f} GiB of host memory on this machine "
+                f"({self.host_bytes() / 2 ** 30:.1f} GiB per rank x {config.get('local_size', 1)} ranks) but only "
+                f"{avail / 2 ** 30:.0f} GiB are available; use more machines, a smaller model, or AdamOptimizer")
+
     # ------------------------------------------------------------------ state
     def _init_state(self, p):
+        self._check_host_memory()
         state = self.state[p]
         pin = p.is_cuda
         state["step"] = 0
@@ -388,7 +421,8 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
             used = sum(3 * 4 * q.numel() for q in self._ahead_owners)
             if used + need > self._ahead_budget:
                 return
-            state["_ahead_state"] = {k: torch.empty_like(state[k], pin_memory=False) for k in _STATE_KEYS}
+            # touched here, once: the first write to fresh pages would otherwise cost page faults inside a later step
+            state["_ahead_state"] = {k: torch.empty_like(state[k], pin_memory=False).fill_(0.0) for k in _STATE_KEYS}
             self._ahead_owners.append(p)
         key = self._hyper(p, state, group, self._announced_scale)
         n = p.numel()

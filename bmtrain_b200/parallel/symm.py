@@ -114,7 +114,7 @@ class MulticastBuffer:
         self._handle = symm_mem.rendezvous(self._bytes, comm.group)
         self.ptrs: List[int] = [int(p) for p in self._handle.buffer_ptrs]
         self.local_ptr = self.ptrs[comm.rank]
-        self.mc_ptr = int(self._handle.multicast_ptr) if self._handle.has_multicast_support(config["device"].type, config["device"].index) else 0
+        self.mc_ptr = int(self._handle.multicast_ptr or 0)
 
     def tensor(self, dtype: torch.dtype, numel: int, byte_offset: int = 0) -> torch.Tensor:
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
@@ -190,8 +190,13 @@ class PeerRuntime:
                 try:
                     buf = MulticastBuffer(self.comm, nbytes)
                     good = 1 if buf.mc_ptr else 0
-                except Exception:
-                    good = 0
+                    why = "the platform reports no multicast support"
+                except Exception as exc:
+                    good, why = 0, f"{type(exc).__name__}: {exc}"
+                if not good and self.comm.rank == 0:
+                    import sys
+
+                    print(f"bmtrain_b200: multicast-bound buffers are not used on {self.comm.name} ({why})", file=sys.stderr)
                 flag = torch.tensor([good], dtype=torch.int32, device=config["device"])
                 self.comm.all_reduce(flag, "min")
                 if int(flag.item()) == 0:   # some rank cannot: everybody uses plain peer memory for this and later slots

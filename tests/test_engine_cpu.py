@@ -599,3 +599,17 @@ def test_reference_named_internals(bmt_cpu):
     out = blk._module(xin)
     (out,) = PostHookFunc.apply(blk, out)
     assert torch.allclose(out, want)
+
+
+def test_offload_optimizer_host_memory_sizing(bmt_cpu, monkeypatch):
+    """The offloading optimizer states what it needs in host memory and refuses, before allocating anything, when the
+    machine cannot hold the state of all its ranks."""
+    bmt = bmt_cpu
+    p = torch.nn.Parameter(torch.zeros(1000, dtype=torch.float32))
+    opt = bmt.optim.AdamOffloadOptimizer([p], lr=1e-3)
+    assert opt.host_bytes() == 1000 * 16
+    monkeypatch.setattr(opt, "host_bytes", lambda: 1 << 60)
+    p.grad = torch.ones_like(p)
+    with pytest.raises(MemoryError):
+        opt.step()
+    assert len(opt.state[p]) == 0
