@@ -425,6 +425,7 @@ def main():
         torch.cuda.synchronize()
         sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 and os.environ.get("BMT_BENCH_NO_CLOCKS") != "1" else None
         l0 = launch_count()
+        stats0 = dict(getattr(om.optimizers[0], "stats", {}))
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         start.record()
@@ -445,8 +446,11 @@ def main():
         if world > 1:
             t = bmt.distributed.all_reduce(t, "max")  # same call in both arms (each arm's own collective layer)
         clocks = sampler.stop() if sampler else None
+        now = dict(getattr(om.optimizers[0], "stats", {}))
+        offload_stats.append({k: now[k] - stats0.get(k, 0) for k in now})
         return float(t[0]), int(t[1]), launch_count() - l0, clocks, float(t[2])
 
+    offload_stats = []   # per timed pass: parameter updates computed during backward (queued / adopted / re-queued / dropped)
     ms, skip_dev, launches, clocks, _ = timed(False)
     ms_e2e, skip_e2e, _, _, final_loss = timed(True)
 
@@ -509,6 +513,7 @@ def main():
             "gpu_launches": launches,
             "overflow_skipped_steps": {"device_timed": skip_dev, "e2e": skip_e2e},
             "final_loss": round(final_loss, 4),
+            "offload_stats": {"device_timed": offload_stats[0], "e2e": offload_stats[1]},
             "phase_ms": phase_ms,
             "exposed_comm_fraction": round(float(pt[3]) / (ms / args.steps), 4) if args.impl == "ours" else None,
             "timing_note": "value: max(CUDA events, wall clock) over K steps, each region starts and ends with the "

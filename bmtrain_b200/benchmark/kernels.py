@@ -1,6 +1,7 @@
 """Single-GPU kernel micro-benchmarks against the measured roofline.
 
     python -m bmtrain_b200.benchmark.kernels --op gemm --m 8192 --n 8192 --k 8192 --dtype bf16 --layout nt
+    python -m bmtrain_b200.benchmark.kernels --op gemm_block_shapes      # the 15 GEMMs of the benchmark block vs the library
     python -m bmtrain_b200.benchmark.kernels --op adam --n 268435456
     python -m bmtrain_b200.benchmark.kernels --op norm|ce|softmax ...
     python -m bmtrain_b200.benchmark.kernels --op attention --batch 2 --seq 4096 --heads 20 --kv-heads 20 --head-dim 128
@@ -49,7 +50,7 @@ def time_it(fn, iters: int, flush: bool) -> float:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "adam", "norm", "norm_bwd", "rmsnorm", "ce", "ce_bwd", "softmax", "softmax_bwd", "embedding",
+    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_block_shapes", "adam", "norm", "norm_bwd", "rmsnorm", "ce", "ce_bwd", "softmax", "softmax_bwd", "embedding",
                                                   "embedding_bwd", "infnan", "sqnorm", "colsum", "rope", "swiglu", "attention"])
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=4096)
@@ -94,6 +95,60 @@ def main():
             lib_ms = time_it(lib_fn, args.iters, flush)
             out.update({"library_ms": lib_ms, "vs_library": lib_ms / ms})
         print(json.dumps(out))
+    elif args.op == "gemm_block_shapes":
+        # forward / dgrad / wgrad GEMMs of one block of the headline model (GPT d2560, FFN 8192, vocab 10240) at --m tokens
+        # (default here: 1024 = batch 2 x 512), each as 20 back-to-back launches in a CUDA graph (launch gaps excluded, L2
+        # warm: weights of one GEMM fit), against torch.matmul (cuBLAS) the same way
+        t = args.m if args.m != 8192 else 1024
+        d_, dff, voc = 2560, 8192, 10240
+        shapes = [("nt", t, 3 * d_, d_), ("nt", t, d_, d_), ("nt", t, dff, d_), ("nt", t, d_, dff), ("nt", t, voc, d_),
+                  ("nn", t, dff, d_), ("nn", t, d_, dff), ("nn", t, d_, d_), ("nn", t, d_, 3 * d_), ("nn", t, d_, voc),
+                  ("tn", d_, dff, t), ("tn", dff, d_, t), ("tn", d_, d_, t), ("tn", 3 * d_, d_, t), ("tn", voc, d_, t)]
+        side = torch.cuda.Stream()
+
+        def graph_time(fn):
+            with torch.cuda.stream(side):
+                for _ in range(5):
+                    fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(20):
+                        fn()
+            torch.cuda.synchronize()
+            g.replay()
+            torch.cuda.synchronize()
+            s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            g.replay()
+            g.replay()
+            e0.record()
+            torch.cuda.synchronize()
+            return s0.elapsed_time(e0) / 40
+
+        rows, tot_ours, tot_lib = [], 0.0, 0.0
+        for lay, m, n, k in shapes:
+            if lay == "nt":
+                a, b = torch.randn(m, k, device=dev, dtype=dt), torch.randn(n, k, device=dev, dtype=dt)
+                o = torch.empty(m, n, device=dev, dtype=dt)
+                f1, f2 = (lambda: G.gemm_nt(a, b, out=o)), (lambda: torch.matmul(a, b.t(), out=o))
+            elif lay == "nn":
+                a, b = torch.randn(m, k, device=dev, dtype=dt), torch.randn(k, n, device=dev, dtype=dt)
+                o = torch.empty(m, n, device=dev, dtype=dt)
+                f1, f2 = (lambda: G.gemm_nn(a, b, out=o)), (lambda: torch.matmul(a, b, out=o))
+            else:
+                a, b = torch.randn(k, m, device=dev, dtype=dt), torch.randn(k, n, device=dev, dtype=dt)
+                o = torch.empty(m, n, device=dev, dtype=dt)
+                f1, f2 = (lambda: G.gemm_tn(a, b, out=o)), (lambda: torch.matmul(a.t(), b, out=o))
+            ours, libt = graph_time(f1), graph_time(f2)
+            tot_ours += ours
+            tot_lib += libt
+            rows.append({"layout": lay, "m": m, "n": n, "k": k, "ours_us": round(ours * 1e3, 1), "library_us": round(libt * 1e3, 1),
+                         "ours_tflops": round(2.0 * m * n * k / ours / 1e9), "vs_library": round(libt / ours, 3)})
+        print(json.dumps({"op": "gemm_block_shapes", "tokens": t, "dtype": args.dtype, "shapes": rows,
+                          "sum_ours_us": round(tot_ours * 1e3, 1), "sum_library_us": round(tot_lib * 1e3, 1),
+                          "vs_library": round(tot_lib / tot_ours, 3)}))
     elif args.op == "adam":
         n = args.n
         p32 = torch.randn(n, device=dev)
@@ -204,9 +259,9 @@ def main():
             fn = (lambda: IN.multi_has_inf_nan([x], flag)) if args.op == "infnan" else (lambda: IN.multi_sq_norm([x], tot))
             nbytes = x.numel() * 2
         elif args.op == "colsum":
-            x, out = torch.randn(m, n, device=dev, dtype=dt), torch.empty(n, device=dev, dtype=dt)
-            fn = lambda: lib.bmt_colsum(ctypes.c_int64(m), ctypes.c_int64(n), _native.ptr(x), ctypes.c_int(code), _native.ptr(out),
-                                        _native.stream_handle())
+            from ..ops import gemm as G
+            x = torch.randn(m, n, device=dev, dtype=dt)
+            fn = lambda: G.bias_grad(x)
             nbytes = x.numel() * 2
         elif args.op == "rope":
             hk = args.kv_heads or args.heads

@@ -53,6 +53,10 @@ int bmt_norm_bwd(int64_t rows, int64_t d, const void* x, const void* dy, const v
 int bmt_norm_bwd_res(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms,
                      int dtype, int nblk, void* dx, void* partial_2xnblkxd_f32, void* dw, void* db, const void* dres, void* stream);
 
+int bmt_norm_bwd_ex(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms,
+                    int dtype, int nblk, void* dx, void* partial_2xnblkxd_f32, void* dw, void* db, const void* dres,
+                    int accumulate, void* stream);
+
 int bmt_embedding_fwd(int64_t tokens, int64_t d, const void* ids_i64, const void* weight, int dtype, void* out, void* stream);
 int bmt_embedding_bwd(int64_t tokens, int64_t d, const void* ids_i64, const void* grad, int dtype, void* acc_f32, void* stream);
 
@@ -64,6 +68,10 @@ int bmt_swiglu_fwd(int64_t rows, int64_t f, const void* x, int dtype, void* out,
 int bmt_swiglu_bwd(int64_t rows, int64_t f, const void* x, const void* g, int dtype, void* dx, void* stream);
 int bmt_gelu_fwd(int64_t n, const void* x, int dtype, void* out, void* stream);
 int bmt_colsum(int64_t m, int64_t n, const void* x, int dtype, void* out, void* stream);
+// Same with a row-split grid: `scratch` = 4 KB of zero-initialised ticket counters followed by room for the partial sums
+// (splits x n floats; the split count adapts to `scratch_bytes`); `accumulate`: out += column sums.
+int bmt_colsum_ex(int64_t m, int64_t n, const void* x, int dtype, void* out, int accumulate, void* scratch,
+                  int64_t scratch_bytes, void* stream);
 
 // Full description of one (optionally batched) GEMM launch; zero-initialise, then fill what is needed.
 typedef struct {
@@ -136,6 +144,9 @@ typedef struct {
     // fused attention backward scratch (used when the block carries lse): fp32, T*heads*d_head and batch*heads*seq
     void* dq_acc;
     void* delta;
+    int acc_small;            // bias and norm gradients are added to what d_*_b / d_ln*_w already hold
+    void* colsum_scratch;     // optional work space of bmt_colsum_ex (zero-initialised once), colsum_scratch_bytes large
+    int64_t colsum_scratch_bytes;
 } BmtGptBlockGrad;
 
 int bmt_gpt_block_forward(const BmtGptBlock* blk, void* stream);
@@ -230,8 +241,9 @@ int64_t bmt_offload_submit_uploads(const BmtOffloadJob* jobs, int n, void* h2d_s
 
 // Rotary position embedding on a packed (b, s, hk, g + 2, d) projection (csrc/elementwise.cu): split != 0 writes rotated q
 // (b, s, hk*g, d), rotated k and copied v (b, s, hk, d); split == 0 is the backward (q, k, v gradients -> packed gradient).
+// cos_sin: fp32 (cos, sin) pairs for every (position, frequency), (pos0 + s) x d/2 of them.
 int bmt_rope_qkv(int64_t batch, int64_t seq, int hk, int g, int d, void* packed, int64_t p_tok, int64_t p_batch, void* q, void* k,
-                 void* v, float theta, int64_t pos0, int split, int dtype, void* stream);
+                 void* v, const void* cos_sin, int64_t pos0, int split, int dtype, void* stream);
 
 // Fused attention forward (csrc/attn_sm100.cu): o = softmax(scale * q k^T + masks) v, lse = log-sum-exp per row.
 // q (b, sq, h, d), k / v (b, sk, hk, d), o (b, sq, h, d); *_strides = element strides {token, head, batch}, head dim

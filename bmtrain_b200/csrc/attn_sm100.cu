@@ -253,12 +253,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #pragma unroll
                 for (int c4 = 0; c4 < TILE / 32; ++c4) vis[c4] = visible_bits(kv0 + c4 * 32, limit, mrow);
             }
+            // tiles away from the diagonal and the ragged edge (the common case) skip the per-element visibility tests
             float mt = -INFINITY;
+            if (need_mask) {
 #pragma unroll
-            for (int c4 = 0; c4 < TILE / 32; ++c4)
+                for (int c4 = 0; c4 < TILE / 32; ++c4)
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if ((vis[c4] >> i) & 1u) mt = fmaxf(mt, __uint_as_float(r[c4][i]));
+                    for (int i = 0; i < 32; ++i)
+                        if ((vis[c4] >> i) & 1u) mt = fmaxf(mt, __uint_as_float(r[c4][i]));
+            } else {
+#pragma unroll
+                for (int c4 = 0; c4 < TILE / 32; ++c4)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mt = fmaxf(mt, __uint_as_float(r[c4][i]));
+            }
             // move the reference maximum?  (first visible score of the row, or growth beyond the threshold)
             float alpha = 1.f;
             bool move = false;
@@ -296,7 +304,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         float e = ex2(fmaf(__uint_as_float(r[c4][8 * t + i]), p.sl2, neg_m));
-                        if (!((vis[c4] >> (8 * t + i)) & 1u)) e = 0.f;
+                        if (need_mask && !((vis[c4] >> (8 * t + i)) & 1u)) e = 0.f;
                         pv[i] = e;
                         rowsum += e;
                     }

@@ -132,7 +132,7 @@ extern "C" int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockG
         g.accumulate = w.acc_w;
         RUN(bmt_gemm_ex(&g, stream));
     }
-    RUN(bmt_colsum(q.T, q.d, w.dy, dt, w.d_fc2_b, stream));
+    RUN(bmt_colsum_ex(q.T, q.d, w.dy, dt, w.d_fc2_b, w.acc_small, w.colsum_scratch, w.colsum_scratch_bytes, stream));
     {   // d_ln2 = d_ff W_1
         BmtGemmDesc g = plain(q.T, q.d, q.dff, w.d_ff, q.dff, 0, k.fc1_w, q.d, 1, w.d_ln2, q.d, dt);
         RUN(bmt_gemm_ex(&g, stream));
@@ -142,10 +142,10 @@ extern "C" int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockG
         g.accumulate = w.acc_w;
         RUN(bmt_gemm_ex(&g, stream));
     }
-    RUN(bmt_colsum(q.T, q.dff, w.d_ff, dt, w.d_fc1_b, stream));
+    RUN(bmt_colsum_ex(q.T, q.dff, w.d_ff, dt, w.d_fc1_b, w.acc_small, w.colsum_scratch, w.colsum_scratch_bytes, stream));
     // d_h1 = dy + LN2'(d_ln2)
-    RUN(bmt_norm_bwd_res(q.T, q.d, k.h1, w.d_ln2, k.ln2_w, k.stats2, 0, dt, w.nblk, w.d_h1, w.norm_partial, w.d_ln2_w, w.d_ln2_b,
-                         w.dy, stream));
+    RUN(bmt_norm_bwd_ex(q.T, q.d, k.h1, w.d_ln2, k.ln2_w, k.stats2, 0, dt, w.nblk, w.d_h1, w.norm_partial, w.d_ln2_w, w.d_ln2_b,
+                        w.dy, w.acc_small, stream));
     // ---- attention output projection
     {   // d_ctx = d_h1 W_o
         BmtGemmDesc g = plain(q.T, q.hd, q.d, w.d_h1, q.d, 0, k.out_w, q.hd, 1, w.d_ctx, q.hd, dt);
@@ -156,7 +156,7 @@ extern "C" int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockG
         g.accumulate = w.acc_w;
         RUN(bmt_gemm_ex(&g, stream));
     }
-    RUN(bmt_colsum(q.T, q.d, w.d_h1, dt, w.d_out_b, stream));
+    RUN(bmt_colsum_ex(q.T, q.d, w.d_h1, dt, w.d_out_b, w.acc_small, w.colsum_scratch, w.colsum_scratch_bytes, stream));
     // ---- attention core
     const int64_t pl = k.probs_ld;
     if (k.lse) {
@@ -203,9 +203,9 @@ extern "C" int bmt_gpt_block_backward(const BmtGptBlock* blk, const BmtGptBlockG
         g.accumulate = w.acc_w;
         RUN(bmt_gemm_ex(&g, stream));
     }
-    RUN(bmt_colsum(q.T, 3 * q.hd, w.d_qkv, dt, w.d_qkv_b, stream));
+    RUN(bmt_colsum_ex(q.T, 3 * q.hd, w.d_qkv, dt, w.d_qkv_b, w.acc_small, w.colsum_scratch, w.colsum_scratch_bytes, stream));
     // dx = d_h1 + LN1'(d_ln1)
-    RUN(bmt_norm_bwd_res(q.T, q.d, k.x, w.d_ln2, k.ln1_w, k.stats1, 0, dt, w.nblk, w.dx, w.norm_partial, w.d_ln1_w, w.d_ln1_b,
-                         w.d_h1, stream));
+    RUN(bmt_norm_bwd_ex(q.T, q.d, k.x, w.d_ln2, k.ln1_w, k.stats1, 0, dt, w.nblk, w.dx, w.norm_partial, w.d_ln1_w, w.d_ln1_b,
+                        w.d_h1, w.acc_small, stream));
     return 0;
 }

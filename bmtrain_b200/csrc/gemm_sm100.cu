@@ -54,6 +54,8 @@ struct GemmParams {
     uint32_t out_stage_off;  // byte offset of the epilogue's row staging area (128 rows x OUT_PITCH) when rows go out as bulk copies
     int staged;              // plain GEMM: the epilogue stages rows in shared memory and writes them with bulk copies
     int a_mn, b_mn;   // 1 = MN-major operand
+    int a_mn5, b_mn5; // the MN-major operand's tensor map has the 64-element chunks as a dimension of their own: one copy per
+                      // stage brings all chunks of the tile (instead of one copy per chunk)
     int m_blocks, n_blocks;
     int64_t batch_inner, batch_outer, b_inner_div;
     void* c;
@@ -670,12 +672,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                         mbar_expect_tx_u32(bar, stage_bytes);
                         if (!p.a_mn) {
                             tma_load_4d_u32(&tma_a, bar, sa, kx, m0, bi, bo);
+                        } else if (p.a_mn5) {
+                            tma_load_5d_u32(&tma_a, bar, sa, 0, kx, m0 / 64, bi, bo);
                         } else {
 #pragma unroll
                             for (int c = 0; c < BM / 64; ++c) tma_load_4d_u32(&tma_a, bar, sa + c * (64 * BK * 2), m0 + c * 64, kx, bi, bo);
                         }
                         if (!p.b_mn) {
                             tma_load_4d_u32(&tma_b, bar, sb, kx, n0, bib, bo);
+                        } else if (p.b_mn5) {
+                            tma_load_5d_u32(&tma_b, bar, sb, 0, kx, n0 / 64, bib, bo);
                         } else {
                             for (int c = 0; c < (int)bn_local / 64; ++c) tma_load_4d_u32(&tma_b, bar, sb + c * (64 * BK * 2), n0 + c * 64, kx, bib, bo);
                         }
@@ -685,12 +691,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                         if (rank == 0) mbar_expect_tx_u32(full0 + 8 * ps, 2 * stage_bytes);
                         if (!p.a_mn) {
                             tma_load_4d_2cta_u32(&tma_a, bar, sa, kx, m0, bi, bo);
+                        } else if (p.a_mn5) {
+                            tma_load_5d_2cta_u32(&tma_a, bar, sa, 0, kx, m0 / 64, bi, bo);
                         } else {
 #pragma unroll
                             for (int c = 0; c < BM / 64; ++c) tma_load_4d_2cta_u32(&tma_a, bar, sa + c * (64 * BK * 2), m0 + c * 64, kx, bi, bo);
                         }
                         if (!p.b_mn) {
                             tma_load_4d_2cta_u32(&tma_b, bar, sb, kx, n0, bib, bo);
+                        } else if (p.b_mn5) {
+                            tma_load_5d_2cta_u32(&tma_b, bar, sb, 0, kx, n0 / 64, bib, bo);
                         } else {
                             for (int c = 0; c < (int)bn_local / 64; ++c) tma_load_4d_2cta_u32(&tma_b, bar, sb + c * (64 * BK * 2), n0 + c * 64, kx, bib, bo);
                         }
@@ -964,6 +974,7 @@ struct MapKey {
     const void* ptr;
     int64_t d[4], s[3];
     int box0, box1, dtype;
+    int chunks;   // 0: 4-D map; > 0: 5-D map of an MN-major operand with this many 64-element chunks per box
     bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
 };
 struct MapKeyHash {
@@ -1024,6 +1035,43 @@ int bmt_tma_map_4d(CUtensorMap* out, const void* ptr, int dtype, int64_t inner, 
 }
 
 namespace {
+
+// 5-D map of an MN-major operand (element (k, mn) at ptr + k * ld + mn, mn contiguous): dims {64, k rows, mn / 64 chunks,
+// batch_inner, batch_outer}; the chunk dimension has a stride of 64 elements, so one box {64, box_rows, chunks} lands in
+// shared memory as `chunks` consecutive [box_rows][64] swizzled blocks -- the layout one copy per chunk produces, with one
+// copy.  Only for mn extents that are multiples of 64 (the inner dimension is the fixed 64 of a chunk, so a ragged last
+// chunk could not be bounds-checked by the copy engine).
+int make_map_mn5(CUtensorMap* out, const void* ptr, int dtype, int64_t mn, int64_t rows, int64_t ld, int64_t nb0, int64_t bs0,
+                 int64_t nb1, int64_t bs1, int box_rows, int chunks) {
+    if (mn % 64 != 0) return -13;
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    key.ptr = ptr; key.d[0] = mn; key.d[1] = rows; key.d[2] = nb0; key.d[3] = nb1;
+    key.s[0] = ld; key.s[1] = bs0; key.s[2] = bs1; key.box0 = 64; key.box1 = box_rows; key.dtype = dtype; key.chunks = chunks;
+    {
+        std::lock_guard<std::mutex> lk(g_maps_mu);
+        auto it = g_maps.find(key);
+        if (it != g_maps.end()) { *out = it->second; return 0; }
+    }
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return -10;
+    if (((uintptr_t)ptr & 15) || (ld & 7) || (nb0 > 1 && (bs0 & 7)) || (nb1 > 1 && (bs1 & 7))) return -11;
+    cuuint64_t dims[5] = {64, (cuuint64_t)rows, (cuuint64_t)(mn / 64), (cuuint64_t)nb0, (cuuint64_t)nb1};
+    cuuint64_t st[4] = {(cuuint64_t)ld * 2, 128, (cuuint64_t)(nb0 > 1 ? bs0 : ld * rows) * 2, (cuuint64_t)(nb1 > 1 ? bs1 : ld * rows) * 2};
+    if (st[2] == 0) st[2] = 16;
+    if (st[3] == 0) st[3] = 16;
+    cuuint32_t box[5] = {64, (cuuint32_t)box_rows, (cuuint32_t)chunks, 1, 1};
+    cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    cudaFree(0);
+    CUresult r = enc(out, dtype == BMT_DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, (void*)ptr,
+                     dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -12;   // the caller falls back to one 4-D copy per chunk
+    std::lock_guard<std::mutex> lk(g_maps_mu);
+    if (g_maps.size() > 8192) g_maps.clear();
+    g_maps[key] = *out;
+    return 0;
+}
 
 int g_num_sms = 0;
 
@@ -1143,11 +1191,21 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     CUtensorMap ma, mb;
     int rc;
     const int64_t nb_b = (batch_inner + p.b_inner_div - 1) / p.b_inner_div;
+    static int mn5_env = -1;
+    if (mn5_env < 0) { const char* e = getenv("BMT_GEMM_MN5"); mn5_env = e ? atoi(e) : 1; }
     if (!a_major) rc = make_map(&ma, a, ab_dtype, k, m, lda, batch_inner, a_bs0, batch_outer, a_bs1, BK, BM);
-    else          rc = make_map(&ma, a, ab_dtype, m, k, lda, batch_inner, a_bs0, batch_outer, a_bs1, 64, BK);
+    else {
+        rc = mn5_env ? make_map_mn5(&ma, a, ab_dtype, m, k, lda, batch_inner, a_bs0, batch_outer, a_bs1, BK, BM / 64) : -1;
+        p.a_mn5 = rc == 0 ? 1 : 0;
+        if (rc) rc = make_map(&ma, a, ab_dtype, m, k, lda, batch_inner, a_bs0, batch_outer, a_bs1, 64, BK);
+    }
     if (rc) return rc;
     if (!b_major) rc = make_map(&mb, b, ab_dtype, k, n, ldb, nb_b, b_bs0, batch_outer, b_bs1, BK, p.bn / ncta);
-    else          rc = make_map(&mb, b, ab_dtype, n, k, ldb, nb_b, b_bs0, batch_outer, b_bs1, 64, BK);
+    else {
+        rc = mn5_env ? make_map_mn5(&mb, b, ab_dtype, n, k, ldb, nb_b, b_bs0, batch_outer, b_bs1, BK, (p.bn / ncta) / 64) : -1;
+        p.b_mn5 = rc == 0 ? 1 : 0;
+        if (rc) rc = make_map(&mb, b, ab_dtype, n, k, ldb, nb_b, b_bs0, batch_outer, b_bs1, 64, BK);
+    }
     if (rc) return rc;
 
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * batch_inner * batch_outer;

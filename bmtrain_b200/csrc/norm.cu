@@ -121,8 +121,9 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(int64_t rows, int d, const
 }
 
 // Fold the per-CTA partial sums: block = 32 columns x 32 row lanes, rows strided over the lanes, smem tree at the end.
-template <typename T>
+template <typename T, bool ACC = false>
 __global__ void __launch_bounds__(1024) norm_fold_kernel(int d, int nblk, const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db) {
+    // ACC: dw / db already hold gradients of earlier passes and are added to
     __shared__ float sa[32][33], sb[32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;
     const int c = blockIdx.x * 32 + tx;
@@ -139,6 +140,10 @@ __global__ void __launch_bounds__(1024) norm_fold_kernel(int d, int nblk, const 
         float ra = 0.f, rb = 0.f;
 #pragma unroll 8
         for (int l = 0; l < 32; ++l) { ra += sa[l][tx]; rb += sb[l][tx]; }
+        if (ACC) {
+            ra += bmt::Cvt<T>::to_f(dw[c]);
+            if (db) rb += bmt::Cvt<T>::to_f(db[c]);
+        }
         dw[c] = bmt::Cvt<T>::from_f(ra);
         if (db) db[c] = bmt::Cvt<T>::from_f(rb);
     }
@@ -227,10 +232,110 @@ __global__ void __launch_bounds__(NT, 2) norm_fwd_reg_kernel(int64_t rows, int d
     }
 }
 
+// Streaming form of the kernel above: the row stays packed (16-byte vectors) in registers and the loads of the CTA's next
+// group of rows are issued before the arithmetic on the current one starts, so every warp has VPL loads in flight all the
+// time instead of only at the top of each row.  The exchange slots of a row's warp team alternate between two sets, which
+// saves the barrier at the end of a group.
+template <typename T, int VPL, int WPR>
+__global__ void __launch_bounds__(NT, VPL <= 4 ? 3 : 2) norm_fwd_stream_kernel(int64_t rows, int d, const T* __restrict__ x, const T* __restrict__ w,
+                                                             const T* __restrict__ b, float eps, int rms, T* __restrict__ y,
+                                                             float* __restrict__ stats) {
+    constexpr int RPC = 8 / WPR;
+    __shared__ float ex[2][2][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = warp % WPR, slot = warp / WPR;
+    const int64_t groups = (rows + RPC - 1) / RPC;
+    bmt::Vec16<T> cur[VPL], nxt[VPL];
+    const auto load = [&](bmt::Vec16<T>(&v)[VPL], int64_t gi) {
+        const int64_t r = gi * RPC + slot;
+        if (r < rows) {
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const int c = ((i * WPR + sub) * 32 + lane) * 8;
+                if (c < d) v[i] = bmt::ld16(x + r * d + c);
+            }
+        }
+    };
+    int64_t gi = blockIdx.x;
+    if (gi < groups) load(cur, gi);
+    int par = 0;
+    for (; gi < groups; gi += gridDim.x, par ^= 1) {
+        if (gi + gridDim.x < groups) load(nxt, gi + gridDim.x);
+        const int64_t r = gi * RPC + slot;
+        const bool live = r < rows;
+        float mean = 0.f;
+        if (!rms) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const int c = ((i * WPR + sub) * 32 + lane) * 8;
+                if (live && c < d) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) s += bmt::Cvt<T>::to_f(cur[i].v[k]);
+                }
+            }
+            s = bmt::warp_sum(s);
+            if (WPR > 1) {
+                if (lane == 0) ex[par][0][warp] = s;
+                __syncthreads();
+                s = 0.f;
+#pragma unroll
+                for (int i = 0; i < WPR; ++i) s += ex[par][0][slot * WPR + i];
+            }
+            mean = s / d;
+        }
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int c = ((i * WPR + sub) * 32 + lane) * 8;
+            if (live && c < d) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { const float t = bmt::Cvt<T>::to_f(cur[i].v[k]) - mean; q += t * t; }
+            }
+        }
+        q = bmt::warp_sum(q);
+        if (WPR > 1) {
+            if (lane == 0) ex[par][1][warp] = q;
+            __syncthreads();
+            q = 0.f;
+#pragma unroll
+            for (int i = 0; i < WPR; ++i) q += ex[par][1][slot * WPR + i];
+        }
+        const float rstd = rsqrtf(q / d + eps);
+        if (live && sub == 0 && lane == 0) { stats[r] = mean; stats[rows + r] = rstd; }
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int c = ((i * WPR + sub) * 32 + lane) * 8;
+            if (live && c < d) {
+                const bmt::Vec16<T> wv = bmt::ld16(w + c);   // a few KB re-read by every row: stays in L1
+                bmt::Vec16<T> bv, o;
+                if (b) bv = bmt::ld16(b + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    float t = (bmt::Cvt<T>::to_f(cur[i].v[k]) - mean) * rstd * bmt::Cvt<T>::to_f(wv.v[k]);
+                    if (b) t += bmt::Cvt<T>::to_f(bv.v[k]);
+                    o.v[k] = bmt::Cvt<T>::from_f(t);
+                }
+                bmt::st16(y + r * d + c, o);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) cur[i] = nxt[i];
+    }
+}
+
 template <typename T, int VPL, int WPR>
 void launch_fwd_reg(int64_t rows, int d, const void* x, const void* w, const void* b, float eps, int rms, void* y, void* stats,
                     cudaStream_t s) {
     const int64_t groups = (rows + (8 / WPR) - 1) / (8 / WPR);
+    static const bool stream = [] { const char* e = getenv("BMT_NORM_STAGED"); return !(e && atoi(e) == 2); }();
+    if (stream) {
+        const int64_t cap = 148 * (VPL <= 4 ? 3 : 2);
+        const int64_t grid = groups < cap ? groups : cap;
+        norm_fwd_stream_kernel<T, VPL, WPR><<<(unsigned)grid, NT, 0, s>>>(rows, d, (const T*)x, (const T*)w, (const T*)b, eps, rms,
+                                                                           (T*)y, (float*)stats);
+        return;
+    }
     const int64_t grid = groups < 148 * 2 ? groups : 148 * 2;
     norm_fwd_reg_kernel<T, VPL, WPR><<<(unsigned)grid, NT, 0, s>>>(rows, d, (const T*)x, (const T*)w, (const T*)b, eps, rms, (T*)y,
                                                                     (float*)stats);
@@ -269,11 +374,169 @@ int fwd(int64_t rows, int64_t d, const void* x, const void* w, const void* b, fl
     return (int)cudaGetLastError();
 }
 
+// Backward with the same work split as norm_fwd_reg_kernel: a team of WPR warps per row, every lane owns fixed columns.
+// x and dy are read once (kept as packed 16-byte vectors in registers between the statistics and the dx pass), the
+// per-column sums of dy * xhat and dy accumulate in registers over all rows a lane sees and are combined once per CTA
+// through shared memory into the (nblk x d) scratch that norm_fold_kernel reduces.  No block-wide barrier per row
+// unless a row is shared by several warps.
+template <typename T, int VPL, int WPR>
+__global__ void __launch_bounds__(NT, 1) norm_bwd_reg_kernel(int64_t rows, int d, const T* __restrict__ x, const T* __restrict__ dy,
+                                                             const T* __restrict__ w, const float* __restrict__ stats, int rms,
+                                                             T* __restrict__ dx, float* __restrict__ partial,
+                                                             const T* __restrict__ dres) {
+    constexpr int RPC = 8 / WPR;
+    __shared__ float ex[2][8];
+    extern __shared__ float fold[];                    // [RPC][2][d / ... ] reused for the final combination
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = warp % WPR, slot = warp / WPR;
+    float dg[VPL][8], db[VPL][8];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) dg[v][k] = db[v][k] = 0.f;
+    const int64_t groups = (rows + RPC - 1) / RPC;
+    for (int64_t gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+        const int64_t r = gi * RPC + slot;
+        const bool live = r < rows;
+        const float mean = live ? stats[r] : 0.f, rstd = live ? stats[rows + r] : 0.f;
+        bmt::Vec16<T> xv[VPL], gv[VPL];
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int c = ((v * WPR + sub) * 32 + lane) * 8;
+            if (live && c < d) { xv[v] = bmt::ld16(x + r * d + c); gv[v] = bmt::ld16(dy + r * d + c); }
+        }
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int c = ((v * WPR + sub) * 32 + lane) * 8;
+            if (live && c < d) {
+                const bmt::Vec16<T> wv = bmt::ld16(w + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float xh = (bmt::Cvt<T>::to_f(xv[v].v[k]) - mean) * rstd;
+                    const float g = bmt::Cvt<T>::to_f(gv[v].v[k]);
+                    const float wg = g * bmt::Cvt<T>::to_f(wv.v[k]);
+                    s1 += wg; s2 += wg * xh;
+                    dg[v][k] += g * xh; db[v][k] += g;
+                }
+            }
+        }
+        s1 = bmt::warp_sum(s1);
+        s2 = bmt::warp_sum(s2);
+        if (WPR > 1) {
+            if (lane == 0) { ex[0][warp] = s1; ex[1][warp] = s2; }
+            __syncthreads();
+            s1 = s2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < WPR; ++i) { s1 += ex[0][slot * WPR + i]; s2 += ex[1][slot * WPR + i]; }
+        }
+        s1 = rms ? 0.f : s1 / d;
+        s2 = s2 / d;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int c = ((v * WPR + sub) * 32 + lane) * 8;
+            if (live && c < d) {
+                const bmt::Vec16<T> wv = bmt::ld16(w + c);
+                bmt::Vec16<T> o, rv;
+                if (dres) rv = bmt::ld16(dres + r * d + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float xh = (bmt::Cvt<T>::to_f(xv[v].v[k]) - mean) * rstd;
+                    const float wg = bmt::Cvt<T>::to_f(gv[v].v[k]) * bmt::Cvt<T>::to_f(wv.v[k]);
+                    float val = rstd * (wg - s1 - xh * s2);
+                    if (dres) val += bmt::Cvt<T>::to_f(rv.v[k]);
+                    o.v[k] = bmt::Cvt<T>::from_f(val);
+                }
+                bmt::st16(dx + r * d + c, o);
+            }
+        }
+        if (WPR > 1) __syncthreads();
+    }
+    // combine the RPC row slots of this CTA: slot 0 ends up with the CTA's column sums
+    float* pg = partial + (int64_t)blockIdx.x * d;
+    float* pb = partial + ((int64_t)gridDim.x + blockIdx.x) * d;
+    for (int s_ = 1; s_ < RPC; ++s_) {
+        __syncthreads();
+        if (slot == s_) {
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                const int c = ((v * WPR + sub) * 32 + lane) * 8;
+                if (c < d) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) { fold[c + k] = dg[v][k]; fold[d + c + k] = db[v][k]; }
+                }
+            }
+        }
+        __syncthreads();
+        if (slot == 0) {
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                const int c = ((v * WPR + sub) * 32 + lane) * 8;
+                if (c < d) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) { dg[v][k] += fold[c + k]; db[v][k] += fold[d + c + k]; }
+                }
+            }
+        }
+    }
+    if (slot == 0) {
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int c = ((v * WPR + sub) * 32 + lane) * 8;
+            if (c < d) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { pg[c + k] = dg[v][k]; pb[c + k] = db[v][k]; }
+            }
+        }
+    }
+}
+
+template <typename T, int WPR>
+bool bwd_reg_vpl(int vpl, int64_t rows, int d, const void* x, const void* dy, const void* w, const void* stats, int rms, int nblk,
+                 void* dx, void* partial, const void* dres, cudaStream_t s) {
+    const size_t smem = (size_t)2 * d * sizeof(float);
+#define BMT_BWD_REG(V)                                                                                                          \
+    do {                                                                                                                        \
+        static bool cfg = false;                                                                                                \
+        if (!cfg) { cudaFuncSetAttribute(norm_bwd_reg_kernel<T, V, WPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16384 * 4); cfg = true; } \
+        norm_bwd_reg_kernel<T, V, WPR><<<nblk, NT, smem, s>>>(rows, d, (const T*)x, (const T*)dy, (const T*)w, (const float*)stats, rms, \
+                                                              (T*)dx, (float*)partial, (const T*)dres);                         \
+    } while (0)
+    if (vpl <= 2) BMT_BWD_REG(2);
+    else if (vpl <= 4) BMT_BWD_REG(4);
+    else if (vpl <= 6) BMT_BWD_REG(6);
+    else if (vpl <= 8) BMT_BWD_REG(8);
+    else return false;
+#undef BMT_BWD_REG
+    return true;
+}
+
 template <typename T>
 int bwd(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms, int nblk, void* dx,
-        void* partial, void* dw, void* db, cudaStream_t s, const void* dres = nullptr) {
+        void* partial, void* dw, void* db, cudaStream_t s, const void* dres = nullptr, bool acc = false) {
+    const auto fold = [&] {
+        const unsigned g = (unsigned)((d + 31) / 32);
+        if (acc) norm_fold_kernel<T, true><<<g, dim3(32, 32), 0, s>>>((int)d, nblk, (const float*)partial, (T*)dw, (T*)db);
+        else norm_fold_kernel<T><<<g, dim3(32, 32), 0, s>>>((int)d, nblk, (const float*)partial, (T*)dw, (T*)db);
+    };
+    static const bool use_reg = [] { const char* e = getenv("BMT_NORM_STAGED"); return !(e && atoi(e) == 1); }();
+    if (use_reg && d <= 16384) {
+        // the backward keeps two column-sum accumulators per value: at most 6 vectors per lane where the row length allows
+        const int wpr = d <= 1536 ? 1 : d <= 3072 ? 2 : d <= 6144 ? 4 : 8;
+        const int vpl = (int)((d + 256 * wpr - 1) / (256 * wpr));
+        bool done = false;
+        if (wpr == 1) done = bwd_reg_vpl<T, 1>(vpl, rows, (int)d, x, dy, w, stats, rms, nblk, dx, partial, dres, s);
+        else if (wpr == 2) done = bwd_reg_vpl<T, 2>(vpl, rows, (int)d, x, dy, w, stats, rms, nblk, dx, partial, dres, s);
+        else if (wpr == 4) done = bwd_reg_vpl<T, 4>(vpl, rows, (int)d, x, dy, w, stats, rms, nblk, dx, partial, dres, s);
+        else done = bwd_reg_vpl<T, 8>(vpl, rows, (int)d, x, dy, w, stats, rms, nblk, dx, partial, dres, s);
+        if (done) {
+            fold();
+            bmt_count_launch(2);
+            return (int)cudaGetLastError();
+        }
+    }
     norm_bwd_kernel<T><<<nblk, NT, 0, s>>>(rows, (int)d, (const T*)x, (const T*)dy, (const T*)w, (const float*)stats, rms, (T*)dx, (float*)partial, (const T*)dres);
-    norm_fold_kernel<T><<<(unsigned)((d + 31) / 32), dim3(32, 32), 0, s>>>((int)d, nblk, (const float*)partial, (T*)dw, (T*)db);
+    fold();
     bmt_count_launch(2);
     return (int)cudaGetLastError();
 }
@@ -306,6 +569,17 @@ extern "C" int bmt_norm_bwd_res(int64_t rows, int64_t d, const void* x, const vo
     cudaStream_t s = (cudaStream_t)stream;
     return dtype == BMT_DT_F16 ? bwd<__half>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s, dres)
                                : bwd<__nv_bfloat16>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s, dres);
+}
+
+// Backward with residual-branch gradient and, when `accumulate` is set, dw / db += instead of =.
+extern "C" int bmt_norm_bwd_ex(int64_t rows, int64_t d, const void* x, const void* dy, const void* w, const void* stats, int rms,
+                               int dtype, int nblk, void* dx, void* partial, void* dw, void* db, const void* dres, int accumulate,
+                               void* stream) {
+    if (rows <= 0) return 0;
+    if (d % 8 != 0 || d > NT * 8 * MAXIT || dtype == BMT_DT_F32) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    return dtype == BMT_DT_F16 ? bwd<__half>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s, dres, accumulate != 0)
+                               : bwd<__nv_bfloat16>(rows, d, x, dy, w, stats, rms, nblk, dx, partial, dw, db, s, dres, accumulate != 0);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

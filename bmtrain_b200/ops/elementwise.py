@@ -85,6 +85,22 @@ def rope(q: torch.Tensor, k: torch.Tensor, theta: float = 10000.0) -> Tuple[torc
     return RopeFunction.apply(q, k, theta)
 
 
+_rope_cache = {}
+
+
+def _rope_table(s: int, d: int, theta: float, device) -> torch.Tensor:
+    """(s, d/2, 2) fp32 table of (cos, sin) of position x frequency, built once per shape and kept on the device."""
+    key = (s, d, float(theta), str(device))
+    tab = _rope_cache.get(key)
+    if tab is None:
+        cos, sin = _rope_tables(s, d, theta, device)
+        tab = torch.stack([cos, sin], dim=-1).contiguous()
+        if len(_rope_cache) > 16:
+            _rope_cache.clear()
+        _rope_cache[key] = tab
+    return tab
+
+
 class RopeQKVFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, packed, g, theta):
@@ -95,7 +111,8 @@ class RopeQKVFunction(torch.autograd.Function):
         _native.check(_native.cuda_lib().bmt_rope_qkv(
             ctypes.c_int64(b), ctypes.c_int64(s), ctypes.c_int(hk), ctypes.c_int(g), ctypes.c_int(d), _native.ptr(packed),
             ctypes.c_int64(packed.stride(1)), ctypes.c_int64(packed.stride(0)), _native.ptr(q), _native.ptr(k), _native.ptr(v),
-            ctypes.c_float(theta), ctypes.c_int64(0), ctypes.c_int(1), ctypes.c_int(_DT[packed.dtype]), _native.stream_handle()),
+            _native.ptr(_rope_table(s, d, theta, packed.device)), ctypes.c_int64(0), ctypes.c_int(1), ctypes.c_int(_DT[packed.dtype]),
+            _native.stream_handle()),
             "rotary embedding kernel")
         ctx.g, ctx.theta, ctx.shape = g, theta, packed.shape
         return q, k, v
@@ -108,7 +125,8 @@ class RopeQKVFunction(torch.autograd.Function):
         _native.check(_native.cuda_lib().bmt_rope_qkv(
             ctypes.c_int64(b), ctypes.c_int64(s), ctypes.c_int(hk), ctypes.c_int(ctx.g), ctypes.c_int(d), _native.ptr(out),
             ctypes.c_int64(out.stride(1)), ctypes.c_int64(out.stride(0)), _native.ptr(gq), _native.ptr(gk), _native.ptr(gv),
-            ctypes.c_float(ctx.theta), ctypes.c_int64(0), ctypes.c_int(0), ctypes.c_int(_DT[gq.dtype]), _native.stream_handle()),
+            _native.ptr(_rope_table(s, d, ctx.theta, gq.device)), ctypes.c_int64(0), ctypes.c_int(0), ctypes.c_int(_DT[gq.dtype]),
+            _native.stream_handle()),
             "rotary embedding backward kernel")
         return out, None, None
 

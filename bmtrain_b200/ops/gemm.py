@@ -132,6 +132,19 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
+_scratch = {}
+
+
+def colsum_scratch(dev) -> torch.Tensor:
+    """Work space of the row-split column sums (4 KB of ticket counters + partial sums), one per device and stream, zeroed
+    once: the kernel leaves the counters at zero, and calls that share it are ordered on their stream."""
+    key = (str(dev), torch.cuda.current_stream(dev).cuda_stream)
+    buf = _scratch.get(key)
+    if buf is None:
+        buf = _scratch[key] = torch.zeros(1024 + 2 * 1024 * 1024, dtype=torch.float32, device=dev)
+    return buf
+
+
 def bias_grad(grad_out: torch.Tensor) -> torch.Tensor:
     """Column sums of ``grad_out`` (M, N), accumulated in fp32, returned in the input dtype."""
     if not grad_out.is_cuda:
@@ -141,8 +154,10 @@ def bias_grad(grad_out: torch.Tensor) -> torch.Tensor:
     m, n = g.shape
     out = torch.empty(n, dtype=g.dtype, device=g.device)
     dt = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[g.dtype]
-    _native.check(lib.bmt_colsum(ctypes.c_int64(m), ctypes.c_int64(n), _native.ptr(g), ctypes.c_int(dt),
-                                 _native.ptr(out), _native.stream_handle()), "column-sum kernel")
+    scratch = colsum_scratch(g.device)
+    _native.check(lib.bmt_colsum_ex(ctypes.c_int64(m), ctypes.c_int64(n), _native.ptr(g), ctypes.c_int(dt), _native.ptr(out),
+                                    ctypes.c_int(0), _native.ptr(scratch), ctypes.c_int64(scratch.numel() * 4),
+                                    _native.stream_handle()), "column-sum kernel")
     return out
 
 

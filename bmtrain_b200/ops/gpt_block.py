@@ -13,6 +13,7 @@ from typing import Optional
 import torch
 
 from . import _native
+from . import gemm as _gemm
 
 _c_void_p, _i64, _int, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
 
@@ -41,6 +42,7 @@ class _Grad(ctypes.Structure):
         ("d_ff", _c_void_p), ("d_ln2", _c_void_p), ("d_h1", _c_void_p), ("d_ctx", _c_void_p), ("d_probs", _c_void_p),
         ("d_qkv", _c_void_p), ("norm_partial", _c_void_p), ("nblk", _int),
         ("dq_acc", _c_void_p), ("delta", _c_void_p),
+        ("acc_small", _int), ("colsum_scratch", _c_void_p), ("colsum_scratch_bytes", ctypes.c_int64),
     ]
 
 
@@ -147,18 +149,24 @@ class GPTBlockFunction(torch.autograd.Function):
         g = _Grad()
         dx = torch.empty_like(x)
         g.dy, g.dx = dy.data_ptr(), dx.data_ptr()
-        # weight gradients: accumulate in place when the owner already attached same-dtype gradient buffers
-        weights = [p for name, p in zip(_PARAM_NAMES, params) if name in _WEIGHTS]
-        in_place = all(p.is_leaf and p.requires_grad and p.grad is not None and p.grad.dtype == dt and p.grad.is_contiguous()
-                       for p in weights)
+        # gradients of the parameters: accumulate in place when the owner already attached same-dtype gradient buffers (no
+        # tensor goes back to autograd for them, so no add kernel per parameter either)
+        def attached(p):
+            return p.is_leaf and p.requires_grad and p.grad is not None and p.grad.dtype == dt and p.grad.is_contiguous()
+
+        acc_w = all(attached(p) for name, p in zip(_PARAM_NAMES, params) if name in _WEIGHTS)
+        acc_small = all(attached(p) for name, p in zip(_PARAM_NAMES, params) if name not in _WEIGHTS)
         grads = {}
         for name, p in zip(_PARAM_NAMES, params):
-            if name in _WEIGHTS and in_place:
+            if acc_w if name in _WEIGHTS else acc_small:
                 setattr(g, "d_" + name, p.grad.data_ptr())
             else:
                 grads[name] = torch.empty_like(p)
                 setattr(g, "d_" + name, grads[name].data_ptr())
-        g.acc_w = 1 if in_place else 0
+        g.acc_w = 1 if acc_w else 0
+        g.acc_small = 1 if acc_small else 0
+        scratch = _gemm.colsum_scratch(dev)
+        g.colsum_scratch, g.colsum_scratch_bytes = scratch.data_ptr(), scratch.numel() * 4
         nblk = min(T, 296)
         work = {
             "d_ff": torch.empty(T, dff, dtype=dt, device=dev), "d_ln2": torch.empty(T, d, dtype=dt, device=dev),

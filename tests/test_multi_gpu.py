@@ -333,3 +333,9 @@ def body_pipe_zero_gpu():
 def test_pipeline_with_zero_4gpu():
     _need(4)
     run_distributed("test_multi_gpu", "body_pipe_zero_gpu", 4, device="cuda", init_kwargs=dict(pipe_size=2, num_micro_batches=4))
+
+
+def test_pipeline_2gpu():
+    """Two pipeline stages on two GPUs (NCCL send / recv between the stages, no ZeRO sharding inside a stage)."""
+    _need(2)
+    run_distributed("test_multi_gpu", "body_pipe_zero_gpu", 2, device="cuda", init_kwargs=dict(pipe_size=2, num_micro_batches=4))
