@@ -139,9 +139,11 @@ def test_training_matches_fp32_oracle(bmt_gpu, form, optim):
     for k, r in ref_final.items():
         g = final[k]
         assert g.shape == r.shape, k
-        for stat in (torch.std, torch.mean, torch.max, torch.min):
+        # Adam moves every entry by about lr per step whatever the size of its gradient, so a single entry whose gradient
+        # is rounding noise in fp16 can end up to steps * lr = 0.04 away: the extremes get that tolerance
+        for stat, tol in ((torch.std, 1e-2), (torch.mean, 1e-2), (torch.max, 4e-2), (torch.min, 4e-2)):
             if r.numel() > 1:
-                assert abs(float(stat(g)) - float(stat(r))) < 1e-2, (k, stat.__name__)
+                assert abs(float(stat(g)) - float(stat(r))) < tol, (k, stat.__name__)
 
 
 def test_wrapped_model_logits_equal_plain_model(bmt_gpu):
