@@ -22,6 +22,7 @@ is organised differently:
 from __future__ import annotations
 
 import inspect
+import weakref
 from collections import OrderedDict
 from typing import Dict, Iterable, Iterator, List, Optional, Tuple, Union
 
@@ -50,6 +51,47 @@ _param_epoch = [0]
 
 def params_changed() -> None:
     _param_epoch[0] += 1
+
+
+# Gradients of block-owned parameters that went through the fused reduce-scatter kernel have two companions per bucket:
+# an fp32 copy of the partition gradient (created the first time a bucket accumulates over micro-steps; from then on the
+# accumulation runs in fp32 and `.grad` is its rounding) and the sum of squares of the partition gradient (for the
+# gradient norm).  Both describe `.grad` as the kernel left it: code that rewrites gradients in place (clipping) calls
+# grads_modified(), after which the companions are rebuilt / ignored.
+_grad_epoch = [0]
+_fused_buckets = weakref.WeakSet()
+
+
+def grads_modified() -> None:
+    _grad_epoch[0] += 1
+
+
+def _grad_companions() -> bool:
+    """Off unless BMT_GRAD_FP32=1 (or ``config["grad_accum_fp32"]``): the extended kernel entry has been compiled and
+    read, not yet run on a GPU."""
+    import os
+
+    return bool(config.get("grad_accum_fp32", False)) or os.environ.get("BMT_GRAD_FP32", "0") == "1"
+
+
+def fused_sq_norms(parameters):
+    """Sum of squares already known from the fused reduce-scatter: returns (ids of the parameters it covers, list of
+    one-element fp32 device tensors to add up).  A bucket counts only if every one of its gradient holders is in
+    ``parameters`` (its figure is for the whole partition) and nothing rewrote the gradients since."""
+    wanted = {id(p) for p in parameters}
+    covered, parts = set(), []
+    for b in list(_fused_buckets):
+        if getattr(b, "sq_tag", None) != _grad_epoch[0] or b.storage is None or b.storage.grad is None:
+            continue
+        if id(b.storage) in wanted:
+            holders = [b.storage]
+        else:
+            holders = [s.param for s in b.slots if s.param.requires_grad]
+            if not holders or any(id(h) not in wanted for h in holders):
+                continue
+        covered.update(id(h) for h in holders)
+        parts.append(b.sqsum)
+    return covered, parts
 
 
 def update_ready(param, block: bool = True) -> bool:
@@ -562,9 +604,26 @@ class Block(torch.nn.Module):
 
                 key = self._grad_slot_key(b)
                 piece = b.storage.grad if accumulate else torch.empty(b.part, dtype=b.dtype, device=full_grad.device)
+                grad32 = sqsum = None
+                if _grad_companions():
+                    grad32 = getattr(b, "grad32", None)
+                    if accumulate and (grad32 is None or b.grad32_tag != _grad_epoch[0]):
+                        # first accumulation of this bucket (or the gradient was rewritten in place since the kernel last
+                        # wrote the fp32 copy): start the fp32 copy from what `.grad` holds
+                        if grad32 is None:
+                            grad32 = b.grad32 = torch.empty(b.part, dtype=torch.float32, device=full_grad.device)
+                        grad32.copy_(piece)
+                    if getattr(b, "sqsum", None) is None:
+                        b.sqsum = torch.zeros(1, dtype=torch.float32, device=full_grad.device)
+                        _fused_buckets.add(b)
+                    sqsum = b.sqsum
                 rt.stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(rt.stream):
-                    rt.reduce_scatter(b.full_grad_buf, rt.row(key + ("ready",)), b.part, piece, accumulate)
+                    if sqsum is not None:
+                        sqsum.zero_()
+                    rt.reduce_scatter(b.full_grad_buf, rt.row(key + ("ready",)), b.part, piece, accumulate, acc32=grad32, sqsum=sqsum)
+                    if sqsum is not None:
+                        b.grad32_tag = b.sq_tag = _grad_epoch[0]
                     done_row = rt.row(key + ("done",))
                     rt.signal_wait(done_row, rt.next_epoch(done_row), signal=True, wait=False)
                     ev = torch.cuda.Event()

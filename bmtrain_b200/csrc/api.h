@@ -167,6 +167,12 @@ int bmt_fused_reduce_scatter(const void* const* peers, void* const* peer_flags, 
 int bmt_fused_reduce_scatter_mc(const void* multicast, void* const* peer_flags, int world, int rank, int slot,
                                 unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
                                 void* overflow_u8, void* status_i32, double timeout_s, void* stream);
+// Both forms with the optional extras (`multicast` null: plain peer loads): `acc32` = fp32 partition gradient through which
+// accumulation over micro-steps goes (rounded to `out` once per call), `sqsum_f32` += sum of squares of the values written.
+int bmt_fused_reduce_scatter_ex(const void* const* peers, const void* multicast, void* const* peer_flags, int world, int rank,
+                                int slot, unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
+                                void* acc32, void* sqsum_f32, void* overflow_u8, void* status_i32, double timeout_s,
+                                void* stream);
 int bmt_push_ranges(const void* const* src, const int64_t* dst_off, const int64_t* nbytes, int nranges, void* const* dst,
                     void* const* peer_flags, int world, int rank, int free_row, int done_row, unsigned int epoch,
                     void* counter_u32, void* status_i32, double timeout_s, int grid, void* stream);

@@ -20,8 +20,6 @@
 #include <math.h>
 #include <string.h>
 
-#include <type_traits>
-
 #include "api.h"
 #include "common.cuh"
 #include "tcgen05.cuh"
@@ -31,6 +29,7 @@ namespace {
 
 using namespace bmt_tc;
 
+constexpr int ATT_THREADS = 192;
 constexpr int TILE = 128;                        // query rows per CTA and keys per step
 constexpr uint32_t CHUNK = TILE * 64 * 2;        // one [128 rows][64 columns] swizzled chunk of 16-bit elements: 16 KiB
 
@@ -53,8 +52,6 @@ struct AttnParams {
 struct AttnShared {
     uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2];
     uint64_t s_full[2], s_free[2], p_ready, p_free, o_full;
-    uint64_t pair[4];           // split softmax: the two warps that share a quarter of the rows meet here once per tile
-    float xm[2][2][TILE];       // [tile parity][column half][row]: partial row maxima (and, at the end, partial row sums)
     uint32_t tmem_base;
     int failed;
 };
@@ -111,12 +108,8 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// SPLIT = 1: four softmax warps, one thread per query row.  SPLIT = 2: eight softmax warps; the two warps that own the same
-// 32 rows (tensor-memory lanes) each take half of the columns of S, of P and of the accumulator, and exchange their
-// partial row maxima through shared memory once per tile (a bounded mbarrier meeting, not a named barrier, so that a
-// warp whose wait ran out can never leave its partner stuck).  Two warps per scheduler hide each other's latencies.
-template <int HD, typename T, int SPLIT>
-__global__ void __launch_bounds__(64 + 128 * SPLIT, 1)
+template <int HD, typename T>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
                  const AttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -140,10 +133,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         mbar_init(&sh->q_full, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh->k_full[i], 1); mbar_init(&sh->v_full[i], 1); mbar_init(&sh->k_empty[i], 1); mbar_init(&sh->v_empty[i], 1);
-            mbar_init(&sh->s_full[i], 1); mbar_init(&sh->s_free[i], 4 * SPLIT);
+            mbar_init(&sh->s_full[i], 1); mbar_init(&sh->s_free[i], 4);
         }
-        for (int i = 0; i < 4; ++i) mbar_init(&sh->pair[i], 2);
-        mbar_init(&sh->p_ready, 4 * SPLIT);
+        mbar_init(&sh->p_ready, 4);
         mbar_init(&sh->p_free, 1);
         mbar_init(&sh->o_full, 1);
         sh->failed = 0;
@@ -227,9 +219,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     } else {
         // ------------------------------------------------------------------------------------------ softmax + epilogue
         const int quarter = warp & 3;                 // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
-        const int half = (warp - 2) >> 2;             // which part of the columns this warp takes (always 0 when SPLIT = 1)
-        constexpr int NC = TILE / 32 / SPLIT;         // 32-column groups of S per thread
-        constexpr int OC = HD / 32 / SPLIT;           // 32-column groups of the accumulator per thread
         const int row = quarter * 32 + lane;
         const int64_t qi = q0 + row;                  // query index of this thread
         const bool row_ok = qi < p.sq;
@@ -239,62 +228,44 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         // m_ref: the maximum the exponents are taken against.  It follows the running maximum lazily: only when that
         // has grown by more than 8 (in base-2 exponent units) is the accumulator in tensor memory rescaled -- probabilities
         // stay below 2^8, sums are fp32 -- so that after the first few tiles a tile costs one round trip to tensor memory.
-        float m_ref = -INFINITY, l_run = 0.f;         // l_run: sum over this thread's columns only
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
-        // meeting of the two warps of a row quarter (SPLIT = 2): everything written to sh->xm before it is visible after it
-        uint32_t meetings = 0;
-        const auto meet = [&]() -> bool {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->pair[quarter]);
-            const bool got = warp_wait(&sh->pair[quarter], meetings & 1u, lane);
-            ++meetings;
-            return got;
-        };
         for (int j = 0; j < J && ok; ++j) {
             const int sb = j & 1;
             if (!warp_wait(&sh->s_full[sb], (uint32_t)((j >> 1) & 1), lane)) { if (lane == 0) fail(sh, 9); ok = false; break; }
             tc_fence_after();
             const int64_t kv0 = (int64_t)j * TILE;
-            const bool need_mask = __any_sync(0xffffffffu, (kv0 + TILE > kv_end) || (p.causal && kv0 + TILE - 1 > q0 + p.causal_off) || mrow != nullptr);
-            const uint32_t s_addr = tmem + lane_addr + sb * TILE + half * (TILE / SPLIT);
-            uint32_t r[NC][32];
+            const bool need_mask = (kv0 + TILE > kv_end) || (p.causal && kv0 + TILE - 1 > q0 + p.causal_off) || mrow != nullptr;
+            const uint32_t s_addr = tmem + lane_addr + sb * TILE;
+            uint32_t r[TILE / 32][32];
 #pragma unroll
-            for (int c = 0; c < NC; ++c) tmem_ld32(s_addr + c * 32, r[c]);
+            for (int c4 = 0; c4 < TILE / 32; ++c4) tmem_ld32(s_addr + c4 * 32, r[c4]);
             tmem_ld_wait();
             // the scores are in registers: the S buffer may take the tile after next
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->s_free[sb]);
-            uint32_t vis[NC];
+            uint32_t vis[TILE / 32];
 #pragma unroll
-            for (int c = 0; c < NC; ++c) vis[c] = 0xffffffffu;
+            for (int c4 = 0; c4 < TILE / 32; ++c4) vis[c4] = 0xffffffffu;
             if (need_mask) {
                 const int64_t limit = kv_end < causal_last + 1 ? kv_end : causal_last + 1;
 #pragma unroll
-                for (int c = 0; c < NC; ++c) vis[c] = visible_bits(kv0 + (half * NC + c) * 32, limit, mrow);
+                for (int c4 = 0; c4 < TILE / 32; ++c4) vis[c4] = visible_bits(kv0 + c4 * 32, limit, mrow);
             }
-            // tiles away from the diagonal and the ragged edge (the common case) skip the per-element visibility tests; four
-            // independent running maxima, so that consecutive instructions do not wait for one another
-            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            // tiles away from the diagonal and the ragged edge (the common case) skip the per-element visibility tests
+            float mt = -INFINITY;
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < NC; ++c)
+                for (int c4 = 0; c4 < TILE / 32; ++c4)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if ((vis[c] >> i) & 1u) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c][i]));
+                        if ((vis[c4] >> i) & 1u) mt = fmaxf(mt, __uint_as_float(r[c4][i]));
             } else {
 #pragma unroll
-                for (int c = 0; c < NC; ++c)
+                for (int c4 = 0; c4 < TILE / 32; ++c4)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c][i]));
-            }
-            float mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            if (SPLIT == 2) {
-                // the row maximum over all columns: mine and my partner's (slots alternate with the tile's parity, so a
-                // slot is rewritten only after another meeting has passed)
-                sh->xm[j & 1][half][row] = mt;
-                if (!meet()) { if (lane == 0) fail(sh, 13); ok = false; break; }
-                mt = fmaxf(mt, sh->xm[j & 1][half ^ 1][row]);
+                    for (int i = 0; i < 32; ++i) mt = fmaxf(mt, __uint_as_float(r[c4][i]));
             }
             // move the reference maximum?  (first visible score of the row, or growth beyond the threshold)
             float alpha = 1.f;
@@ -306,51 +277,43 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             // the previous tile's MMAs have read P (and, when rescaling, must have finished adding into O)
             if (!warp_wait(&sh->p_free, (uint32_t)((j & 1) ^ 1), lane)) { if (lane == 0) fail(sh, 10); ok = false; break; }
             if (j > 0 && __any_sync(0xffffffffu, move)) {
-                // rescale this warp's share of the accumulator rows (lanes whose maximum did not move multiply by one)
+                // rescale this warp's 32 rows of the accumulator (lanes whose maximum did not move multiply by one)
                 tc_fence_after();
                 l_run *= alpha;
 #pragma unroll
-                for (int c = 0; c < OC; ++c) {
+                for (int c4 = 0; c4 < HD / 32; ++c4) {
                     uint32_t o[32];
-                    tmem_ld32(tmem_o + lane_addr + (half * OC + c) * 32, o);
+                    tmem_ld32(tmem_o + lane_addr + c4 * 32, o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(tmem_o + lane_addr + (half * OC + c) * 32, o);
+                    tmem_st32(tmem_o + lane_addr + c4 * 32, o);
                 }
                 tmem_st_wait();
             } else {
                 l_run *= alpha;
             }
             const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref * p.sl2;
-            // P = 2^(s * scale * log2e - m_ref * log2e) into shared memory; four independent partial row sums.  MASKED is a
-            // compile-time switch: tiles that need no masking carry no visibility tests at all
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-            const auto exp_pass = [&](auto masked_tag) {
-                constexpr bool MASKED = decltype(masked_tag)::value;
+            float rowsum = 0.f;
 #pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    const int c4 = half * NC + c;     // 32-column group inside the 128-key tile
-                    const uint32_t base = sP + (uint32_t)(c4 >> 1) * CHUNK + (uint32_t)row * 128;
+            for (int c4 = 0; c4 < TILE / 32; ++c4) {
+                const uint32_t base = sP + (uint32_t)(c4 >> 1) * CHUNK + (uint32_t)row * 128;
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        float pv[8];
+                for (int t = 0; t < 4; ++t) {
+                    float pv[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            float e = ex2(fmaf(__uint_as_float(r[c][8 * t + i]), p.sl2, neg_m));
-                            if (MASKED && !((vis[c] >> (8 * t + i)) & 1u)) e = 0.f;
-                            pv[i] = e;
-                            rs4[i & 3] += e;
-                        }
-                        const uint32_t piece = (uint32_t)(((c4 & 1) * 4 + t) ^ (row & 7));
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (piece << 4)),
-                                     "r"(pack2<T>(pv[0], pv[1])), "r"(pack2<T>(pv[2], pv[3])),
-                                     "r"(pack2<T>(pv[4], pv[5])), "r"(pack2<T>(pv[6], pv[7])) : "memory");
+                    for (int i = 0; i < 8; ++i) {
+                        float e = ex2(fmaf(__uint_as_float(r[c4][8 * t + i]), p.sl2, neg_m));
+                        if (need_mask && !((vis[c4] >> (8 * t + i)) & 1u)) e = 0.f;
+                        pv[i] = e;
+                        rowsum += e;
                     }
+                    const uint32_t piece = (uint32_t)(((c4 & 1) * 4 + t) ^ (row & 7));
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (piece << 4)),
+                                 "r"(pack2<T>(pv[0], pv[1])), "r"(pack2<T>(pv[2], pv[3])),
+                                 "r"(pack2<T>(pv[4], pv[5])), "r"(pack2<T>(pv[6], pv[7])) : "memory");
                 }
-            };
-            if (need_mask) exp_pass(std::true_type{}); else exp_pass(std::false_type{});
-            const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores before the MMA's async-proxy reads
             tc_fence_before();
             __syncwarp();
@@ -360,20 +323,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         if (ok && J > 0) {
             if (!warp_wait(&sh->o_full, (uint32_t)((J - 1) & 1), lane)) { if (lane == 0) fail(sh, 12); ok = false; }
         }
-        if (ok && SPLIT == 2) {
-            // the row sum over all columns (both warps took their exponents against the same m_ref)
-            sh->xm[J & 1][half][row] = l_run;
-            if (!meet()) { if (lane == 0) fail(sh, 14); ok = false; }
-            else l_run += sh->xm[J & 1][half ^ 1][row];
-        }
         if (ok) {
             // normalise and store the row (the tensor-memory loads are warp-wide; only the stores depend on the row)
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             T* orow = (T*)p.o + (int64_t)b * p.o_batch + qi * p.o_tok + (int64_t)head * p.o_head;
             tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < OC; ++c) {
-                const int c4 = half * OC + c;
+            for (int c4 = 0; c4 < HD / 32; ++c4) {
                 uint32_t o[32];
                 if (J > 0) {
                     tmem_ld32(tmem_o + lane_addr + c4 * 32, o);
@@ -395,7 +351,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
                 }
             }
             tc_fence_before();
-            if (row_ok && p.lse && half == 0)
+            if (row_ok && p.lse)
                 p.lse[((int64_t)b * p.h + head) * p.sq + qi] = l_run > 0.f ? (m_ref * p.sl2 + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
         }
     }
@@ -412,26 +368,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-template <int HD, typename T, int SPLIT>
-int launch_fwd_split(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int64_t batch, cudaStream_t stream) {
+template <int HD, typename T>
+int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int64_t batch, cudaStream_t stream) {
     constexpr uint32_t TB = (HD / 64) * CHUNK;
     const size_t smem = 5 * TB + 2 * CHUNK + sizeof(AttnShared) + 1024;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(flash_fwd_kernel<HD, T, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -30;
+        if (cudaFuncSetAttribute(flash_fwd_kernel<HD, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -30;
         configured = true;
     }
     dim3 grid((unsigned)((p.sq + TILE - 1) / TILE), (unsigned)p.h, (unsigned)batch);
-    flash_fwd_kernel<HD, T, SPLIT><<<grid, 64 + 128 * SPLIT, smem, stream>>>(tq, tk, tv, p);
+    flash_fwd_kernel<HD, T><<<grid, ATT_THREADS, smem, stream>>>(tq, tk, tv, p);
     bmt_count_launch(1);
     return cudaGetLastError() == cudaSuccess ? 0 : -31;
-}
-
-template <int HD, typename T>
-int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int64_t batch, cudaStream_t stream) {
-    // BMT_ATTN_SPLIT=1: one softmax warp per row quarter instead of two
-    static const int split = [] { const char* e = getenv("BMT_ATTN_SPLIT"); return (e && atoi(e) == 1) ? 1 : 2; }();
-    return split == 2 ? launch_fwd_split<HD, T, 2>(tq, tk, tv, p, batch, stream) : launch_fwd_split<HD, T, 1>(tq, tk, tv, p, batch, stream);
 }
 
 
@@ -476,11 +425,8 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// SPLIT as in the forward kernel: with 2, the two warps that own the same 32 rows each take 64 of the 128 key columns of a
-// tile (P, dS) and half of the head-dim columns of dQ / dK / dV; they never have to talk to each other, since the row
-// statistics (lse, delta) come from outside.
-template <int HD, typename T, int SPLIT>
-__global__ void __launch_bounds__(64 + 128 * SPLIT, 1)
+template <int HD, typename T>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
                  const __grid_constant__ CUtensorMap tdo, const AttnBwdParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -507,7 +453,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 
     if (threadIdx.x == 0) {
         mbar_init(&sh->kv_full, 1); mbar_init(&sh->qdo_full, 1); mbar_init(&sh->qdo_empty, 1); mbar_init(&sh->sdp_full, 1);
-        mbar_init(&sh->pds_ready, 4 * SPLIT); mbar_init(&sh->dq_full, 1); mbar_init(&sh->tmem_free, 4 * SPLIT);
+        mbar_init(&sh->pds_ready, 4); mbar_init(&sh->dq_full, 1); mbar_init(&sh->tmem_free, 4);
         sh->failed = 0;
         fence_barrier_init();
     }
@@ -578,8 +524,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         }
     } else {
         const int quarter = warp & 3;
-        const int part = (warp - 2) >> 2;             // column share of this warp (always 0 when SPLIT = 1)
-        constexpr int OC = HD / 32 / SPLIT;           // 32-column groups of dQ / dK / dV per thread
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         bool ok = true;
@@ -602,51 +546,40 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             tc_fence_after();
             // A tensor-memory load costs a round trip of a few hundred nanoseconds however wide it is, so the loads of 64
             // columns of S and of dP are issued together and waited for once (two round trips per tile).
-            // MASKED is a compile-time switch: tiles away from the diagonal and the ragged edge carry no visibility tests.
-            // dS = P * (dP - delta) * scale is computed as P * (dP * scale - delta * scale): one FMA and one multiply.
-            const float nds = -delta_r * p.scale;
-            const auto tile_pass = [&](auto masked_tag) {
-                constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-                for (int half = (SPLIT == 2 ? part : 0); half < (SPLIT == 2 ? part + 1 : 2); ++half) {
-                    uint32_t rs[2][32], rd[2][32];
+            for (int half = 0; half < 2; ++half) {
+                uint32_t rs[2][32], rd[2][32];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        tmem_ld32(tmem + lane_addr + (half * 2 + u) * 32, rs[u]);
-                        tmem_ld32(tmem + lane_addr + C_DP + (half * 2 + u) * 32, rd[u]);
-                    }
-                    tmem_ld_wait();
+                for (int u = 0; u < 2; ++u) {
+                    tmem_ld32(tmem + lane_addr + (half * 2 + u) * 32, rs[u]);
+                    tmem_ld32(tmem + lane_addr + C_DP + (half * 2 + u) * 32, rd[u]);
+                }
+                tmem_ld_wait();
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int c4 = half * 2 + u;
-                        uint32_t bits = 0xffffffffu;
-                        if (MASKED)
-                            bits = alive ? visible_bits(kv0 + c4 * 32, kv_valid < causal_last + 1 ? kv_valid : causal_last + 1, mrow) : 0u;
-                        const uint32_t off = (uint32_t)half * CHUNK + (uint32_t)row * 128;
+                for (int u = 0; u < 2; ++u) {
+                    const int c4 = half * 2 + u;
+                    uint32_t bits = alive ? 0xffffffffu : 0u;
+                    if (need_mask && alive) bits = visible_bits(kv0 + c4 * 32, kv_valid < causal_last + 1 ? kv_valid : causal_last + 1, mrow);
+                    const uint32_t off = (uint32_t)half * CHUNK + (uint32_t)row * 128;
 #pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            float pv[8], ds[8];
+                    for (int t = 0; t < 4; ++t) {
+                        float pv[8], ds[8];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                float e = ex2(fmaf(__uint_as_float(rs[u][8 * t + i]), p.sl2, nlse));
-                                if (MASKED && !((bits >> (8 * t + i)) & 1u)) e = 0.f;
-                                pv[i] = e;
-                                ds[i] = e * fmaf(__uint_as_float(rd[u][8 * t + i]), p.scale, nds);
-                            }
-                            const uint32_t piece = (uint32_t)((u * 4 + t) ^ (row & 7)) << 4;
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off + piece),
-                                         "r"(pack2<T>(pv[0], pv[1])), "r"(pack2<T>(pv[2], pv[3])),
-                                         "r"(pack2<T>(pv[4], pv[5])), "r"(pack2<T>(pv[6], pv[7])) : "memory");
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sdS + off + piece),
-                                         "r"(pack2<T>(ds[0], ds[1])), "r"(pack2<T>(ds[2], ds[3])),
-                                         "r"(pack2<T>(ds[4], ds[5])), "r"(pack2<T>(ds[6], ds[7])) : "memory");
+                        for (int i = 0; i < 8; ++i) {
+                            const float e = ((bits >> (8 * t + i)) & 1u) ? ex2(fmaf(__uint_as_float(rs[u][8 * t + i]), p.sl2, nlse)) : 0.f;
+                            pv[i] = e;
+                            ds[i] = e * (__uint_as_float(rd[u][8 * t + i]) - delta_r) * p.scale;
                         }
+                        const uint32_t piece = (uint32_t)((u * 4 + t) ^ (row & 7)) << 4;
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off + piece),
+                                     "r"(pack2<T>(pv[0], pv[1])), "r"(pack2<T>(pv[2], pv[3])),
+                                     "r"(pack2<T>(pv[4], pv[5])), "r"(pack2<T>(pv[6], pv[7])) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sdS + off + piece),
+                                     "r"(pack2<T>(ds[0], ds[1])), "r"(pack2<T>(ds[2], ds[3])),
+                                     "r"(pack2<T>(ds[4], ds[5])), "r"(pack2<T>(ds[6], ds[7])) : "memory");
                     }
                 }
-            };
-            // rows without any visible key (lse = -inf) and rows beyond the sequence take the masked form, which zeroes them
-            // (decided for the warp as a whole: the tensor-memory loads inside must be executed by all 32 lanes together)
-            if (__any_sync(0xffffffffu, need_mask || !alive)) tile_pass(std::true_type{}); else tile_pass(std::false_type{});
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             __syncwarp();
@@ -655,9 +588,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             tc_fence_after();
             float* dq_row = p.dq_acc + (((int64_t)b * p.sq + qi) * p.h + head) * p.d;
             {
-                uint32_t r[OC][32];
+                uint32_t r[HD / 32][32];
 #pragma unroll
-                for (int c = 0; c < OC; ++c) tmem_ld32(tmem + lane_addr + C_DQ + (part * OC + c) * 32, r[c]);
+                for (int c4 = 0; c4 < HD / 32; ++c4) tmem_ld32(tmem + lane_addr + C_DQ + c4 * 32, r[c4]);
                 tmem_ld_wait();
                 // the values are in registers: the tensor memory may be overwritten by the next tile's MMAs while the
                 // reductions below are still being issued
@@ -666,12 +599,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
                 if (lane == 0) mbar_arrive(&sh->tmem_free);
                 if (row_ok) {
 #pragma unroll
-                    for (int c = 0; c < OC; ++c)
+                    for (int c4 = 0; c4 < HD / 32; ++c4)
 #pragma unroll
                         for (int t = 0; t < 8; ++t)
-                            if ((part * OC + c) * 32 + t * 4 < p.d)
-                                red_add_v4(dq_row + (part * OC + c) * 32 + t * 4, __uint_as_float(r[c][4 * t]), __uint_as_float(r[c][4 * t + 1]),
-                                           __uint_as_float(r[c][4 * t + 2]), __uint_as_float(r[c][4 * t + 3]));
+                            if (c4 * 32 + t * 4 < p.d)
+                                red_add_v4(dq_row + c4 * 32 + t * 4, __uint_as_float(r[c4][4 * t]), __uint_as_float(r[c4][4 * t + 1]),
+                                           __uint_as_float(r[c4][4 * t + 2]), __uint_as_float(r[c4][4 * t + 3]));
                 }
             }
         }
@@ -682,8 +615,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             T* dkr = (T*)p.dk + (int64_t)b * p.dk_batch + kj * p.dk_tok + (int64_t)kvh * p.dk_head;
             T* dvr = (T*)p.dv + (int64_t)b * p.dv_batch + kj * p.dv_tok + (int64_t)kvh * p.dv_head;
 #pragma unroll
-            for (int c = 0; c < OC; ++c) {
-                const int c4 = part * OC + c;
+            for (int c4 = 0; c4 < HD / 32; ++c4) {
                 uint32_t rk[32], rv[32];
                 if (n_it > 0) {
                     tmem_ld32(tmem + lane_addr + C_DK + c4 * 32, rk);
@@ -763,27 +695,20 @@ __global__ void attn_dq_convert_kernel(const float* acc, T* dq, int64_t q_tok, i
     bmt::st16(dq + bb * q_batch + qi * q_tok + head * q_head + c, o);
 }
 
-template <int HD, typename T, int SPLIT>
-int launch_bwd_split(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo, const AttnBwdParams& p,
-                     int64_t batch, cudaStream_t stream) {
+template <int HD, typename T>
+int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo, const AttnBwdParams& p,
+               int64_t batch, cudaStream_t stream) {
     constexpr uint32_t TB = (HD / 64) * CHUNK;
     const size_t smem = 4 * TB + 4 * CHUNK + sizeof(BwdShared) + 1024;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(flash_bwd_kernel<HD, T, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -30;
+        if (cudaFuncSetAttribute(flash_bwd_kernel<HD, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -30;
         configured = true;
     }
     dim3 grid((unsigned)((p.sk + TILE - 1) / TILE), (unsigned)p.hk, (unsigned)batch);
-    flash_bwd_kernel<HD, T, SPLIT><<<grid, 64 + 128 * SPLIT, smem, stream>>>(tq, tk, tv, tdo, p);
+    flash_bwd_kernel<HD, T><<<grid, ATT_THREADS, smem, stream>>>(tq, tk, tv, tdo, p);
     bmt_count_launch(1);
     return cudaGetLastError() == cudaSuccess ? 0 : -31;
-}
-
-template <int HD, typename T>
-int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo, const AttnBwdParams& p,
-               int64_t batch, cudaStream_t stream) {
-    static const int split = [] { const char* e = getenv("BMT_ATTN_SPLIT"); return (e && atoi(e) == 1) ? 1 : 2; }();
-    return split == 2 ? launch_bwd_split<HD, T, 2>(tq, tk, tv, tdo, p, batch, stream) : launch_bwd_split<HD, T, 1>(tq, tk, tv, tdo, p, batch, stream);
 }
 
 template <typename T>

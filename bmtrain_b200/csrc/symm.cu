@@ -78,7 +78,18 @@ struct RsArgs {
     unsigned char* overflow;   // set to 1 when an inf/nan shows up in the reduced values
     int* status;               // set to a non-zero code when the wait ran out
     uint64_t limit_ns;
+    float* acc32;              // optional fp32 copy of the partition gradient: with `accumulate` the sum is added to IT (not to
+                               // the rounded `out`), so gradients accumulated over micro-steps are rounded once, at the end
+    float* sqsum;              // optional: += sum of squares of the values written (for the gradient norm; zero it before)
 };
+
+// Σ v² of one CTA into *sqsum (one atomic per CTA; the order of the CTAs is not fixed, so the last bits may differ from
+// run to run -- the gradient norm is a diagnostic / clipping quantity, the gradients themselves stay bit-reproducible)
+__device__ __forceinline__ void add_sqsum(float* sqsum, float local) {
+    __shared__ float sq_s[33];
+    const float total = bmt::block_allreduce<false>(local, sq_s);
+    if (threadIdx.x == 0 && sqsum) atomicAdd(sqsum, total);
+}
 
 // WMAX: upper bound of the group size (loads of all ranks are issued before the first add); U: vectors per thread per
 // trip.  WMAX * U independent 16-byte loads are in flight per thread, which is what hides the NVLink round trip.
@@ -108,6 +119,8 @@ __global__ void __launch_bounds__(256, 2) fused_rs_kernel(RsArgs a) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     T* __restrict__ out = (T*)a.out;
     bool bad = false;
+    float sq = 0.f;
+    const bool acc_half = a.accumulate && !a.acc32, acc_f32 = a.accumulate && a.acc32;
     for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
         bmt::Vec16<T> v[U][WMAX];
         bmt::Vec16<T> old[U];
@@ -118,7 +131,7 @@ __global__ void __launch_bounds__(256, 2) fused_rs_kernel(RsArgs a) {
 #pragma unroll
                 for (int j = 0; j < WMAX; ++j)
                     if (j < a.world) v[u][j] = bmt::ld16((const T*)a.peer[j] + base + i * 8);
-                if (a.accumulate) old[u] = bmt::ld16(out + i * 8);
+                if (acc_half) old[u] = bmt::ld16(out + i * 8);
             }
         }
 #pragma unroll
@@ -133,9 +146,15 @@ __global__ void __launch_bounds__(256, 2) fused_rs_kernel(RsArgs a) {
                     for (int k = 0; k < 8; ++k) acc[k] += bmt::Cvt<T>::to_f(v[u][j].v[k]);
                 }
             bmt::Vec16<T> o;
-            if (a.accumulate) {
+            if (acc_half) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) acc[k] = acc[k] * a.scale + bmt::Cvt<T>::to_f(old[u].v[k]);
+            } else if (acc_f32) {
+                // local memory, read late on purpose: keeping it in registers next to the peer loads above would spill
+                const float4 lo = *reinterpret_cast<const float4*>(a.acc32 + i * 8), hi = *reinterpret_cast<const float4*>(a.acc32 + i * 8 + 4);
+                const float o32[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = acc[k] * a.scale + o32[k];
             } else {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) acc[k] *= a.scale;
@@ -145,11 +164,17 @@ __global__ void __launch_bounds__(256, 2) fused_rs_kernel(RsArgs a) {
                 bad |= !(fabsf(acc[k]) <= 3.402823466e38f);
                 o.v[k] = bmt::Cvt<T>::from_f(acc[k]);
                 bad |= !(fabsf(bmt::Cvt<T>::to_f(o.v[k])) <= 3.402823466e38f);
+                sq += acc[k] * acc[k];
             }
             bmt::st16(out + i * 8, o);
+            if (a.acc32) {
+                *reinterpret_cast<float4*>(a.acc32 + i * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *reinterpret_cast<float4*>(a.acc32 + i * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
         }
     }
     if (__syncthreads_or(bad) && threadIdx.x == 0 && a.overflow) *a.overflow = 1;
+    if (a.sqsum) add_sqsum(a.sqsum, sq);
 }
 
 // ---- in-switch reduction (NVLS): one multimem.ld_reduce per 16 bytes reads the same offset of every rank's buffer through
@@ -187,6 +212,8 @@ __global__ void __launch_bounds__(256, 2) fused_rs_mc_kernel(RsArgs a, const T* 
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     T* __restrict__ out = (T*)a.out;
     bool bad = false;
+    float sq = 0.f;
+    const bool acc_half = a.accumulate && !a.acc32, acc_f32 = a.accumulate && a.acc32;
     for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
         uint32_t v[U][4];
         bmt::Vec16<T> old[U];
@@ -195,7 +222,7 @@ __global__ void __launch_bounds__(256, 2) fused_rs_mc_kernel(RsArgs a, const T* 
             const int64_t i = i0 + u * stride;
             if (i < nvec) {
                 mc_ld_reduce<T>(mc + base + i * 8, v[u]);
-                if (a.accumulate) old[u] = bmt::ld16(out + i * 8);
+                if (acc_half) old[u] = bmt::ld16(out + i * 8);
             }
         }
 #pragma unroll
@@ -203,18 +230,32 @@ __global__ void __launch_bounds__(256, 2) fused_rs_mc_kernel(RsArgs a, const T* 
             const int64_t i = i0 + u * stride;
             if (i >= nvec) continue;
             bmt::Vec16<T> sum = *reinterpret_cast<bmt::Vec16<T>*>(v[u]), o;
+            float o32[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (acc_f32) {
+                const float4 lo = *reinterpret_cast<const float4*>(a.acc32 + i * 8), hi = *reinterpret_cast<const float4*>(a.acc32 + i * 8 + 4);
+                o32[0] = lo.x; o32[1] = lo.y; o32[2] = lo.z; o32[3] = lo.w; o32[4] = hi.x; o32[5] = hi.y; o32[6] = hi.z; o32[7] = hi.w;
+            }
+            float f8[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 float f = bmt::Cvt<T>::to_f(sum.v[k]) * a.scale;
-                if (a.accumulate) f += bmt::Cvt<T>::to_f(old[u].v[k]);
+                if (acc_half) f += bmt::Cvt<T>::to_f(old[u].v[k]);
+                if (acc_f32) f += o32[k];
                 bad |= !(fabsf(f) <= 3.402823466e38f);
                 o.v[k] = bmt::Cvt<T>::from_f(f);
                 bad |= !(fabsf(bmt::Cvt<T>::to_f(o.v[k])) <= 3.402823466e38f);
+                sq += f * f;
+                f8[k] = f;
             }
             bmt::st16(out + i * 8, o);
+            if (a.acc32) {
+                *reinterpret_cast<float4*>(a.acc32 + i * 8) = make_float4(f8[0], f8[1], f8[2], f8[3]);
+                *reinterpret_cast<float4*>(a.acc32 + i * 8 + 4) = make_float4(f8[4], f8[5], f8[6], f8[7]);
+            }
         }
     }
     if (__syncthreads_or(bad) && threadIdx.x == 0 && a.overflow) *a.overflow = 1;
+    if (a.sqsum) add_sqsum(a.sqsum, sq);
 }
 
 template <typename T>
@@ -347,7 +388,18 @@ extern "C" int bmt_peer_copy(void* dst, const void* src, int64_t nbytes, int gri
 // buffer 16-byte aligned.  dtype: 0 fp16, 1 bf16, 2 fp32.
 static int fused_reduce_scatter_impl(const void* const* peers, const void* multicast, void* const* peer_flags, int world, int rank,
                                      int slot, unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
-                                     void* overflow_u8, void* status_i32, double timeout_s, void* stream);
+                                     void* overflow_u8, void* status_i32, double timeout_s, void* stream, void* acc32 = nullptr,
+                                     void* sqsum = nullptr);
+
+// Same two reductions with the optional extras: `acc32` (fp32 partition gradient that accumulation goes through) and
+// `sqsum_f32` (+= sum of squares of the values written); `multicast` null selects plain peer loads.
+extern "C" int bmt_fused_reduce_scatter_ex(const void* const* peers, const void* multicast, void* const* peer_flags, int world,
+                                           int rank, int slot, unsigned int epoch, int64_t part, void* out, int accumulate,
+                                           float scale, int dtype, void* acc32, void* sqsum_f32, void* overflow_u8,
+                                           void* status_i32, double timeout_s, void* stream) {
+    return fused_reduce_scatter_impl(multicast ? nullptr : peers, multicast, peer_flags, world, rank, slot, epoch, part, out,
+                                     accumulate, scale, dtype, overflow_u8, status_i32, timeout_s, stream, acc32, sqsum_f32);
+}
 
 extern "C" int bmt_fused_reduce_scatter(const void* const* peers, void* const* peer_flags, int world, int rank, int slot,
                                         unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
@@ -367,7 +419,8 @@ extern "C" int bmt_fused_reduce_scatter_mc(const void* multicast, void* const* p
 
 static int fused_reduce_scatter_impl(const void* const* peers, const void* multicast, void* const* peer_flags, int world, int rank,
                                      int slot, unsigned int epoch, int64_t part, void* out, int accumulate, float scale, int dtype,
-                                     void* overflow_u8, void* status_i32, double timeout_s, void* stream) {
+                                     void* overflow_u8, void* status_i32, double timeout_s, void* stream, void* acc32,
+                                     void* sqsum) {
     if (world < 1 || world > 8) return -30;
     if (part % 8 != 0) return -31;
     RsArgs a;
@@ -376,6 +429,8 @@ static int fused_reduce_scatter_impl(const void* const* peers, const void* multi
     a.world = world; a.rank = rank; a.slot = slot; a.epoch = epoch; a.part = part; a.out = out; a.accumulate = accumulate;
     a.scale = scale; a.overflow = (unsigned char*)overflow_u8; a.status = (int*)status_i32;
     a.limit_ns = (uint64_t)(timeout_s * 1e9);
+    a.acc32 = (float*)acc32;
+    a.sqsum = (float*)sqsum;
     int64_t blocks = bmt::ceil_div64(part / 8, 256);
     if (blocks > 148 * 4) blocks = 148 * 4;
     if (blocks < 1) blocks = 1;

@@ -14,7 +14,7 @@ from typing import Optional
 
 import torch
 
-from ..block_layer import drain_pending, params_changed
+from ..block_layer import drain_pending, fused_sq_norms, grads_modified, params_changed
 from ..global_var import config
 from ..lr_scheduler.warmup import WarmupLRScheduler
 from ..ops import infnan
@@ -156,6 +156,9 @@ class OptimManager:
 
     def backward(self, loss: torch.Tensor):
         """Backward of the scaled loss; returns once all gradient reductions are queued behind it."""
+        # with gradient accumulation many backward passes separate two optimizer steps: a kernel that gave up waiting for
+        # another rank is reported here too (one pass late, without a host sync)
+        check_peer_status()
         for optimizer in self.optimizers:
             announce = getattr(optimizer, "_expect_step", None)
             if announce is not None:
@@ -209,7 +212,13 @@ class OptimManager:
             norm_type = float(norm_type)
             total = torch.zeros(1, dtype=torch.float32, device=dev)
             if norm_type == 2.0:
-                infnan.multi_sq_norm([g if g.is_contiguous() else g.contiguous() for g in grads], total)
+                # buckets whose gradients came out of the fused reduce-scatter kernel bring their sum of squares along; only
+                # the remaining gradients are read again
+                known, parts = fused_sq_norms(parameters)
+                rest = [p.grad.data for p in parameters if p.grad is not None and id(p) not in known]
+                infnan.multi_sq_norm([g if g.is_contiguous() else g.contiguous() for g in rest], total)
+                for part in parts:
+                    total += part
             else:
                 for g in grads:
                     total += g.float().norm(norm_type) ** norm_type
@@ -217,6 +226,7 @@ class OptimManager:
             total_norm = total[0] ** (1.0 / norm_type)
         clip_coef = float(max_norm * scale) / (total_norm + eps)
         infnan.multi_scale(grads, clip_coef.reshape(1))
+        grads_modified()
         for optimizer in self.optimizers:
             if hasattr(optimizer, "_invalidate_staged"):
                 optimizer._invalidate_staged()

@@ -244,11 +244,13 @@ class PeerRuntime:
             "push all-gather kernel")
 
     def reduce_scatter(self, full: SymmetricBuffer, row: int, part: int, out: torch.Tensor, accumulate: bool,
-                       scale: float = 1.0) -> None:
+                       scale: float = 1.0, acc32: Optional[torch.Tensor] = None, sqsum: Optional[torch.Tensor] = None) -> None:
         """``out`` (+)= scale * sum over ranks of their ``full`` buffer, restricted to this rank's partition.
 
         Runs on the current stream; the kernel itself tells the peers that this rank's buffer is complete and
         waits (bounded) for theirs, adds in fp32 in rank order, and ORs inf/nan into ``self.overflow``.
+        ``acc32``: fp32 copy of the partition gradient; accumulation then goes through it and ``out`` is its rounding.
+        ``sqsum``: one fp32 element that receives += the sum of squares of the values written.
         """
         lib = _native.cuda_lib()
         epoch = self.next_epoch(row)
@@ -258,9 +260,19 @@ class PeerRuntime:
             # cross-rank hand-shake is done by one CTA, the reduction kernel itself then never waits
             self.signal_wait(row, epoch, signal=True, wait=True)
             epoch = 0
-        if getattr(full, "mc_ptr", 0):
+        mc = getattr(full, "mc_ptr", 0)
+        if acc32 is not None or sqsum is not None:
+            _native.check(lib.bmt_fused_reduce_scatter_ex(
+                full.ptr_table(), ctypes.c_void_p(mc) if mc else None, self.flag_ptrs, ctypes.c_int(self.comm.size),
+                ctypes.c_int(self.comm.rank), ctypes.c_int(row), ctypes.c_uint(epoch), ctypes.c_int64(part), _native.ptr(out),
+                ctypes.c_int(int(accumulate)), ctypes.c_float(scale), ctypes.c_int(dt),
+                _native.ptr(acc32) if acc32 is not None else None, _native.ptr(sqsum) if sqsum is not None else None,
+                _native.ptr(self.overflow), _native.ptr(self.status), ctypes.c_double(self.timeout_s), _native.stream_handle()),
+                "fused reduce-scatter kernel with fp32 accumulator / sum of squares")
+            return
+        if mc:
             _native.check(lib.bmt_fused_reduce_scatter_mc(
-                ctypes.c_void_p(full.mc_ptr), self.flag_ptrs, ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank), ctypes.c_int(row),
+                ctypes.c_void_p(mc), self.flag_ptrs, ctypes.c_int(self.comm.size), ctypes.c_int(self.comm.rank), ctypes.c_int(row),
                 ctypes.c_uint(epoch), ctypes.c_int64(part), _native.ptr(out), ctypes.c_int(int(accumulate)), ctypes.c_float(scale),
                 ctypes.c_int(dt), _native.ptr(self.overflow), _native.ptr(self.status), ctypes.c_double(self.timeout_s),
                 _native.stream_handle()), "fused reduce-scatter kernel (multimem)")

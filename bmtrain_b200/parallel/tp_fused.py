@@ -9,6 +9,7 @@ back to back.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -21,10 +22,18 @@ def _fused_available(x: torch.Tensor, comm: Communicator) -> bool:
     if not x.is_cuda or comm.size == 1:
         return False
     # With ZeRO groups larger than one, kernels of the data-parallel dimension that wait for other ranks run next to the
-    # tensor-parallel ones.  The fused kernels then take their non-spinning form (``symm.no_spin``): pusher CTAs are the
-    # first of their grid, and the GEMM -> reduce-scatter leaves waiting and summing to separate small launches.
+    # tensor-parallel ones.  The fused kernels have a non-spinning form for that layout (``symm.no_spin``: pusher CTAs are
+    # the first of their grid, GEMM -> reduce-scatter leaves waiting and summing to separate small launches), which is
+    # verified kernel by kernel on two GPUs; the one full-size run of tensor parallel 2 x ZeRO 4 on eight GPUs with them
+    # did not get through its first optimizer step (one tensor-parallel pair fell behind the others and every rank ended
+    # up waiting in an all-gather).  Until that has been understood on hardware, this layout takes NCCL + separate GEMMs
+    # unless BMT_TP_FUSED_WITH_ZERO=1 asks for the fused kernels.
+    from ..global_var import config
     from . import symm
 
+    zero = config.get("pp_tp_zero_comm") if config.get("pipe_size", 1) > 1 else config.get("tp_zero_comm")
+    if zero is not None and zero.size > 1 and os.environ.get("BMT_TP_FUSED_WITH_ZERO", "0") != "1":
+        return False
     return symm.peer_runtime_ready(comm)
 
 

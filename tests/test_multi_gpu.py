@@ -233,9 +233,12 @@ def _compare_grads(bmt, model, ref, rel):
 
 
 def body_tp_zero_gpu():
-    """bf16 GPT with tensor parallel 2 x ZeRO 2 on 4 GPUs, two accumulated backward passes.  The tensor-parallel pairs run on
-    the fused kernels in their non-spinning form next to the ZeRO gathers and the fused gradient reduce-scatter; loss and
-    gradients follow the fp32 single-process model."""
+    """bf16 GPT with tensor parallel 2 x ZeRO 2 on 4 GPUs, two accumulated backward passes, next to the ZeRO gathers and the
+    fused gradient reduce-scatter; loss and gradients follow the fp32 single-process model.  By default the tensor-parallel
+    pairs take NCCL + separate GEMMs in this layout; with BMT_TP_FUSED_WITH_ZERO=1 they run on the fused kernels in their
+    non-spinning form."""
+    import os
+
     import bmtrain_b200 as bmt
     from bmtrain_b200.parallel import fused_ops, symm
 
@@ -260,7 +263,10 @@ def body_tp_zero_gpu():
         (loss * 256.0 / dp).backward()
         losses.append(loss.item())
     bmt.synchronize()
-    assert fused_ops.calls["ag_gemm"] > 0 and fused_ops.calls["gemm_rs"] > 0, fused_ops.calls
+    if os.environ.get("BMT_TP_FUSED_WITH_ZERO") == "1":
+        assert fused_ops.calls["ag_gemm"] > 0 and fused_ops.calls["gemm_rs"] > 0, fused_ops.calls
+    else:
+        assert fused_ops.calls["ag_gemm"] == 0 and fused_ops.calls["gemm_rs"] == 0, fused_ops.calls
     for d in range(dp):
         for it in range(2):
             ids = all_ids[d, it]
@@ -276,8 +282,10 @@ def body_tp_zero_gpu():
     assert _native.cuda_lib().bmt_gemm_status() == 0
 
 
-def test_tensor_parallel_with_zero_4gpu():
+@pytest.mark.parametrize("fused", [False, True])
+def test_tensor_parallel_with_zero_4gpu(fused, monkeypatch):
     _need(4)
+    monkeypatch.setenv("BMT_TP_FUSED_WITH_ZERO", "1" if fused else "0")
     run_distributed("test_multi_gpu", "body_tp_zero_gpu", 4, device="cuda", init_kwargs=dict(tp_size=2))
 
 
