@@ -88,6 +88,9 @@ typedef struct {
     const void* residual; int64_t ldr;                                // + residual (m x n, operand dtype)
     const void* aux; int64_t ld_aux; int aux_mode;                    // 1: *= (aux > 0), 2: *= gelu'(aux)
 } BmtGemmDesc;
+// Fused GEMM + collective kernels launched from now on leave `n` SMs (even, at most 64) out of their grids, so that a kernel
+// of another parallel dimension can start while their CTAs wait for other ranks; 0 restores full grids.
+int bmt_gemm_reserve_sms(int n);
 int bmt_gemm_ex(const BmtGemmDesc* desc, void* stream);
 
 // C[M,N] (+)= alpha * op(A) op(B) (+ bias) with optional activation; majors: 0 = reduction dim contiguous, 1 = output dim contiguous.

@@ -1074,6 +1074,10 @@ int make_map_mn5(CUtensorMap* out, const void* ptr, int dtype, int64_t mn, int64
 }
 
 int g_num_sms = 0;
+// SMs that fused (compute + collective) kernels leave free.  Their CTAs wait for other ranks while they hold their SM; when
+// kernels of another parallel dimension (NCCL gathers of a ZeRO group) must be able to start next to them at any time, a
+// few SMs stay out of the fused grids so that such a kernel always finds room (bmt_gemm_reserve_sms).
+int g_reserved_sms = 0;
 
 // Tile selection.  Per k-block (64 deep) an SM spends about 2.05 * BN clocks on the MMAs of its 128 accumulator rows
 // and has to pull (128 + BN / ncta) * 128 bytes from L2 at about 64 bytes per clock; the slower of the two sets
@@ -1138,11 +1142,12 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     p.M = m; p.N = n; p.K = k;
     p.a_mn = a_major; p.b_mn = b_major;
     const int comm_ctas = (fused && (fused->mode == 2 || fused->mode == 3)) ? fused->ag_ctas : 0;
-    if (fused) g_num_sms -= comm_ctas;  // tile choice for the CTAs that do math
+    const int held_back = fused ? comm_ctas + g_reserved_sms : 0;
+    if (fused) g_num_sms -= held_back;  // tile choice for the CTAs that do math
     // a fused kernel can run as CTA pairs when its pusher CTAs pair up too and (mode 2) a rank's rows fill whole 256-row tiles
     const bool pair_ok = !fused || (comm_ctas % 2 == 0 && (fused->mode != 2 || fused->ag_rows % (2 * BM) == 0));
     TileChoice tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, force_bn, pair_ok ? force_cta2 : 0);
-    if (fused) g_num_sms += comm_ctas;
+    if (fused) g_num_sms += held_back;
     if (tc.bn == 0) tc = pick_tile(m, n, k, batch_inner * batch_outer, b_major != 0, 0, -1);  // forced shape not applicable here
     if (tc.bn == 0) return -22;
     p.bn = tc.bn;
@@ -1216,7 +1221,7 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
     FusedComm none;
     memset(&none, 0, sizeof(none));
     if (fused) {
-        const int compute = (g_num_sms - comm_ctas) / ncta;   // CTAs (or CTA pairs) that do math
+        const int compute = (g_num_sms - held_back) / ncta;   // CTAs (or CTA pairs) that do math
         const unsigned grid = (unsigned)(ncta * (tiles < compute ? tiles : compute)) + comm_ctas;
         FusedComm fc = *fused;
         if (fc.mode == 3) fc.bg_first_block = (int)(((fc.bg_first / k) / p.bn) % p.n_blocks);
@@ -1272,6 +1277,11 @@ int launch_gemm(const BmtGemmDesc& g, cudaStream_t stream, const FusedComm* fuse
 }
 
 }  // namespace
+
+extern "C" int bmt_gemm_reserve_sms(int n) {
+    g_reserved_sms = n <= 0 ? 0 : (n > 64 ? 64 : (n & ~1));
+    return 0;
+}
 
 extern "C" int bmt_gemm_ex(const BmtGemmDesc* desc, void* stream) { return launch_gemm(*desc, (cudaStream_t)stream); }
 

@@ -58,6 +58,20 @@ def kernel_stats() -> dict:
             "rs_wait_us_max": out[5] / 1e3, "rs_total_us_max": out[6] / 1e3, "rs_wait_us_sum": out[7] / 1e3}
 
 
+_reserved = [None]
+
+
+def _reserve_sms() -> None:
+    """When kernels of another parallel dimension run next to the fused ones (``symm.no_spin``), the fused grids leave
+    ``BMT_RESERVED_SMS`` SMs (default 16) free: their CTAs hold an SM while they wait for rows of another rank, and an NCCL
+    gather of the ZeRO group that cannot start on this rank keeps a rank of another pair waiting -- a cycle over pairs
+    and groups that only the bounded waits would break.  (NCCL's own grid can be capped to fit with ``NCCL_MAX_CTAS``.)"""
+    want = int(os.environ.get("BMT_RESERVED_SMS", "16")) if symm.no_spin() else 0
+    if _reserved[0] != want:
+        _native.cuda_lib().bmt_gemm_reserve_sms(ctypes.c_int(want))
+        _reserved[0] = want
+
+
 def _next_parity(rt, key: Tuple) -> int:
     # ring positions and grid counters belong to the runtime: they start over together with its epochs when the
     # process group is torn down and set up again, and two communicators never share them
@@ -92,6 +106,7 @@ def gemm_rs(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
         return None
     x, weight = _tma_ready(x), _tma_ready(weight)
     lib = _native.cuda_lib()
+    _reserve_sms()
     rows = M // W
     es = x.element_size()
     base = ("rs", M, N, K, x.dtype, b_is_kn)
@@ -145,6 +160,7 @@ def ag_gemm(x_local: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     if not x_local.is_contiguous() or x_local.data_ptr() % 16:
         x_local = x_local.contiguous()  # the pushers copy flat 32 KiB pieces
     lib = _native.cuda_lib()
+    _reserve_sms()
     es = x_local.element_size()
     # everything that decides how the pushers cut the rows (pusher count, runs per block) has to be constant per key: the
     # per-block counters on the peers grow by the same amount every time the key's buffers are used
