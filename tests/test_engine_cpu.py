@@ -613,3 +613,40 @@ def test_offload_optimizer_host_memory_sizing(bmt_cpu, monkeypatch):
     with pytest.raises(MemoryError):
         opt.step()
     assert len(opt.state[p]) == 0
+
+
+def test_known_gradient_norms_are_only_used_when_they_apply(bmt_cpu):
+    """``fused_sq_norms`` hands ``clip_grad_norm`` the sum of squares a reduce-scatter kernel left behind: only for buckets
+    all of whose gradient holders are asked for, and only until gradients are rewritten in place."""
+    from bmtrain_b200 import block_layer as BL
+
+    class Slot:
+        def __init__(self, p):
+            self.param = p
+
+    def bucket(n_params, value):
+        b = BL._Bucket("k", torch.float32, None, bmt_cpu.config["comm"])
+        b.storage = torch.nn.Parameter(torch.zeros(4))
+        b.storage.grad = torch.ones(4)
+        b.slots = [Slot(torch.nn.Parameter(torch.zeros(2))) for _ in range(n_params)]
+        b.sqsum = torch.tensor([value])
+        b.sq_tag = BL._grad_epoch[0]
+        BL._fused_buckets.add(b)
+        return b
+
+    b1, b2 = bucket(2, 3.0), bucket(2, 5.0)
+    inner1 = [s.param for s in b1.slots]
+    other = torch.nn.Parameter(torch.zeros(3))
+    # all holders of b1 asked for, only one of b2: b1 counts, b2 does not
+    known, parts = BL.fused_sq_norms(inner1 + [b2.slots[0].param, other])
+    assert known == {id(p) for p in inner1} and [float(t) for t in parts] == [3.0]
+    # the flat storage parameter stands for its bucket as well
+    known, parts = BL.fused_sq_norms([b2.storage])
+    assert known == {id(b2.storage)} and [float(t) for t in parts] == [5.0]
+    # dropped gradients and in-place rewrites invalidate the figures
+    b1.storage.grad = None
+    assert BL.fused_sq_norms(inner1)[1] == []
+    BL.grads_modified()
+    assert BL.fused_sq_norms([b2.storage]) == (set(), [])
+    BL._fused_buckets.discard(b1)
+    BL._fused_buckets.discard(b2)

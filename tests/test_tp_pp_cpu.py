@@ -173,3 +173,68 @@ def body_tp_helpers():
 
 def test_tp_helper_functions_cpu():
     run_distributed("test_tp_pp_cpu", "body_tp_helpers", 2, init_kwargs=dict(tp_size=2))
+
+
+def body_tp_linear_modules():
+    """Column- and row-parallel linears, every flag combination, inside a Block and bare, against ``torch.nn.Linear`` with
+    the full weight (the intent of the reference's ``tests/test_column_parallel_linear.py:6-75`` and
+    ``tests/test_row_parallel_linear.py:6-54``): output, weight / bias gradient of this rank's shard, input gradient."""
+    import bmtrain_b200 as bmt
+
+    tp, r = bmt.config["tp_size"], bmt.config["topology"].tp_id
+    torch.manual_seed(100)
+    full = torch.nn.Linear(8, 8)
+    x = torch.randn(8, 4, 8, requires_grad=True)
+    y_ref = full(x)
+    y_ref.sum().backward()
+    w_ref, b_ref, gx_ref = full.weight.grad.clone(), full.bias.grad.clone(), x.grad.clone()
+
+    def build(cls, blocked, **kw):
+        mod = cls(8, 8, dtype=torch.float32, **kw)
+        if blocked:
+            mod = bmt.Block(mod)
+        bmt.init_parameters(mod)
+        mod.load_state_dict(full.state_dict())
+        return mod
+
+    for blocked in (False, True):
+        for gather_input, gather_output in ((True, True), (True, False), (False, True)):
+            mod = build(bmt.nn.ColumnParallelLinear, blocked, gather_input=gather_input, gather_output=gather_output)
+            xin = (x.detach().chunk(tp, dim=0)[r] if gather_input else x.detach()).clone().requires_grad_()
+            y = mod(xin)
+            want = y_ref if gather_output else y_ref.chunk(tp, dim=-1)[r]
+            tag = ("column", blocked, gather_input, gather_output)
+            assert torch.allclose(y, want, atol=1e-5), tag
+            y.sum().backward()
+            bmt.synchronize()
+            inner = mod._module if blocked else mod
+            gw, gb = _local_grad(bmt, mod, inner, "weight"), _local_grad(bmt, mod, inner, "bias")
+            # a gathered output is a replicated quantity: its backward hands every rank the gradient of its own slice
+            assert torch.allclose(gw, w_ref.chunk(tp, dim=0)[r].reshape(-1), atol=1e-4), ("dW",) + tag
+            assert torch.allclose(gb, b_ref.chunk(tp, dim=0)[r].reshape(-1), atol=1e-4), ("db",) + tag
+            want_gx = gx_ref.chunk(tp, dim=0)[r] if gather_input else gx_ref
+            assert torch.allclose(xin.grad, want_gx, atol=1e-4), ("dx",) + tag
+        for split_input in (True, False):
+            mod = build(bmt.nn.RowParallelLinear, blocked, split_input=split_input, all_reduce_output=True)
+            xin = x.detach().chunk(tp, dim=0 if split_input else 2)[r].clone().requires_grad_()
+            y = mod(xin)
+            assert torch.allclose(y, y_ref, atol=1e-5), ("row", blocked, split_input)
+            y.sum().backward()
+            bmt.synchronize()
+            inner = mod._module if blocked else mod
+            gw = _local_grad(bmt, mod, inner, "weight")
+            gb = _local_grad(bmt, mod, inner, "bias")
+            assert torch.allclose(gw, w_ref.chunk(tp, dim=1)[r].reshape(-1), atol=1e-4), ("row dW", blocked, split_input)
+            assert torch.allclose(gb, b_ref.reshape(-1), atol=1e-4), ("row db", blocked, split_input)
+
+
+def _local_grad(bmt, mod, inner, name):
+    """Gradient of this rank's shard of ``inner.<name>``, flattened (attribute access on a distributed module returns the
+    gathered tensor; the parameter itself, with its gradient, sits in ``_parameters``)."""
+    p = inner._parameters[name]
+    assert p.grad is not None, f"no gradient on {name}"
+    return p.grad.detach().reshape(-1).clone()
+
+
+def test_tp_linear_modules_cpu():
+    run_distributed("test_tp_pp_cpu", "body_tp_linear_modules", 2, init_kwargs=dict(tp_size=2))
