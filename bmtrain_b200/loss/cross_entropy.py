@@ -2,9 +2,10 @@
 
 ``FusedCrossEntropy`` takes half-precision logits ``(N, C)`` and returns an fp32
 loss.  With ``parallel=True`` the class dimension is sharded over the
-tensor-parallel group (``(N, C / tp)`` per rank) and the per-row statistics are
-combined with two small all-reduces (max; then packed [sum-exp, target logit])
-instead of the reference's three.
+tensor-parallel group (``(N, C / tp)`` per rank) and the per-row statistics of
+all ranks (maximum, sum of exponentials, target logit) travel in ONE small
+all-gather and are combined locally, where the reference issues three all-reduces
+(``bmtrain/loss/cross_entropy.py:46,65,71``).
 """
 from __future__ import annotations
 
@@ -50,14 +51,19 @@ class VPFusedCrossEntropy(torch.autograd.Function):
         t = target.reshape(-1)
         start = rank * n
         mx, se, tl = _ce.row_stats(x, t, start)
-        gmax = mx.clone()
-        if comm is not None:
-            comm.all_reduce(gmax, "max")
-        packed = torch.stack([se * torch.exp(mx - gmax), tl])
-        if comm is not None:
-            comm.all_reduce(packed, "sum")
-        lse = gmax + torch.log(packed[0] + 1e-10)
-        loss = lse - packed[1]
+        if comm is not None and comm.size > 1:
+            # one collective: every rank's (max, sum-exp, target logit) rows; the combination is the usual rescaling of
+            # partial sums to the common maximum (a rank that does not own the target contributes a target logit of 0)
+            mine = torch.stack([mx, se, tl])
+            every = mine.new_zeros((comm.size,) + tuple(mine.shape))
+            comm.all_gather_into(every, mine)
+            gmax = every[:, 0].max(dim=0).values
+            total = (every[:, 1] * torch.exp(every[:, 0] - gmax)).sum(dim=0)
+            tl = every[:, 2].sum(dim=0)
+        else:
+            gmax, total = mx, se
+        lse = gmax + torch.log(total + 1e-10)
+        loss = lse - tl
         ctx.start = start
         ctx.save_for_backward(x, t, lse)
         ctx.logits_shape = logits.shape
