@@ -709,6 +709,9 @@ class AdamOffloadOptimizer(torch.optim.Optimizer):
 
     def load_state_dict(self, state_dict: dict) -> None:
         self._host_state_ready()
+        # the state objects are replaced below: results computed ahead and the second sets of arrays go with the old ones
+        self._drop_ahead()
+        self._ahead_owners = []
         if self._gpu_pipe is not None:
             self._gpu_pipe["host_done"].clear()
         state_dict = deepcopy(state_dict)
