@@ -5,6 +5,11 @@ call keeps ``x`` (and asks autograd to keep its gradient).  After the block,
 ``inspector.get_summary()`` reduces min / max / mean / std (and gradient mean /
 std) over all ranks.  While recording is on, blocks run without activation
 recomputation so that each tensor is seen exactly once and keeps its gradient.
+
+Tensors recorded inside a ``PipelineTransformerBlockList`` exist once per micro-batch and only on the stage that owns
+the layer.  When the context is left, the micro-batch pieces are joined along the batch dimension and every stage
+hands its records to the other stages of its pipeline group, so that every rank lists every layer, in layer order,
+and holds its own share of the batch of each record (reference: ``bmtrain/inspect/tensor.py:28-175``).
 """
 from __future__ import annotations
 
@@ -28,7 +33,20 @@ class InspectTensor:
         self._raw = records
         self.summary = []
         seen: Dict[str, int] = {}
-        for item in records:
+        flat: List[Dict] = []
+        i = 0
+        while i < len(records):
+            marker = records[i].get("pipe_marker")
+            if marker is None:
+                flat.append(records[i])
+                i += 1
+                continue
+            j = i + 1
+            while j < len(records) and (records[j].get("inside_pipe") or {}).get("segment") == marker["segment"]:
+                j += 1
+            flat.extend(_exchange_pipeline_records(records[i + 1:j], marker))
+            i = j
+        for item in flat:
             prefix = f"{item['group']}." if item["group"] is not None else ""
             base = prefix + item["name"]
             idx = seen.get(base, 0)
@@ -73,6 +91,57 @@ class InspectTensor:
         return None
 
 
+def _exchange_pipeline_records(local: List[Dict], where: Dict) -> List[Dict]:
+    """Records of one pass through a pipeline: join the micro-batches of this stage, then let every stage in turn
+    broadcast its records over the pipeline group.  Returns the records of all stages in stage order; each tensor (and
+    gradient) is cut down to this rank's share of the batch."""
+    comm = config["pipe_comm"]
+    stages, me, micros = where["stages"], where["stage_id"], where["micros"]
+    per_micro: List[List[Dict]] = [[] for _ in range(micros)]
+    for rec in local:
+        per_micro[rec["inside_pipe"]["micro"]].append(rec)
+    count = len(per_micro[0])
+    assert all(len(m) == count for m in per_micro), "every micro-batch has to record the same tensors"
+    mine = []
+    for k in range(count):
+        pieces = [per_micro[m][k] for m in range(micros)]
+        first = pieces[0]
+        tensor = torch.cat([p["tensor"].detach() for p in pieces], dim=0).contiguous()
+        grads = [p["tensor"].grad for p in pieces]
+        grad = torch.cat(grads, dim=0).contiguous() if first["requires_grad"] and all(g is not None for g in grads) else None
+        mine.append({"name": first["name"], "group": first["group"], "requires_grad": first["requires_grad"], "tensor": tensor,
+                     "grad": grad})
+    from ..store import broadcast_object
+
+    out: List[Dict] = []
+    dev = config["device"]
+    for stage in range(stages):
+        if stage == me:
+            meta = [{"name": r["name"], "group": r["group"], "requires_grad": r["requires_grad"], "shape": tuple(r["tensor"].shape),
+                     "dtype": r["tensor"].dtype, "has_grad": r["grad"] is not None} for r in mine]
+            broadcast_object(meta, comm, src=stage)
+        else:
+            meta = broadcast_object(None, comm, src=stage)
+        for k, info in enumerate(meta):
+            if stage == me:
+                tensor, grad = mine[k]["tensor"], mine[k]["grad"]
+            else:
+                tensor = torch.empty(info["shape"], dtype=info["dtype"], device=dev)
+                grad = torch.empty(info["shape"], dtype=info["dtype"], device=dev) if info["has_grad"] else None
+            if comm.size > 1:
+                comm.broadcast(tensor, stage)
+                if grad is not None:
+                    comm.broadcast(grad, stage)
+            share = tensor.chunk(stages, dim=0)[me].clone()
+            if info["has_grad"]:
+                share.requires_grad_()
+                share.grad = grad.chunk(stages, dim=0)[me].clone()
+            out.append({"name": info["name"], "group": info["group"], "shape": tuple(share.shape), "tensor": share,
+                        "requires_grad": info["requires_grad"], "min": None, "max": None, "mean": None, "std": None,
+                        "grad_mean": None, "grad_std": None, "inside_pipe": {"stage_id": stage}})
+    return out
+
+
 class InspectTensorManager:
     def __init__(self) -> None:
         self._inspector: Optional[InspectTensor] = None
@@ -107,5 +176,6 @@ def record_tensor(x: torch.Tensor, name: str, group: Optional[str] = None) -> No
         x.retain_grad()
     debug.append("_inspect_hidden_states", {
         "name": name, "group": group, "shape": tuple(x.shape), "tensor": x, "requires_grad": x.requires_grad,
-        "min": None, "max": None, "mean": None, "std": None, "grad_mean": None, "grad_std": None, "inside_pipe": None,
+        "min": None, "max": None, "mean": None, "std": None, "grad_mean": None, "grad_std": None,
+        "inside_pipe": debug.get("_inspect_pipe"),   # set while a pipeline stage runs its layers on a micro-batch
     })

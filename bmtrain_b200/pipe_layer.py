@@ -26,6 +26,7 @@ from typing import Dict, Iterable, Iterator, List, Union
 import torch
 
 from . import block_layer as _bl
+from . import debug
 from .block_layer import Block, _block_wrapper
 from .distributed.ops import recv_activations, send_activations
 from .global_var import config
@@ -221,8 +222,18 @@ class PipelineTransformerBlockList(torch.nn.Module):
         gathered, args_list = PipePreFunction.apply(hidden_state, *args, batch_related)
         micro_inputs = gathered.flatten(0, 1).chunk(micros, dim=0)
         outputs, hidden_states = [], []
+        recording = debug.get("_inspect_tensor", False)
+        if recording:
+            # tensors recorded inside the stages are put together across micro-batches and stages when the inspector is
+            # read: a marker tells it (on every rank of the pipeline group, with or without records) where a pass begins
+            segment = debug.get("_inspect_pipe_segments", 0) + 1
+            debug.set("_inspect_pipe_segments", segment)
+            where = {"segment": segment, "stage_id": self.stage_id, "stages": self.stages, "micros": micros}
+            debug.append("_inspect_hidden_states", {"pipe_marker": dict(where)})
         for micro_idx, (x, arg) in enumerate(zip(micro_inputs, args_list)):
             seen = []
+            if recording:
+                debug.set("_inspect_pipe", dict(where, micro=micro_idx))
             x = StagePreFunction.apply(x, self.stage_id)
             for layer_id in self.layer_ids:
                 block = self._modules[str(layer_id)]
@@ -234,6 +245,8 @@ class PipelineTransformerBlockList(torch.nn.Module):
             outputs.append(x)
             if return_hidden_states:
                 hidden_states.append(torch.stack(seen, dim=0))
+        if recording:
+            debug.set("_inspect_pipe", None)
         _reap_sends()
         last_hidden = torch.cat(outputs, dim=0)
         if not return_hidden_states:

@@ -238,3 +238,61 @@ def _local_grad(bmt, mod, inner, name):
 
 def test_tp_linear_modules_cpu():
     run_distributed("test_tp_pp_cpu", "body_tp_linear_modules", 2, init_kwargs=dict(tp_size=2))
+
+
+def body_inspect_in_pipeline():
+    """``record_tensor`` inside the blocks of a pipeline (the intent of the reference's ``tests/test_inspector_hidden.py``):
+    every rank lists every layer in order, statistics and gradient statistics equal those of the same network run in one
+    process on the batches of all ranks."""
+    import bmtrain_b200 as bmt
+
+    rank, world = bmt.rank(), bmt.world_size()
+    torch.manual_seed(21)
+    weights = [torch.randn(8, 8) * 0.5 for _ in range(4)]
+
+    class Layer(bmt.DistributedModule):
+        def __init__(self, w):
+            super().__init__()
+            self.fc = bmt.nn.Linear(8, 8, bias=False, dtype=torch.float32)
+            self._w = w
+
+        def forward(self, x):
+            bmt.inspect.record_tensor(x, "hidden")
+            return torch.tanh(self.fc(x))
+
+    layers = [Layer(w) for w in weights]
+    net = bmt.PipelineTransformerBlockList(layers)
+    bmt.init_parameters(net)
+    net.load_state_dict({f"{i}.fc.weight": w for i, w in enumerate(weights)})
+    data = torch.randn(world, 4, 8, generator=torch.Generator().manual_seed(5))
+    x = data[rank].clone().requires_grad_()
+    with bmt.inspect.inspect_tensor() as insp:
+        out = net(x)
+        (out * out).sum().backward()
+    summary = insp.get_summary()
+    assert [s["name"] for s in summary] == [f"{i}.hidden" for i in range(4)], [s["name"] for s in summary]
+
+    # one process, all data
+    ref_x = data.reshape(-1, 8).clone().requires_grad_()
+    hidden, h = [], ref_x
+    for w in weights:
+        h.retain_grad()
+        hidden.append(h)
+        h = torch.tanh(h @ w.t())
+    (h * h).sum().backward()
+    for got, want in zip(summary, hidden):
+        assert got["shape"][1:] == (8,), got["shape"]
+        assert abs(got["mean"] - want.mean().item()) < 1e-5, (got["name"], got["mean"], want.mean().item())
+        assert abs(got["max"] - want.max().item()) < 1e-5 and abs(got["min"] - want.min().item()) < 1e-5
+        assert got["grad_mean"] is not None
+        assert abs(got["grad_mean"] - want.grad.mean().item()) < 1e-5, (got["name"], got["grad_mean"], want.grad.mean().item())
+    t = insp.get_tensor("hidden", index=3)
+    assert t is not None and t.shape[1:] == (8,)
+
+
+def test_inspect_inside_pipeline_cpu():
+    run_distributed("test_tp_pp_cpu", "body_inspect_in_pipeline", 2, init_kwargs=dict(pipe_size=2, num_micro_batches=2))
+
+
+def test_inspect_inside_pipeline_with_zero_cpu():
+    run_distributed("test_tp_pp_cpu", "body_inspect_in_pipeline", 4, init_kwargs=dict(pipe_size=2, num_micro_batches=2))
