@@ -296,3 +296,59 @@ def test_inspect_inside_pipeline_cpu():
 
 def test_inspect_inside_pipeline_with_zero_cpu():
     run_distributed("test_tp_pp_cpu", "body_inspect_in_pipeline", 4, init_kwargs=dict(pipe_size=2, num_micro_batches=2))
+
+
+def body_init_parameters_in_lists(tmp):
+    """``init_parameters`` draws what a single process draws under the same seed, whichever list type holds the layers and
+    whichever stage owns them (the intent of the reference's ``tests/test_init_parameters_multi_gpu.py:98-141``)."""
+    import os
+
+    import bmtrain_b200 as bmt
+
+    class Lin(bmt.DistributedModule):
+        def __init__(self):
+            super().__init__()
+            self.weight = bmt.DistributedParameter(torch.empty(5, 3), init_method=torch.nn.init.xavier_normal_)
+            self.bias = bmt.DistributedParameter(torch.empty(5), init_method=torch.nn.init.zeros_)
+
+        def forward(self, x):
+            return torch.nn.functional.linear(x, self.weight, self.bias)
+
+    torch.manual_seed(33)
+    want = {}
+    for i in range(2):
+        w = torch.empty(5, 3)
+        torch.nn.init.xavier_normal_(w)
+        want[f"l.{i}.weight"], want[f"l.{i}.bias"] = w, torch.zeros(5)
+
+    def holder(make_list):
+        class Net(bmt.DistributedModule):
+            def __init__(self):
+                super().__init__()
+                self.l = make_list([Lin(), Lin()])
+
+        return Net()
+
+    kinds = {
+        "pipeline": lambda layers: bmt.PipelineTransformerBlockList(layers),
+        "block list": lambda layers: bmt.TransformerBlockList(layers),
+        "checkpoint blocks": lambda layers: torch.nn.ModuleList([bmt.CheckpointBlock(layer) for layer in layers]),
+    }
+    path = os.path.join(tmp, "init.pt")
+    for kind, make_list in kinds.items():
+        torch.manual_seed(33)
+        net = holder(make_list)
+        bmt.init_parameters(net)
+        bmt.save(net, path)
+        bmt.synchronize()
+        if bmt.rank() == 0:
+            got = torch.load(path)
+            assert list(got.keys()) == list(want.keys()), (kind, list(got.keys()))
+            for k, v in want.items():
+                assert torch.equal(got[k], v), (kind, k)
+        bmt.synchronize()
+
+
+def test_init_parameters_in_lists_cpu(tmp_path):
+    run_distributed("test_tp_pp_cpu", "body_init_parameters_in_lists", 2, init_kwargs=dict(pipe_size=2, num_micro_batches=2),
+                    tmp=str(tmp_path))
