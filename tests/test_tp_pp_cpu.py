@@ -352,3 +352,63 @@ def body_init_parameters_in_lists(tmp):
 def test_init_parameters_in_lists_cpu(tmp_path):
     run_distributed("test_tp_pp_cpu", "body_init_parameters_in_lists", 2, init_kwargs=dict(pipe_size=2, num_micro_batches=2),
                     tmp=str(tmp_path))
+
+
+def body_pipeline_hidden_states():
+    """``return_hidden_states=True`` through a pipeline with several micro-batches: the stacked per-layer inputs equal those
+    of a single process, and a loss that also uses the middle hidden states gives the single-process gradients (the intent
+    of the reference's ``tests/test_middle_hidden.py:120-190`` for its pipeline model)."""
+    import bmtrain_b200 as bmt
+
+    rank, world = bmt.rank(), bmt.world_size()
+    torch.manual_seed(8)
+    weights = [torch.randn(6, 6) * 0.4 for _ in range(4)]
+
+    class Lin(bmt.DistributedModule):
+        def __init__(self):
+            super().__init__()
+            self.fc = bmt.nn.Linear(6, 6, bias=False, dtype=torch.float32)
+
+        def forward(self, x):
+            return torch.tanh(self.fc(x))
+
+    net = bmt.PipelineTransformerBlockList([Lin() for _ in weights])
+    bmt.init_parameters(net)
+    net.load_state_dict({f"{i}.fc.weight": w for i, w in enumerate(weights)})
+    data = torch.randn(world, 4, 6, generator=torch.Generator().manual_seed(2))
+    x = data[rank].clone().requires_grad_()
+    last, hidden = net(x, return_hidden_states=True)
+    assert hidden.shape == (4, 4, 6), hidden.shape          # (layers, this rank's batch, features)
+    loss = (last * last).sum() + sum((i + 1) * hidden[i].sum() for i in range(4))
+    loss.backward()
+    bmt.synchronize()
+
+    ws = [w.clone().requires_grad_() for w in weights]
+    grads_x = []
+    for d in range(world):
+        xr = data[d].clone().requires_grad_()
+        h, seen = xr, []
+        for w in ws:
+            seen.append(h)
+            h = torch.tanh(h @ w.t())
+        ((h * h).sum() + sum((i + 1) * seen[i].sum() for i in range(4))).backward()
+        grads_x.append(xr.grad)
+        if d == rank:
+            assert torch.allclose(last, h, atol=1e-5)
+            for i in range(4):
+                assert torch.allclose(hidden[i], seen[i], atol=1e-5), i
+    assert torch.allclose(x.grad, grads_x[rank], atol=1e-5)
+    # weight gradients: the sum over the data of every rank that shares the layer's ZeRO group and pipeline group
+    got = {r["name"]: r for r in bmt.inspect.inspect_model(net, "*")}
+    for i, w in enumerate(ws):
+        name = f"{i}.fc.weight"
+        if name in got:
+            assert abs(got[name]["grad_std"] - w.grad.std().item()) < 1e-4 * max(1.0, w.grad.std().item()), name
+
+
+def test_pipeline_hidden_states_cpu():
+    run_distributed("test_tp_pp_cpu", "body_pipeline_hidden_states", 2, init_kwargs=dict(pipe_size=2, num_micro_batches=2))
+
+
+def test_pipeline_hidden_states_with_zero_cpu():
+    run_distributed("test_tp_pp_cpu", "body_pipeline_hidden_states", 4, init_kwargs=dict(pipe_size=2, num_micro_batches=4))
