@@ -412,3 +412,30 @@ def test_pipeline_hidden_states_cpu():
 
 def test_pipeline_hidden_states_with_zero_cpu():
     run_distributed("test_tp_pp_cpu", "body_pipeline_hidden_states", 4, init_kwargs=dict(pipe_size=2, num_micro_batches=4))
+
+
+def body_vp_cross_entropy():
+    """Cross-entropy over a vocabulary sharded across the tensor-parallel group equals ``F.cross_entropy`` on the full
+    logits: loss, ignored rows, and the gradient of this rank's slice (intent of ``tests/test_parallel_projection.py``)."""
+    import bmtrain_b200 as bmt
+
+    tp, r = bmt.config["tp_size"], bmt.config["topology"].tp_id
+    torch.manual_seed(4)
+    full = (torch.randn(37, 16 * tp) * 3).requires_grad_()
+    target = torch.randint(0, 16 * tp, (37,))
+    target[5] = target[20] = -100
+    want = torch.nn.functional.cross_entropy(full, target, ignore_index=-100)
+    want.backward()
+    mine = full.detach()[:, r * 16:(r + 1) * 16].clone().requires_grad_()
+    loss = bmt.loss.FusedCrossEntropy(ignore_index=-100, parallel=True)(mine, target)
+    loss.backward()
+    assert abs(loss.item() - want.item()) < 1e-5, (loss.item(), want.item())
+    assert torch.allclose(mine.grad, full.grad[:, r * 16:(r + 1) * 16], atol=1e-6)
+    none = bmt.loss.FusedCrossEntropy(ignore_index=-100, parallel=True, reduction="none")(mine.detach(), target)
+    assert none[5].item() == 0.0 and none[20].item() == 0.0
+    ref_rows = torch.nn.functional.cross_entropy(full.detach(), target, ignore_index=-100, reduction="none")
+    assert torch.allclose(none, ref_rows, atol=1e-5)
+
+
+def test_vp_cross_entropy_cpu():
+    run_distributed("test_tp_pp_cpu", "body_vp_cross_entropy", 2, init_kwargs=dict(tp_size=2))
