@@ -104,6 +104,63 @@ def _make_comm(kind: str, fn: str, rank: int, world_size: int, pipe_size: int, t
     return mine
 
 
+def _read_cpu_list(text: str):
+    """``"0-3,8,10-11"`` -> [0, 1, 2, 3, 8, 10, 11] (format of the kernel's ``cpulist`` files)."""
+    out = []
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        out.extend(range(int(lo), int(hi or lo) + 1))
+    return out
+
+
+def _numa_layout(local_size: int):
+    """(cpus of every NUMA node, node of every local GPU) from sysfs, or None when that cannot be told (one node, no CUDA,
+    no sysfs).  The offloading optimizer streams tens of bytes per parameter between host memory and the cores of its
+    rank: on a host with several sockets those cores and that memory should be the ones the rank's GPU hangs on."""
+    try:
+        nodes = {}
+        base = "/sys/devices/system/node"
+        for entry in os.listdir(base):
+            if entry.startswith("node") and entry[4:].isdigit():
+                with open(os.path.join(base, entry, "cpulist")) as f:
+                    nodes[int(entry[4:])] = _read_cpu_list(f.read())
+        if len(nodes) < 2 or not torch.cuda.is_available():
+            return None
+        gpu_node = []
+        for i in range(local_size):
+            props = torch.cuda.get_device_properties(i)
+            bus = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+            with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+                gpu_node.append(int(f.read().strip()))
+        return nodes, gpu_node
+    except (OSError, AttributeError, ValueError, RuntimeError, AssertionError):
+        return None
+
+
+def _split_cpus(cpus, local_rank: int, local_size: int, layout=None):
+    """The cores of ``cpus`` that local rank ``local_rank`` gets.  Without a NUMA layout: equal consecutive parts.  With
+    one: the cores of the node its GPU is attached to, shared out among the ranks whose GPUs sit on that node (a rank
+    whose node is unknown or has no usable cores falls back to the equal split)."""
+    if local_size <= 1 or len(cpus) < local_size:
+        return list(cpus)
+    per = len(cpus) // local_size
+    equal = list(cpus[local_rank * per:(local_rank + 1) * per])
+    if layout is None:
+        return equal
+    nodes, gpu_node = layout
+    node = gpu_node[local_rank] if local_rank < len(gpu_node) else -1
+    allowed = set(cpus)
+    here = [c for c in nodes.get(node, []) if c in allowed]
+    mates = [r for r in range(local_size) if r < len(gpu_node) and gpu_node[r] == node]
+    if node < 0 or len(here) < len(mates) or local_rank not in mates:
+        return equal
+    share = len(here) // len(mates)
+    k = mates.index(local_rank)
+    return here[k * share:(k + 1) * share]
+
+
 def _partition_cpus(local_rank: int, local_size: int):
     try:
         cpus = sorted(os.sched_getaffinity(0))
@@ -111,8 +168,7 @@ def _partition_cpus(local_rank: int, local_size: int):
         return None
     if local_size <= 1 or len(cpus) < local_size:
         return cpus
-    per = len(cpus) // local_size
-    mine = cpus[local_rank * per:(local_rank + 1) * per]
+    mine = _split_cpus(cpus, local_rank, local_size, _numa_layout(local_size))
     try:
         os.sched_setaffinity(0, mine)
     except OSError:  # pragma: no cover

@@ -650,3 +650,20 @@ def test_known_gradient_norms_are_only_used_when_they_apply(bmt_cpu):
     assert BL.fused_sq_norms([b2.storage]) == (set(), [])
     BL._fused_buckets.discard(b1)
     BL._fused_buckets.discard(b2)
+
+
+def test_cpu_partition_follows_numa_nodes():
+    """Ranks share out the cores of the NUMA node their GPU is attached to; without a layout the split is even."""
+    from bmtrain_b200.init import _read_cpu_list, _split_cpus
+
+    assert _read_cpu_list("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    cpus = list(range(32))
+    assert _split_cpus(cpus, 1, 4) == list(range(8, 16))
+    nodes = {0: list(range(0, 16)), 1: list(range(16, 32))}
+    layout = (nodes, [0, 0, 0, 1])                       # three GPUs on node 0, one on node 1
+    assert _split_cpus(cpus, 0, 4, layout) == [0, 1, 2, 3, 4]
+    assert _split_cpus(cpus, 2, 4, layout) == [10, 11, 12, 13, 14]
+    assert _split_cpus(cpus, 3, 4, layout) == list(range(16, 32))
+    # a rank whose node is unknown, or whose node has fewer usable cores than ranks, keeps the even split
+    assert _split_cpus(cpus, 1, 4, (nodes, [0, -1, 0, 1])) == list(range(8, 16))
+    assert _split_cpus(list(range(16, 32)), 0, 2, (nodes, [0, 1])) == list(range(16, 24))
